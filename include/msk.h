@@ -1,0 +1,74 @@
+/* C ABI of libmsk_b200.so: one decoder layer's decode step on B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the given CUDA stream
+ * (a cudaStream_t passed as void*), never synchronises and never allocates (except msk_selftest_*
+ * and the *_create/*_workspace_bytes helpers, which say so).  Return value: 0 on success, a
+ * negative code for a rejected call (-1 invalid argument, -2 CUDA error, -3 unsupported shape).
+ * Device-side problems (a bounded wait that expired, an index out of range) do not trap: the
+ * kernel records them in `status`, a device int32[4] owned by the caller:
+ *   status[0] code (1 timeout, 2 bounds, 3 capacity), status[1] kernel<<8|site, status[2..3] detail.
+ * The caller zeroes it once and reads it back outside any timed region.
+ *
+ * Each function names the interface of the reference (Kushagrabainsla/muse-spark-open) that it
+ * stands in for, by path inside that project.
+ */
+#ifndef MSK_H
+#define MSK_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int msk_version(void);
+
+/* Number of SMs / L2 bytes of the current device (for sizing flush buffers and grids). */
+int msk_device_info(int* sm_count, int* l2_bytes);
+
+/* Layout self-test of one tensor-core operand path on a toy product (see csrc/selftest.cu).
+ * Replaces the reference's tools/wg_test.py (muse_attention_decode/tools/wg_test.py:39-126),
+ * which validates MMA descriptor and fragment layouts on a 64x64 toy before the real kernel. */
+int msk_selftest_umma(int mode, const void* a, const void* b, float* d, int n, int* status, void* stream);
+
+/* ---------------------------------------------------------------- skinny BF16 projection
+ * out[M, N] = x[M, K] * W[N, K]^T with FP32 accumulation, M <= 256, K % 64 == 0.
+ * Stands in for muse_bf16_proj/submission.py: `skinny` (pybind, :316-325) / `skinny_kernel`
+ * (:161-286) behind `kernel_fn` (:416-436), including the layer hooks `data["out"]` (ldo) and
+ * `data["ssq"]` (out_ssq) of :430-435.
+ *
+ * Optional fused epilogue, applied in this order to the FP32 accumulator acc[t, n]:
+ *   acc *= rsqrt(sum_p in_ssq[p*M + t] * in_inv_dim + in_eps)   (RMSNorm of the input rows, folded)
+ *   acc += resid[t*ldr + n]                                       (FP32 residual)
+ *   out (bf16 or fp32) = acc
+ *   out_normed[t*ldn + n] = bf16(acc * (1 + next_norm_w[n]))     (input of the next op, un-normalised)
+ *   out_ssq[tile*M + t] = sum over the tile's 128 columns of acc^2 (tile = n / 128)
+ */
+typedef struct {
+    const void* x;          /* bf16 [M, K], row stride K */
+    const void* w;          /* bf16 [N, K], row stride K */
+    int M, N, K;
+    int splits;             /* split-K ways = cluster size, 1..8; 0 = pick for the device */
+    void* out;              /* [M, ldo] bf16, or fp32 when out_fp32 != 0; may be NULL */
+    int out_fp32;
+    int ldo;
+    const float* in_ssq;    /* [in_ssq_parts, M] partial sums of squares of the un-normalised input, or NULL */
+    int in_ssq_parts;
+    float in_inv_dim;
+    float in_eps;
+    const float* resid;     /* fp32 [M, ldr] or NULL */
+    int ldr;
+    const void* next_norm_w;/* bf16 [N] or NULL */
+    void* out_normed;       /* bf16 [M, ldn] or NULL */
+    int ldn;
+    float* out_ssq;         /* fp32 [ceil(N/128), M] or NULL */
+    int pdl;                /* launch with programmatic stream serialization (the kernel waits for its
+                               predecessor only after it has started streaming W) */
+} MskProjParams;
+
+int msk_proj_skinny(const MskProjParams* p, int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MSK_H */

@@ -1,0 +1,102 @@
+"""ctypes binding of libmsk_b200.so (the C ABI declared in include/msk.h).
+
+The library is the product; this module only loads it, mirrors its parameter structs and turns
+return codes / the device status word into Python exceptions, the way the reference turns a
+failed TORCH_CHECK into one (muse_attention_decode/submission.py:1899).  There is no fallback:
+if the library is missing or a GPU is absent, calls raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG, "libmsk_b200.so")
+
+_lib = None
+
+STATUS_CODES = {1: "a bounded device wait expired", 2: "an index was out of range", 3: "a work list overflowed"}
+RETURN_CODES = {-1: "invalid argument", -2: "CUDA error", -3: "unsupported shape"}
+KERNEL_NAMES = {1: "selftest", 2: "proj_skinny", 3: "attn_decode", 4: "moe_gemm1", 5: "moe_gemm2", 6: "moe_combine",
+                7: "layer_glue", 8: "ep_pack"}
+
+
+class MskError(RuntimeError):
+    pass
+
+
+class ProjParams(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("w", C.c_void_p), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("splits", C.c_int),
+        ("out", C.c_void_p), ("out_fp32", C.c_int), ("ldo", C.c_int),
+        ("in_ssq", C.c_void_p), ("in_ssq_parts", C.c_int), ("in_inv_dim", C.c_float), ("in_eps", C.c_float),
+        ("resid", C.c_void_p), ("ldr", C.c_int),
+        ("next_norm_w", C.c_void_p), ("out_normed", C.c_void_p), ("ldn", C.c_int),
+        ("out_ssq", C.c_void_p), ("pdl", C.c_int),
+    ]
+
+
+def lib() -> C.CDLL:
+    """The loaded library.  Raises if it has not been built (python -m muse_spark_open_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise MskError(f"{LIB_PATH} is missing: build it with `python -m muse_spark_open_b200.build`")
+        _lib = C.CDLL(LIB_PATH)
+        _lib.msk_version.restype = C.c_int
+        for name in EXPORTS:
+            getattr(_lib, name).restype = C.c_int
+    return _lib
+
+
+# every symbol include/msk.h declares
+EXPORTS = ["msk_version", "msk_device_info", "msk_selftest_umma", "msk_proj_skinny"]
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise MskError("the CUDA path needs CUDA tensors; there is no CPU fallback")
+    return t.data_ptr()
+
+
+def stream_ptr() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise MskError(f"{what}: {RETURN_CODES.get(rc, rc)}")
+
+
+class Status:
+    """The device int32[4] status word kernels report into."""
+
+    def __init__(self, device):
+        self.t = torch.zeros(4, dtype=torch.int32, device=device)
+
+    @property
+    def p(self) -> C.c_void_p:
+        return C.c_void_p(self.t.data_ptr())
+
+    def raise_if_set(self, what: str = "") -> None:
+        """Host read (synchronises): call outside timed regions."""
+        s = self.t.tolist()
+        if s[0] != 0:
+            self.t.zero_()
+            kern = KERNEL_NAMES.get(s[1] >> 8, s[1] >> 8)
+            raise MskError(f"{what} device status: {STATUS_CODES.get(s[0], s[0])} in {kern} site {s[1] & 255} "
+                           f"detail {s[2]} {s[3]}")
+
+
+_status: dict = {}
+
+
+def status_for(device) -> Status:
+    key = torch.device(device).index or 0
+    if key not in _status:
+        _status[key] = Status(device)
+    return _status[key]

@@ -1,0 +1,20 @@
+// Host-side construction of TMA tensor maps.  cuTensorMapEncodeTiled is fetched through the
+// runtime (cudaGetDriverEntryPoint), so the library links against cudart only.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace msk {
+
+// Returns 0 on success, a negative MskStatus otherwise.
+// dims/strides are innermost first; strides_bytes[i] is the byte stride of dim i+1 (rank-1 entries).
+int make_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const void* base, const uint64_t* dims,
+              const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle);
+
+// Row-major 2-D matrix [rows, cols] of 2-byte elements, box [box_rows x 64 elements] (128 B), 128-byte swizzle.
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems,
+                      uint32_t box_rows);
+
+}  // namespace msk

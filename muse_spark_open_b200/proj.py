@@ -1,0 +1,74 @@
+"""Skinny BF16 projections: the reference's per-op entry points over the C ABI.
+
+Same call shape as muse_bf16_proj/submission.py: `prepare(weights) -> state` once (untimed),
+`kernel_fn(data, state) -> tensor` per step, with `data = {"x": bf16 [m, k], "config": {"m", "n",
+"k", "layer"}}` (submission.py:23-40,390-436).  Layer names are whatever keys `weights` has; FP32
+weights (the router) are split into BF16 hi + lo halves at prepare time and the two halves are
+accumulated in one FP32 pass (the legal fast path the reference's rules name, reference.py:28-29).
+The layer hooks `data["out"]` (write into a caller-provided, possibly wider buffer) and `data["ssq"]`
+are honoured like submission.py:430-435.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import abi
+
+MAX_M = 256
+
+
+def prepare(weights: dict) -> dict:
+    state = {"w": {}, "fp32": set()}
+    for name, w in weights.items():
+        if w.dim() != 2:
+            continue
+        if not w.is_cuda:
+            raise abi.MskError("prepare() needs CUDA weights")
+        if w.dtype == torch.float32:
+            hi = w.to(torch.bfloat16)
+            lo = (w - hi.float()).to(torch.bfloat16)
+            state["w"][name] = torch.cat([hi, lo], dim=1).contiguous()  # [N, 2K]: x @ hi^T + x @ lo^T in one K loop
+            state["fp32"].add(name)
+        else:
+            state["w"][name] = w.contiguous()
+    abi.lib()
+    return state
+
+
+def skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, fp32_out: bool = False,
+           splits: int = 0, pdl: bool = False, in_ssq=None, in_dim: int = 0, in_eps: float = 0.0, resid=None,
+           next_norm_w=None, out_normed=None, out_ssq=None) -> torch.Tensor:
+    """One launch of msk_proj_skinny.  x bf16 [M, K] contiguous, w bf16 [N, K] contiguous."""
+    m, k = x.shape
+    n = w.shape[0]
+    if out is None and out_normed is None:
+        out = torch.empty((m, n), dtype=torch.float32 if fp32_out else torch.bfloat16, device=x.device)
+    p = abi.ProjParams()
+    p.x, p.w, p.M, p.N, p.K, p.splits = abi.ptr(x), abi.ptr(w), m, n, k, splits
+    if out is not None:
+        p.out, p.out_fp32, p.ldo = abi.ptr(out), int(out.dtype == torch.float32), out.stride(0)
+    if in_ssq is not None:
+        p.in_ssq, p.in_ssq_parts, p.in_inv_dim, p.in_eps = abi.ptr(in_ssq), in_ssq.shape[0], 1.0 / in_dim, in_eps
+    if resid is not None:
+        p.resid, p.ldr = abi.ptr(resid), resid.stride(0)
+    if out_normed is not None:
+        p.next_norm_w, p.out_normed, p.ldn = abi.ptr(next_norm_w), abi.ptr(out_normed), out_normed.stride(0)
+    if out_ssq is not None:
+        p.out_ssq = abi.ptr(out_ssq)
+    p.pdl = int(pdl)
+    st = abi.status_for(x.device)
+    abi.check(abi.lib().msk_proj_skinny(C.byref(p), st.p, abi.stream_ptr()), "msk_proj_skinny")
+    return out
+
+
+def kernel_fn(data: dict, state: dict) -> torch.Tensor:
+    x, cfg = data["x"], data["config"]
+    m, n, layer = cfg["m"], cfg["n"], cfg["layer"]
+    if m > MAX_M:
+        raise abi.MskError(f"projection built for decode/verify steps of up to {MAX_M} tokens, got {m}")
+    w = state["w"][layer][:n]
+    if layer in state["fp32"]:
+        return skinny(torch.cat([x, x], dim=1), w, fp32_out=True)
+    return skinny(x, w, out=data.get("out"), out_ssq=data.get("ssq"))
