@@ -68,6 +68,40 @@ typedef struct {
 
 int msk_proj_skinny(const MskProjParams* p, int* status, void* stream);
 
+/* ---------------------------------------------------------------- gated attention decode / verify
+ * One decode step (L = 1) or one 8-token verify block (L = 8, causal inside the block) of gated
+ * attention over a paged FP8-E4M3 KV cache: per-head RMSNorm of q and k, q * qk_scale_factor,
+ * interleaved RoPE, the new tokens' K/V quantised and written into the cache at `cache_loc`,
+ * softmax(q.k * sm_scale) over the visible keys (sliding window: a token and the window-1 before it;
+ * window 0 = all), output RMSNorm per head times sigmoid(gate), BF16.
+ * Stands in for muse_attention_decode/submission.py `kernel_fn` (:2363-2372) and the kernels behind it
+ * (`attnc_kernel` :1604-1856, `attnpcc_kernel` :1915-2284, `attn_kernel` + `_prep` + `_attn_combine`
+ * :293-539,115-173); the fields mirror its `Inputs` / `Config` (:37-65).
+ * Built for head_dim 128, Hq = 8 * Hkv, page_size a power of two in [8, 128].
+ */
+typedef struct {
+    const void* qkv;          /* bf16 [B*L, ld_qkv]: q (Hq*d) | k (Hkv*d) | v (Hkv*d) | gate (Hq*d) per token */
+    int ld_qkv;
+    void* out;                /* bf16 [B*L, ld_out], Hq*d values per token */
+    int ld_out;
+    void* k_cache;            /* e4m3 [num_pages, page_size, Hkv, d], new rows written in place */
+    void* v_cache;
+    const float* k_scale;     /* device scalars: value = e4m3 * scale */
+    const float* v_scale;
+    const int32_t* seq_lens;  /* [B] cached tokens per request; the block starts at this position */
+    const int32_t* page_table;/* [B, max_pages] physical page of each logical page, -1 = none */
+    int max_pages;
+    const int64_t* cache_loc; /* [B*L] flat cache row (page * page_size + slot) of each new token */
+    const float* inv_freq;    /* [d/2] RoPE frequencies theta^(-2i/d) as FP32, or NULL for no RoPE */
+    int B, L, Hq, Hkv, d, page_size, num_pages, window;
+    float qk_scale_factor, sm_scale;
+    int chunks;               /* split-KV ways = cluster size (1, 2, 4 or 8); 0 = pick */
+    int stages;               /* K/V tile ring depth (2..4); 0 = pick */
+    int pdl;
+} MskAttnParams;
+
+int msk_attn_decode(const MskAttnParams* p, int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -52,7 +52,7 @@ def lib() -> C.CDLL:
 
 
 # every symbol include/msk.h declares
-EXPORTS = ["msk_version", "msk_device_info", "msk_selftest_umma", "msk_proj_skinny"]
+EXPORTS = ["msk_version", "msk_device_info", "msk_selftest_umma", "msk_proj_skinny", "msk_attn_decode"]
 
 
 def ptr(t: torch.Tensor | None) -> int | None:
@@ -100,3 +100,16 @@ def status_for(device) -> Status:
     if key not in _status:
         _status[key] = Status(device)
     return _status[key]
+
+
+class AttnParams(C.Structure):
+    _fields_ = [
+        ("qkv", C.c_void_p), ("ld_qkv", C.c_int), ("out", C.c_void_p), ("ld_out", C.c_int),
+        ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("k_scale", C.c_void_p), ("v_scale", C.c_void_p),
+        ("seq_lens", C.c_void_p), ("page_table", C.c_void_p), ("max_pages", C.c_int),
+        ("cache_loc", C.c_void_p), ("inv_freq", C.c_void_p),
+        ("B", C.c_int), ("L", C.c_int), ("Hq", C.c_int), ("Hkv", C.c_int), ("d", C.c_int), ("page_size", C.c_int),
+        ("num_pages", C.c_int), ("window", C.c_int),
+        ("qk_scale_factor", C.c_float), ("sm_scale", C.c_float),
+        ("chunks", C.c_int), ("stages", C.c_int), ("pdl", C.c_int),
+    ]

@@ -1,0 +1,563 @@
+// Gated attention decode (L = 1) and 8-token verify (L = 8) over a paged FP8-E4M3 KV cache, one launch.
+//
+// Grid (chunks C, KV heads, requests); the C CTAs of one (request, KV head) form a thread block
+// cluster and split that request's cached keys between them (split-KV).  One CTA = 128 threads.
+//
+// Per 128-key tile (two 64-token pages, or 128 / page_size pages):
+//   TMA      4-D boxes [page_size tokens x 128 B] of K and of V land in shared memory with the
+//            128-byte swizzle; the physical page id from the block table is a runtime coordinate.
+//   MMA 1    S^T[key, row] = K[key, :] . Q[row, :]   tcgen05.mma kind::f8f6f4, M = 128 keys,
+//            N = 8 L query rows (row = 8 * token + head-in-group), K = head_dim 128.
+//            The FP8 cache bytes are the A operand as they are (exact, no conversion); the query,
+//            rounded to BF16 like the reference, is split into two E4M3 terms q = hi + lo
+//            (two accumulating passes), which keeps BF16-level precision on FP8 tensor cores.
+//   softmax  thread = key: tcgen05.ld its row of S^T, scale, window / causal mask, running maximum
+//            per query row (redux.sync over the warp, shared memory over the 4 warps), p = 2^(s-m)
+//            split into an E4M3 and an E5M2 term, written as the K-major B operand P[row, key].
+//   MMA 2    O^T[d, row] = V^T[d, key] . P[row, key]; V stays as stored (MN-major A operand).
+//   acc      thread = d: o[row] = o[row] * alpha[row] + O^T[d, row]  (FP32 registers).
+// The L new tokens never travel through global memory: the last CTA of the cluster applies
+// RMSNorm + RoPE to the new keys, quantises keys and values to E4M3, writes them to the cache
+// rows `cache_loc` and attends them from registers / shared memory in FP32.
+// Merge: every CTA pushes its (m, l, o) partials for the query rows another CTA owns into that
+// CTA's shared memory (DSMEM), one cluster barrier, then each owner merges, applies the per-head
+// RMSNorm and the sigmoid gate and stores BF16.
+// Roofline: HBM (K and V bytes of the visible keys, read once).
+#include <cuda_fp8.h>
+
+#include "msk.h"
+#include "ptx.cuh"
+#include "tmap.cuh"
+
+namespace msk {
+
+constexpr int kAttnMaxStages = 4;
+constexpr int kTileKeys = 128;
+constexpr int kStageBytes = 2 * kTileKeys * 128;  // K tile + V tile
+constexpr int kMaxTilesPerCta = 160;
+constexpr float kNeg = -1.0e30f;
+constexpr float kPScale = 256.0f;  // p in [0, 1] is stored as p * 256 (E4M3 / E5M2 range)
+
+struct AttnArgs {
+    const __nv_bfloat16* qkv;
+    int ld_qkv;
+    __nv_bfloat16* out;
+    int ld_out;
+    uint8_t* k_cache;
+    uint8_t* v_cache;
+    const float* k_scale;
+    const float* v_scale;
+    const int* seq_lens;
+    const int* page_table;
+    int max_pages;
+    const long long* cache_loc;
+    const float* inv_freq;
+    int B, Hq, Hkv, page_size, num_pages, window, nstages;
+    float qk_scale_factor, sm_scale, q_split_scale;
+    int* status;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float redux_max(float v) {
+    float r;
+    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+    return r;
+}
+__device__ __forceinline__ uint32_t f2_to_e4m3x2(float a, float b) {
+    return __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+}
+__device__ __forceinline__ float e4m3_to_f(uint32_t byte) {
+    __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(byte), __NV_E4M3);
+    return __half2float(*reinterpret_cast<__half*>(&h));
+}
+__device__ __forceinline__ uint32_t f_to_e4m3(float a) {
+    return __nv_cvt_float_to_fp8(a, __NV_SATFINITE, __NV_E4M3);
+}
+__device__ __forceinline__ uint32_t f_to_e5m2(float a) {
+    return __nv_cvt_float_to_fp8(a, __NV_SATFINITE, __NV_E5M2);
+}
+
+// RMSNorm (weightless, eps 1e-5) and interleaved RoPE of one 128-wide head row held 4 values per lane.
+__device__ __forceinline__ void norm_rope_row(float (&x)[4], float post_scale, const float* inv_freq, int pos, int lane) {
+    float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss * (1.0f / 128.0f) + 1e-5f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) x[i] = (x[i] * r) * post_scale;
+    if (inv_freq != nullptr) {
+        const float fp = static_cast<float>(pos);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float ang = fp * inv_freq[2 * lane + h];
+            const float c = cosf(ang), s = sinf(ang);
+            const float e = x[2 * h], o = x[2 * h + 1];
+            x[2 * h] = e * c - o * s;
+            x[2 * h + 1] = e * s + o * c;
+        }
+    }
+}
+
+template <int L>
+__global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUtensorMap tm_k,
+                                                   const __grid_constant__ CUtensorMap tm_v, AttnArgs p) {
+    constexpr int NR = 8 * L;                 // query rows per KV head
+    constexpr int NP = NR < 16 ? 16 : NR;     // UMMA N
+    constexpr uint32_t kCols = NP <= 16 ? 64 : 256;  // S0 | S1 | O, NP columns each
+    constexpr int QP_BYTES = NP * 128;
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[kAttnMaxStages + 3];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int page_ids[kMaxTilesPerCta * 2];
+    __shared__ float m_s[NR], alpha_s[NR], wred[4][NR], mrg_m[NR], mrg_l[NR];
+    __shared__ float sc_tail[NR][L];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int C = gridDim.x, rank = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int where = MSK_K_ATTN << 8;
+    const int nst = p.nstages;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t s_qhi = base + nst * kStageBytes, s_qlo = s_qhi + QP_BYTES, s_phi = s_qlo + QP_BYTES,
+                   s_plo = s_phi + QP_BYTES, s_mrg = s_plo + QP_BYTES;
+    uint8_t* g_qhi = gbase + nst * kStageBytes;
+    float* mrg_o = reinterpret_cast<float*>(g_qhi + 4 * QP_BYTES);  // [NR][128]
+    auto full = [&](int s) { return smem_u32(&bars[s]); };
+    const uint32_t bar_s0 = smem_u32(&bars[kAttnMaxStages]), bar_s1 = smem_u32(&bars[kAttnMaxStages + 1]),
+                   bar_o = smem_u32(&bars[kAttnMaxStages + 2]);
+
+    // ---------------- set-up that does not depend on the previous kernel
+    if (warp == 0) {
+        tmem_alloc(smem_u32(&tmem_slot), kCols);
+        tmem_relinquish();
+    }
+    if (tid == 32) {
+        for (int s = 0; s < nst; ++s) mbar_init(full(s), 1);
+        mbar_init(bar_s0, 1);
+        mbar_init(bar_s1, 1);
+        mbar_init(bar_o, 1);
+        fence_mbar_init();
+    }
+    const int seq = p.seq_lens[b];
+    const int W = p.window;
+    const int lo_all = W > 0 ? max(0, seq - W + 1) : 0;
+    const int tiles_total = seq > 0 ? ((seq - 1) / kTileKeys - lo_all / kTileKeys + 1) : 0;
+    const int t_first = lo_all / kTileKeys;
+    const int per = (tiles_total + C - 1) / C;
+    const int t_begin = t_first + rank * per;
+    int nt = min(per, t_first + tiles_total - t_begin);
+    if (nt < 0) nt = 0;
+    if (nt > kMaxTilesPerCta) {
+        if (tid == 0) report(p.status, MSK_ERR_CAPACITY, where | 1, nt, kMaxTilesPerCta);
+        nt = kMaxTilesPerCta;
+    }
+    const int ppt = kTileKeys / p.page_size;  // pages per tile
+    for (int i = tid; i < nt * ppt; i += 128) {
+        const int pg = t_begin * ppt + i;
+        int id = pg < p.max_pages ? p.page_table[b * p.max_pages + pg] : -1;
+        if (id >= p.num_pages || id < -1) {
+            report(p.status, MSK_ERR_BOUNDS, where | 2, id, p.num_pages);
+            id = -1;
+        }
+        page_ids[i] = id;
+    }
+    for (int i = tid; i < 4 * QP_BYTES / 16; i += 128) reinterpret_cast<uint4*>(g_qhi)[i] = make_uint4(0, 0, 0, 0);
+    if (tid < NR) m_s[tid] = kNeg;
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    pdl_launch_dependents();
+
+    auto issue_tile = [&](int i) {  // thread 0: TMA for this CTA's tile i into ring slot i % nst
+        const int s = i % nst;
+        const uint32_t kb = base + s * kStageBytes, vb = kb + kTileKeys * 128;
+        mbar_expect_tx(full(s), kStageBytes);
+        for (int j = 0; j < ppt; ++j) {
+            const int id = page_ids[i * ppt + j];
+            tma_load_4d(kb + j * p.page_size * 128, &tm_k, full(s), 0, h, 0, id);
+            tma_load_4d(vb + j * p.page_size * 128, &tm_v, full(s), 0, h, 0, id);
+        }
+    };
+    auto issue_mma1 = [&](int i) {  // thread 0: S^T = K . (q_hi + q_lo)^T into S buffer i & 1
+        const uint32_t kb = base + (i % nst) * kStageBytes;
+        const uint32_t idesc = umma_idesc(128, NP, 0, 0, 0, 0);
+        const uint64_t ad = umma_smem_desc(kb, 16, 1024, kSwizzle128);
+        const uint64_t bh = umma_smem_desc(s_qhi, 16, 1024, kSwizzle128);
+        const uint64_t bl = umma_smem_desc(s_qlo, 16, 1024, kSwizzle128);
+        const uint32_t d = tmem + (i & 1) * NP;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_f8_ss(d, ad + 2 * k, bh + 2 * k, idesc, k != 0);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_f8_ss(d, ad + 2 * k, bl + 2 * k, idesc, 1);
+        umma_commit((i & 1) ? bar_s1 : bar_s0);
+    };
+
+    if (tid == 0) {
+        prefetch_tmap(&tm_k);
+        prefetch_tmap(&tm_v);
+        for (int i = 0; i < nt && i < nst; ++i) issue_tile(i);
+    }
+
+    // ---------------- queries: RMSNorm, scale, RoPE, BF16 rounding, split into two E4M3 terms
+    pdl_wait();
+    const float k_scale = __ldg(p.k_scale), v_scale = __ldg(p.v_scale);
+    const float qs = p.q_split_scale;
+    for (int n = warp; n < NR; n += 4) {
+        const int j = n >> 3, g = n & 7;
+        const size_t tok = static_cast<size_t>(b) * L + j;
+        const __nv_bfloat16* src = p.qkv + tok * p.ld_qkv + (h * 8 + g) * 128 + 4 * lane;
+        const uint2 raw = *reinterpret_cast<const uint2*>(src);
+        float x[4] = {bf16lo(raw.x), bf16hi(raw.x), bf16lo(raw.y), bf16hi(raw.y)};
+        norm_rope_row(x, p.qk_scale_factor, p.inv_freq, seq + j, lane);
+        uint32_t hi = 0, lo = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float q = __bfloat162float(__float2bfloat16(x[i])) * qs;
+            const uint32_t bh = f_to_e4m3(q);
+            const uint32_t bl = f_to_e4m3(q - e4m3_to_f(bh));
+            hi |= bh << (8 * i);
+            lo |= bl << (8 * i);
+        }
+        *reinterpret_cast<uint32_t*>(g_qhi + swz128(n, 4 * lane)) = hi;
+        *reinterpret_cast<uint32_t*>(g_qhi + QP_BYTES + swz128(n, 4 * lane)) = lo;
+    }
+    fence_proxy_async_smem();
+    __syncthreads();
+
+    // ---------------- main loop over this CTA's cached tiles
+    float l_part[NR], o_acc[NR];
+#pragma unroll
+    for (int n = 0; n < NR; ++n) l_part[n] = 0.0f, o_acc[n] = 0.0f;
+    const float s_scale = k_scale * p.sm_scale * 1.4426950408889634f / qs;
+    const uint32_t trow = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    bool ok = true;
+
+    if (tid == 0 && nt > 0) {
+        ok = mbar_wait(full(0), 0, p.status, where | 3);
+        tc_fence_after();
+        if (ok) issue_mma1(0);
+    }
+    __syncwarp();
+    for (int i = 0; i < nt; ++i) {
+        if (tid == 0 && ok && i + 1 < nt) {
+            ok = mbar_wait(full((i + 1) % nst), ((i + 1) / nst) & 1, p.status, where | 4);
+            tc_fence_after();
+            if (ok) issue_mma1(i + 1);
+        }
+        __syncwarp();
+        ok = mbar_wait((i & 1) ? bar_s1 : bar_s0, (i >> 1) & 1, p.status, where | 5) && ok;
+        tc_fence_after();
+        const int pos = (t_begin + i) * kTileKeys + tid;  // this thread's key position
+        const uint32_t srow = trow + (i & 1) * NP;
+        // pass 1: tile maximum per query row
+#pragma unroll
+        for (int c0 = 0; c0 < NR; c0 += 8) {
+            uint32_t v[8];
+            tmem_ld8(srow + c0, v);
+            tmem_wait_ld();
+            const int j = c0 >> 3;
+            const bool vis = pos < seq && (W == 0 || pos > seq + j - W);
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                const float s = vis ? __uint_as_float(v[g]) * s_scale : kNeg;
+                const float mx = redux_max(s);
+                if (lane == 0) wred[warp][c0 + g] = mx;
+            }
+        }
+        __syncthreads();
+        if (tid < NR) {
+            const float mo = m_s[tid];
+            const float mn = fmaxf(fmaxf(fmaxf(wred[0][tid], wred[1][tid]), fmaxf(wred[2][tid], wred[3][tid])), mo);
+            alpha_s[tid] = ex2(mo - mn);
+            m_s[tid] = mn;
+        }
+        // V rows past the cached length may hold anything (even NaN bytes): zero them so that 0 * V stays 0
+        if (pos >= seq) {
+            uint8_t* vrow = gbase + (i % nst) * kStageBytes + kTileKeys * 128 + tid * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) reinterpret_cast<uint4*>(vrow)[c] = make_uint4(0, 0, 0, 0);
+        }
+        __syncthreads();
+        // pass 2: p = 2^(s - m), split into an E4M3 and an E5M2 term, P[row][key] bytes
+#pragma unroll
+        for (int c0 = 0; c0 < NR; c0 += 8) {
+            uint32_t v[8];
+            tmem_ld8(srow + c0, v);
+            tmem_wait_ld();
+            const int j = c0 >> 3;
+            const bool vis = pos < seq && (W == 0 || pos > seq + j - W);
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                const int n = c0 + g;
+                const float pr = vis ? ex2(__uint_as_float(v[g]) * s_scale - m_s[n]) : 0.0f;
+                l_part[n] = l_part[n] * alpha_s[n] + pr;
+                const float ps = pr * kPScale;
+                const uint32_t bh = f_to_e4m3(ps);
+                const uint32_t bl = f_to_e5m2(ps - e4m3_to_f(bh));
+                const uint32_t off = swz128(n, tid);
+                g_qhi[2 * QP_BYTES + off] = static_cast<uint8_t>(bh);
+                g_qhi[3 * QP_BYTES + off] = static_cast<uint8_t>(bl);
+            }
+        }
+        tc_fence_before();
+        fence_proxy_async_smem();
+        __syncthreads();
+        if (tid == 0 && ok) {  // O^T = V^T . (p_hi + p_lo)^T
+            tc_fence_after();
+            const uint32_t vb = base + (i % nst) * kStageBytes + kTileKeys * 128;
+            const uint32_t ih = umma_idesc(128, NP, 0, 0, 1, 0), il = umma_idesc(128, NP, 0, 1, 1, 0);
+            const uint64_t bh = umma_smem_desc(s_phi, 16, 1024, kSwizzle128);
+            const uint64_t bl = umma_smem_desc(s_plo, 16, 1024, kSwizzle128);
+            const uint32_t d = tmem + 2 * NP;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                umma_f8_ss(d, umma_smem_desc(vb + 4096 * k, 1024, 1024, kSwizzle128), bh + 2 * k, ih, k != 0);
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                umma_f8_ss(d, umma_smem_desc(vb + 4096 * k, 1024, 1024, kSwizzle128), bl + 2 * k, il, 1);
+            umma_commit(bar_o);
+        }
+        __syncwarp();
+        ok = mbar_wait(bar_o, i & 1, p.status, where | 6) && ok;
+        tc_fence_after();
+#pragma unroll
+        for (int c0 = 0; c0 < NR; c0 += 8) {
+            uint32_t v[8];
+            tmem_ld8(trow + 2 * NP + c0, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int g = 0; g < 8; ++g) o_acc[c0 + g] = o_acc[c0 + g] * alpha_s[c0 + g] + __uint_as_float(v[g]);
+        }
+        tc_fence_before();
+        if (tid == 0 && ok && i + nst < nt) issue_tile(i + nst);  // both MMAs that read slot i % nst are done
+        __syncwarp();
+    }
+    __syncthreads();
+
+    // ---------------- the L new tokens: last CTA of the cluster, FP32 on CUDA cores
+    if (rank == C - 1) {
+        float* knew = reinterpret_cast<float*>(gbase);                 // [L][128] E4M3 values of the new keys
+        float* vnew = knew + L * 128;                                  // [L][128]
+        __nv_bfloat16* qf = reinterpret_cast<__nv_bfloat16*>(vnew + L * 128);  // [NR][128] BF16 queries
+        for (int j = warp; j < L; j += 4) {
+            const size_t tok = static_cast<size_t>(b) * L + j;
+            const long long row = p.cache_loc[tok];
+            const bool row_ok = row >= 0 && row < static_cast<long long>(p.num_pages) * p.page_size;
+            if (!row_ok && lane == 0) report(p.status, MSK_ERR_BOUNDS, where | 7, static_cast<int>(row), p.num_pages);
+            const __nv_bfloat16* ksrc = p.qkv + tok * p.ld_qkv + (p.Hq + h) * 128 + 4 * lane;
+            const __nv_bfloat16* vsrc = ksrc + p.Hkv * 128;
+            const uint2 kr = *reinterpret_cast<const uint2*>(ksrc), vr = *reinterpret_cast<const uint2*>(vsrc);
+            float kx[4] = {bf16lo(kr.x), bf16hi(kr.x), bf16lo(kr.y), bf16hi(kr.y)};
+            const float vx[4] = {bf16lo(vr.x), bf16hi(vr.x), bf16lo(vr.y), bf16hi(vr.y)};
+            norm_rope_row(kx, 1.0f, p.inv_freq, seq + j, lane);
+            uint32_t kb = 0, vb = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t a = f_to_e4m3(__fdiv_rn(kx[i], k_scale)), c = f_to_e4m3(__fdiv_rn(vx[i], v_scale));
+                kb |= a << (8 * i);
+                vb |= c << (8 * i);
+                knew[j * 128 + 4 * lane + i] = e4m3_to_f(a);
+                vnew[j * 128 + 4 * lane + i] = e4m3_to_f(c);
+            }
+            if (row_ok) {
+                const size_t off = (static_cast<size_t>(row) * p.Hkv + h) * 128 + 4 * lane;
+                *reinterpret_cast<uint32_t*>(p.k_cache + off) = kb;
+                *reinterpret_cast<uint32_t*>(p.v_cache + off) = vb;
+            }
+        }
+        // BF16 queries again (the MMA operands hold them split)
+        for (int n = warp; n < NR; n += 4) {
+            const int j = n >> 3, g = n & 7;
+            const size_t tok = static_cast<size_t>(b) * L + j;
+            const uint2 raw = *reinterpret_cast<const uint2*>(p.qkv + tok * p.ld_qkv + (h * 8 + g) * 128 + 4 * lane);
+            float x[4] = {bf16lo(raw.x), bf16hi(raw.x), bf16lo(raw.y), bf16hi(raw.y)};
+            norm_rope_row(x, p.qk_scale_factor, p.inv_freq, seq + j, lane);
+            *reinterpret_cast<uint2*>(qf + n * 128 + 4 * lane) = make_uint2(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]));
+        }
+        __syncthreads();
+        // scores of (row n, new token r), r <= token of n (causal) and inside the window
+        const float t_scale = k_scale * p.sm_scale * 1.4426950408889634f;
+        for (int e = tid; e < NR * L; e += 128) {
+            const int n = e / L, r = e % L, j = n >> 3;
+            float acc = 0.0f;
+            for (int d = 0; d < 128; d += 2) {
+                const uint32_t qq = *reinterpret_cast<const uint32_t*>(qf + n * 128 + d);
+                acc += bf16lo(qq) * knew[r * 128 + d] + bf16hi(qq) * knew[r * 128 + d + 1];
+            }
+            const bool vis = r <= j && (W == 0 || r > j - W);
+            sc_tail[n][r] = vis ? acc * t_scale : kNeg;
+        }
+        __syncthreads();
+        if (tid < NR) {
+            float mx = m_s[tid];
+            const float mo = mx;
+            for (int r = 0; r < L; ++r) mx = fmaxf(mx, sc_tail[tid][r]);
+            alpha_s[tid] = ex2(mo - mx);
+            m_s[tid] = mx;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int n = 0; n < NR; ++n) {
+            const float a = alpha_s[n], m = m_s[n];
+            float o = o_acc[n] * a;
+            l_part[n] *= a;
+#pragma unroll
+            for (int r = 0; r < L; ++r) {
+                const float sc = sc_tail[n][r];
+                const float pr = sc > 0.5f * kNeg ? ex2(sc - m) : 0.0f;
+                o += pr * kPScale * vnew[r * 128 + tid];
+                if (tid == r) l_part[n] += pr;
+            }
+            o_acc[n] = o;
+        }
+    }
+
+    // ---------------- merge across the cluster
+#pragma unroll
+    for (int n = 0; n < NR; ++n) {
+        const float s = warp_sum(l_part[n]);
+        if (lane == 0) wred[warp][n] = s;
+    }
+    __syncthreads();
+    const int rows_per = NR / C;  // query rows each CTA finalises (C divides NR)
+    if (tid < NR) {
+        const int owner = tid / rows_per, nl = tid % rows_per;
+        const float lsum = (wred[0][tid] + wred[1][tid]) + (wred[2][tid] + wred[3][tid]);
+        dsmem_st_f32(dsmem_addr(smem_u32(&mrg_m[rank * rows_per + nl]), owner), m_s[tid]);
+        dsmem_st_f32(dsmem_addr(smem_u32(&mrg_l[rank * rows_per + nl]), owner), lsum);
+    }
+#pragma unroll
+    for (int n = 0; n < NR; ++n) {
+        const int owner = n / rows_per, nl = n % rows_per;
+        dsmem_st_f32(dsmem_addr(s_mrg + ((rank * rows_per + nl) * 128 + tid) * 4, owner), o_acc[n]);
+    }
+    cluster_sync_all();
+
+    float val[NR];
+#pragma unroll
+    for (int nl = 0; nl < NR; ++nl) {
+        if (nl >= rows_per) break;
+        float mx = kNeg;
+        for (int src = 0; src < C; ++src) mx = fmaxf(mx, mrg_m[src * rows_per + nl]);
+        float lsum = 0.0f, o = 0.0f;
+        for (int src = 0; src < C; ++src) {
+            const float wgt = ex2(mrg_m[src * rows_per + nl] - mx);
+            lsum += wgt * mrg_l[src * rows_per + nl];
+            o += wgt * mrg_o[(src * rows_per + nl) * 128 + tid];
+        }
+        const float vv = lsum > 0.0f ? o * (v_scale / kPScale) / lsum : 0.0f;
+        val[nl] = vv;
+        const float ss = warp_sum(vv * vv);
+        if (lane == 0) wred[warp][nl] = ss;
+    }
+    __syncthreads();
+    if (ok) {
+#pragma unroll
+        for (int nl = 0; nl < NR; ++nl) {
+            if (nl >= rows_per) break;
+            const int n = rank * rows_per + nl, j = n >> 3, g = n & 7;
+            const size_t tok = static_cast<size_t>(b) * L + j;
+            const float ss = (wred[0][nl] + wred[1][nl]) + (wred[2][nl] + wred[3][nl]);
+            const float r = 1.0f / sqrtf(ss * (1.0f / 128.0f) + 1e-5f);
+            const float gate = __bfloat162float(p.qkv[tok * p.ld_qkv + (p.Hq + 2 * p.Hkv + h * 8 + g) * 128 + tid]);
+            const float sg = 1.0f / (1.0f + __expf(-gate));
+            p.out[tok * p.ld_out + (h * 8 + g) * 128 + tid] = __float2bfloat16(val[nl] * r * sg);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, kCols);
+}
+
+template <int L>
+int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
+    constexpr int NR = 8 * L, NP = NR < 16 ? 16 : NR;
+    const int tile_cap = (q->max_pages * q->page_size + kTileKeys - 1) / kTileKeys;
+    int tiles_max = tile_cap;
+    if (q->window > 0) tiles_max = min(tiles_max, q->window / kTileKeys + 2);
+    if (tiles_max < 1) tiles_max = 1;
+    int C = q->chunks;
+    if (C <= 0) {
+        int want = (2 * 148 + q->B * q->Hkv - 1) / (q->B * q->Hkv);  // aim at two CTAs per SM
+        if (want > tiles_max) want = tiles_max;
+        C = 1;
+        while (C < want && C < 8) C *= 2;
+    }
+    if (C != 1 && C != 2 && C != 4 && C != 8) return MSK_ERR_INVALID;
+    if ((tiles_max + C - 1) / C > kMaxTilesPerCta) return MSK_ERR_UNSUPPORTED;
+    int nst = q->stages > 0 ? q->stages : (L == 1 ? 2 : 3);
+    if (nst > kAttnMaxStages) nst = kAttnMaxStages;
+    const int smem = 1024 + nst * kStageBytes + 4 * NP * 128 + NR * 128 * 4;
+
+    CUtensorMap tm_k, tm_v;
+    const uint64_t dims[4] = {128, static_cast<uint64_t>(q->Hkv), static_cast<uint64_t>(q->page_size),
+                              static_cast<uint64_t>(q->num_pages)};
+    const uint64_t strides[3] = {128, static_cast<uint64_t>(q->Hkv) * 128,
+                                 static_cast<uint64_t>(q->Hkv) * 128 * q->page_size};
+    const uint32_t box[4] = {128, 1, static_cast<uint32_t>(q->page_size), 1};
+    int rc = make_tmap(&tm_k, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, q->k_cache, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc == 0)
+        rc = make_tmap(&tm_v, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, q->v_cache, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != 0) return rc;
+
+    AttnArgs a{};
+    a.qkv = static_cast<const __nv_bfloat16*>(q->qkv), a.ld_qkv = q->ld_qkv;
+    a.out = static_cast<__nv_bfloat16*>(q->out), a.ld_out = q->ld_out;
+    a.k_cache = static_cast<uint8_t*>(q->k_cache), a.v_cache = static_cast<uint8_t*>(q->v_cache);
+    a.k_scale = q->k_scale, a.v_scale = q->v_scale, a.seq_lens = q->seq_lens, a.page_table = q->page_table;
+    a.max_pages = q->max_pages, a.cache_loc = reinterpret_cast<const long long*>(q->cache_loc), a.inv_freq = q->inv_freq;
+    a.B = q->B, a.Hq = q->Hq, a.Hkv = q->Hkv, a.page_size = q->page_size, a.num_pages = q->num_pages;
+    a.window = q->window, a.nstages = nst, a.qk_scale_factor = q->qk_scale_factor, a.sm_scale = q->sm_scale;
+    // largest power of two that keeps |q| * scale <= 448 (|q| <= qk_scale_factor * sqrt(128) after RMSNorm)
+    float qs = 1.0f;
+    const float qmax = fabsf(q->qk_scale_factor) * 11.3137085f;
+    while (qs * 2.0f * qmax <= 448.0f && qs < 65536.0f) qs *= 2.0f;
+    while (qs * qmax > 448.0f && qs > 1.0f / 65536.0f) qs *= 0.5f;
+    a.q_split_scale = qs, a.status = status;
+
+    static int configured = 0;
+    if (smem > configured) {
+        if (cudaFuncSetAttribute(attn_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return MSK_ERR_CUDA;
+        configured = smem;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(C, q->Hkv, q->B);
+    cfg.blockDim = dim3(128, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    int na = 0;
+    attrs[na].id = cudaLaunchAttributeClusterDimension;
+    attrs[na].val.clusterDim.x = C;
+    attrs[na].val.clusterDim.y = 1;
+    attrs[na].val.clusterDim.z = 1;
+    ++na;
+    if (q->pdl) {
+        attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = na;
+    return cudaLaunchKernelEx(&cfg, attn_kernel<L>, tm_k, tm_v, a) == cudaSuccess ? 0 : MSK_ERR_CUDA;
+}
+
+}  // namespace msk
+
+extern "C" int msk_attn_decode(const MskAttnParams* q, int* status, void* stream) {
+    using namespace msk;
+    if (q == nullptr || !q->qkv || !q->out || !q->k_cache || !q->v_cache || !q->k_scale || !q->v_scale ||
+        !q->seq_lens || !q->page_table || !q->cache_loc)
+        return MSK_ERR_INVALID;
+    if (q->d != 128 || q->Hkv < 1 || q->Hq != 8 * q->Hkv || q->B < 1) return MSK_ERR_UNSUPPORTED;
+    if (q->page_size < 8 || q->page_size > 128 || (q->page_size & (q->page_size - 1)) != 0) return MSK_ERR_UNSUPPORTED;
+    if (q->L == 1) return launch_attn<1>(q, status, static_cast<cudaStream_t>(stream));
+    if (q->L == 8) return launch_attn<8>(q, status, static_cast<cudaStream_t>(stream));
+    return MSK_ERR_UNSUPPORTED;
+}
