@@ -140,21 +140,19 @@ __global__ void __launch_bounds__(128) proj_skinny_kernel(const __grid_constant_
     const uint32_t trow = tmem + (static_cast<uint32_t>(warp * 32) << 16);
     const int row = tid, n = n0 + row;
 
+    // The code below runs once per CTA, straight from a cold instruction cache: keep it small
+    // (rolled loops, one TMEM column per step) rather than fast per iteration.
     if (S > 1) {
         if (ok) {
-            for (int c0 = 0; c0 < bn; c0 += 16) {
-                uint32_t v[16];
-                tmem_ld16(trow + c0, v);
+#pragma unroll 1
+            for (int t = 0; t < p.M; ++t) {
+                const int owner = t % S;
+                if (owner == rank) continue;
+                const uint32_t v = tmem_ld1(trow + t);
                 tmem_wait_ld();
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int t = c0 + j, owner = t % S;
-                    if (owner != rank && t < p.M) {
-                        const int slot = (rank - owner - 1 + S) % S;
-                        const uint32_t local = red_base + ((slot * p.red_rows + t / S) * 128 + row) * 4;
-                        dsmem_st_f32(dsmem_addr(local, owner), __uint_as_float(v[j]));
-                    }
-                }
+                const int slot = (rank - owner - 1 + S) % S;
+                const uint32_t local = red_base + ((slot * p.red_rows + t / S) * 128 + row) * 4;
+                dsmem_st_f32(dsmem_addr(local, owner), __uint_as_float(v));
             }
         }
         cluster_sync_all();  // every thread of every CTA, also after a failed wait
@@ -162,33 +160,27 @@ __global__ void __launch_bounds__(128) proj_skinny_kernel(const __grid_constant_
 
     if (ok) {
         const float nw = (p.next_norm_w != nullptr && n < p.N) ? 1.0f + __bfloat162float(p.next_norm_w[n]) : 1.0f;
-        for (int c0 = 0; c0 < bn; c0 += 16) {
-            if (c0 >= p.M) break;
-            uint32_t v[16];
-            tmem_ld16(trow + c0, v);
+#pragma unroll 1
+        for (int t = rank; t < p.M; t += S) {
+            float acc = __uint_as_float(tmem_ld1(trow + t));
             tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const int t = c0 + j;
-                if (t >= p.M || t % S != rank) continue;  // uniform over the CTA
-                float acc = __uint_as_float(v[j]);
-                for (int src = 0; src < S - 1; ++src) acc += red[(src * p.red_rows + t / S) * 128 + row];
-                acc *= rs[t];
-                if (n < p.N) {
-                    if (p.resid != nullptr) acc += __ldcg(p.resid + static_cast<size_t>(t) * p.ldr + n);
-                    if (p.out != nullptr) {
-                        if (p.out_fp32) static_cast<float*>(p.out)[static_cast<size_t>(t) * p.ldo + n] = acc;
-                        else static_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(t) * p.ldo + n] = __float2bfloat16(acc);
-                    }
-                    if (p.out_normed != nullptr)
-                        p.out_normed[static_cast<size_t>(t) * p.ldn + n] = __float2bfloat16(acc * nw);
-                } else {
-                    acc = 0.0f;
+#pragma unroll 1
+            for (int src = 0; src < S - 1; ++src) acc += red[(src * p.red_rows + t / S) * 128 + row];
+            acc *= rs[t];
+            if (n < p.N) {
+                if (p.resid != nullptr) acc += __ldcg(p.resid + static_cast<size_t>(t) * p.ldr + n);
+                if (p.out != nullptr) {
+                    if (p.out_fp32) static_cast<float*>(p.out)[static_cast<size_t>(t) * p.ldo + n] = acc;
+                    else static_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(t) * p.ldo + n] = __float2bfloat16(acc);
                 }
-                if (p.out_ssq != nullptr) {
-                    const float q = warp_sum(acc * acc);
-                    if (lane == 0) wsum[warp][t] = q;
-                }
+                if (p.out_normed != nullptr)
+                    p.out_normed[static_cast<size_t>(t) * p.ldn + n] = __float2bfloat16(acc * nw);
+            } else {
+                acc = 0.0f;
+            }
+            if (p.out_ssq != nullptr) {
+                const float q = warp_sum(acc * acc);
+                if (lane == 0) wsum[warp][t] = q;
             }
         }
         if (p.out_ssq != nullptr) {

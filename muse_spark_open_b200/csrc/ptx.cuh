@@ -68,24 +68,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Wait budget for any single wait.  Legitimate waits here last microseconds.
-constexpr uint64_t kWaitBudgetNs = 400ull * 1000 * 1000;
+// Wait budget for any single wait, in SM clock cycles (about half a second).  Legitimate waits
+// here last microseconds.
+constexpr long long kWaitBudgetCycles = 1000ll * 1000 * 1000;
+constexpr long long kWaitSlowPathCycles = 1ll << 20;
 
-// Bounded wait on an mbarrier phase.  Returns false after the budget, or at once when another
-// thread has already recorded an error in `status` (so that one lost signal does not cost a
-// budget per waiter).
+// Bounded wait on an mbarrier phase.  The fast path only polls the barrier.  After about half a
+// millisecond it also looks at `status` (so that one lost signal does not cost a full budget per
+// waiter) and, once the budget is spent, records MSK_ERR_TIMEOUT and returns false.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int where) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = globaltimer_ns();
+    const long long t0 = clock64();
+    uint32_t spins = 0;
     for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 64; ++i) {
-            if (mbar_try_wait(bar, parity)) return true;
-        }
-        if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return false;
-        if (globaltimer_ns() - t0 > kWaitBudgetNs) {
-            report(status, MSK_ERR_TIMEOUT, where, static_cast<int>(bar), static_cast<int>(parity));
-            return false;
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 1023u) == 0) {
+            const long long dt = clock64() - t0;
+            if (dt > kWaitSlowPathCycles) {
+                if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return false;
+                if (dt > kWaitBudgetCycles) {
+                    report(status, MSK_ERR_TIMEOUT, where, static_cast<int>(bar), static_cast<int>(parity));
+                    return false;
+                }
+            }
         }
     }
 }
@@ -200,6 +205,11 @@ __device__ __forceinline__ void umma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uin
 
 // TMEM <-> registers, shape 32x32b: a warp touches the 32 lanes of its quarter (warp_id % 4),
 // thread i gets lane i, N consecutive 32-bit columns.
+__device__ __forceinline__ uint32_t tmem_ld1(uint32_t taddr) {
+    uint32_t r;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
+    return r;
+}
 __device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&r)[4]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
