@@ -15,6 +15,7 @@
 #ifndef MSK_H
 #define MSK_H
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -101,6 +102,62 @@ typedef struct {
 } MskAttnParams;
 
 int msk_attn_decode(const MskAttnParams* p, int* status, void* stream);
+
+/* ---------------------------------------------------------------- NVFP4 (w4a16) routed experts
+ * Per local (token, slot) pair: h = x . W13[e]^T, inter = bf16(silu(h[:I]) * h[I:]), y = inter . W2[e]^T,
+ * out[token] += topk_weight * rmsnorm(y * (1 + post_norm_w), eps); tokens without a local pair give zeros.
+ * Weights are NVFP4: E2M1 codes (two per byte, low nibble first), one E4M3 scale per 16 values, one FP32
+ * scale per expert.  Stands in for muse_moe_w4a16/submission.py: `prepare` + `_pack_expert` (:793-871),
+ * `moe_forward` (pybind, :730-768) behind `kernel_fn` (:874-897) = `moe_gemm` x2 + `norm_kernel`
+ * (:307-666), with the layer hooks `pre_norm` (x_ssq) and `local_start_dev` of :888-896.
+ */
+typedef struct {
+    const void* w13;     /* uint8 [E, 2I, H/2]: gate rows [0, I) then up rows [I, 2I) */
+    const void* w13_sf;  /* e4m3  [E, 2I, H/16] */
+    const void* w2;      /* uint8 [E, H, I/2] */
+    const void* w2_sf;   /* e4m3  [E, H, I/16] */
+    int E, H, I;         /* H and I multiples of 128 */
+} MskMoeWeights;
+
+/* Bytes of the two repacked weight buffers (lossless: same codes and scales, 9216-byte blocks of
+ * 128 rows x 128 k with the codes' bits permuted for the in-kernel decoder). */
+int msk_moe_packed_bytes(int E, int H, int I, size_t* w13_bytes, size_t* w2_bytes);
+int msk_moe_pack(const MskMoeWeights* w, void* w13_packed, void* w2_packed, void* stream);
+/* Test hook: expand a packed buffer to BF16 [E, R, K] = e2m1 * e4m3 scale (no per-expert scale). */
+int msk_moe_dequant(const void* packed, void* out_bf16, int E, int R, int K, void* stream);
+/* Bytes of the two FP32 scratch buffers msk_moe_forward needs for T tokens. */
+int msk_moe_scratch_bytes(int T, int top_k, int H, int I, int s1, int s2, size_t* h1_bytes, size_t* y_bytes);
+
+typedef struct {
+    const void* x;              /* bf16 [T, ldx] */
+    int ldx;
+    const float* x_ssq;         /* optional: [x_ssq_parts, T] partial sums of squares of the un-normalised */
+    int x_ssq_parts;            /*   rows; gemm 1 then scales row t by rsqrt(sum * x_inv_dim + x_eps)      */
+    float x_inv_dim, x_eps;
+    int32_t* topk_ids;          /* [T, top_k] global expert ids: input, or output when logits != NULL */
+    float* topk_weights;        /* [T, top_k] */
+    const float* logits;        /* optional [T, n_logits]: softmax -> top-k -> renormalise inside the GEMM CTAs */
+    int n_logits;
+    int T, top_k;               /* T <= 256, top_k <= 8 */
+    int local_start, local_count; /* this GPU holds experts [local_start, local_start + local_count) */
+    const void* w13_packed;
+    const void* w2_packed;
+    const float* w13_gs;        /* [local_count] */
+    const float* w2_gs;
+    const void* post_norm_w;    /* bf16 [H] */
+    float post_eps;
+    int H, I;
+    float* h1_part;             /* scratch fp32 [s1, T*top_k, 2I] */
+    float* y_part;              /* scratch fp32 [s2, T*top_k, H] */
+    int s1, s2;                 /* K splits of the two GEMMs (divide H/128 and I/128) */
+    const float* resid;         /* optional fp32 [T, ldr] added to the result */
+    int ldr;
+    void* out;                  /* [T, ldo] bf16, or fp32 when out_fp32 != 0 */
+    int out_fp32, ldo;
+    int pdl;
+} MskMoeParams;
+
+int msk_moe_forward(const MskMoeParams* p, int* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -48,11 +48,23 @@ def lib() -> C.CDLL:
         _lib.msk_version.restype = C.c_int
         for name in EXPORTS:
             getattr(_lib, name).restype = C.c_int
+        vp, ci = C.c_void_p, C.c_int
+        # explicit argument types: a bare Python int would be passed as a 32-bit C int and truncate pointers
+        _lib.msk_device_info.argtypes = [vp, vp]
+        _lib.msk_selftest_umma.argtypes = [ci, vp, vp, vp, ci, vp, vp]
+        _lib.msk_proj_skinny.argtypes = [vp, vp, vp]
+        _lib.msk_attn_decode.argtypes = [vp, vp, vp]
+        _lib.msk_moe_packed_bytes.argtypes = [ci, ci, ci, vp, vp]
+        _lib.msk_moe_pack.argtypes = [vp, vp, vp, vp]
+        _lib.msk_moe_dequant.argtypes = [vp, vp, ci, ci, ci, vp]
+        _lib.msk_moe_scratch_bytes.argtypes = [ci, ci, ci, ci, ci, ci, vp, vp]
+        _lib.msk_moe_forward.argtypes = [vp, vp, vp]
     return _lib
 
 
 # every symbol include/msk.h declares
-EXPORTS = ["msk_version", "msk_device_info", "msk_selftest_umma", "msk_proj_skinny", "msk_attn_decode"]
+EXPORTS = ["msk_version", "msk_device_info", "msk_selftest_umma", "msk_proj_skinny", "msk_attn_decode",
+           "msk_moe_packed_bytes", "msk_moe_pack", "msk_moe_dequant", "msk_moe_scratch_bytes", "msk_moe_forward"]
 
 
 def ptr(t: torch.Tensor | None) -> int | None:
@@ -112,4 +124,23 @@ class AttnParams(C.Structure):
         ("num_pages", C.c_int), ("window", C.c_int),
         ("qk_scale_factor", C.c_float), ("sm_scale", C.c_float),
         ("chunks", C.c_int), ("stages", C.c_int), ("pdl", C.c_int),
+    ]
+
+
+class MoeWeights(C.Structure):
+    _fields_ = [("w13", C.c_void_p), ("w13_sf", C.c_void_p), ("w2", C.c_void_p), ("w2_sf", C.c_void_p),
+                ("E", C.c_int), ("H", C.c_int), ("I", C.c_int)]
+
+
+class MoeParams(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("ldx", C.c_int),
+        ("x_ssq", C.c_void_p), ("x_ssq_parts", C.c_int), ("x_inv_dim", C.c_float), ("x_eps", C.c_float),
+        ("topk_ids", C.c_void_p), ("topk_weights", C.c_void_p), ("logits", C.c_void_p), ("n_logits", C.c_int),
+        ("T", C.c_int), ("top_k", C.c_int), ("local_start", C.c_int), ("local_count", C.c_int),
+        ("w13_packed", C.c_void_p), ("w2_packed", C.c_void_p), ("w13_gs", C.c_void_p), ("w2_gs", C.c_void_p),
+        ("post_norm_w", C.c_void_p), ("post_eps", C.c_float), ("H", C.c_int), ("I", C.c_int),
+        ("h1_part", C.c_void_p), ("y_part", C.c_void_p), ("s1", C.c_int), ("s2", C.c_int),
+        ("resid", C.c_void_p), ("ldr", C.c_int), ("out", C.c_void_p), ("out_fp32", C.c_int), ("ldo", C.c_int),
+        ("pdl", C.c_int),
     ]

@@ -1,0 +1,674 @@
+// NVFP4 (w4a16) routed experts: grouped GEMMs with the routing done inside the GEMM CTAs.
+//
+//   gemm 1   h[pair, 2I] = x[token(pair)] . W13[expert(pair)]^T      (gate rows, then up rows)
+//   gemm 2   y[pair, H]  = bf16(silu(h_gate) * h_up) . W2[expert]^T
+//   combine  out[t] = sum over the token's local (expert) slots of w[t, slot] * rmsnorm(y * (1 + w_post))
+//
+// A "pair" is one (token, routed slot).  Every gemm CTA rebuilds the routing in shared memory (from
+// the given top-k ids, or from router logits: softmax, top-8, renormalise), turns it into per-expert
+// pair lists and walks the work units (expert-group of <= 32 pairs, 128-row tile, K split) that fall
+// to it, so every touched expert's weights stream through the SMs once.
+//
+// One persistent CTA per SM, 18 warps:
+//   warp 0        producer: one untiled bulk copy (TMA) per 128x128 weight block: 8 KB of bit-permuted
+//                 E2M1 codes + 1 KB of E4M3 block scales, repacked at prepare time so that a block is
+//                 one contiguous 9216-byte read and each thread's 16 bytes sit at a conflict-free slot.
+//   warps 6..13   dequant: thread = weight row.  8 codes per word become 4 BF16x2 registers with 3
+//                 shift+mask steps (the permutation puts every code's bits where BF16 wants them,
+//                 magnitudes as BF16 subnormals * 2^-126), times the block scale (E4M3 * 2^100 as BF16)
+//                 with one HMUL2 each: exact E2M1 x E4M3 products * 2^-26, written straight into tensor
+//                 memory (tcgen05.st) as the A operand.  No BF16 round trip through shared memory.
+//   warps 14..17  stage the B operand: the expert-group's token rows of x (gemm 1) or silu(gate)*up
+//                 computed from the gemm-1 partials (gemm 2), K-major with the 128-byte swizzle.
+//   warp 1        one lane issues tcgen05.mma kind::f16, A from TMEM, B from shared memory, FP32
+//                 accumulators in TMEM (double-buffered per unit).
+//   warps 2..5    epilogue: tcgen05.ld, times global scale * 2^26 (and the folded pre-expert RMSNorm row
+//                 scale), plain stores into this K split's FP32 partial buffer.  K splits are summed in a
+//                 fixed order by the consumer, so results are bitwise reproducible and no buffer has to
+//                 be zeroed between calls.
+// Roofline: HBM (0.5625 bytes per weight of every touched expert).
+#include <cuda_fp8.h>
+
+#include "msk.h"
+#include "ptx.cuh"
+
+namespace msk {
+
+constexpr int kBlob = 9216;        // one packed 128-row x 128-k weight block
+constexpr int kBlobScales = 8192;  // offset of the 128 x 8 block scales inside a blob
+constexpr int kNRaw = 16;          // raw ring slots
+constexpr int kNB = 4;             // B ring slots
+constexpr int kBSlot = 8192;       // 32 rows x 256 bytes
+constexpr int kNA = 4;             // A slots in tensor memory, 64 columns each
+constexpr int kGroup = 32;         // pairs per expert-group (UMMA N)
+constexpr int kMaxPairs = 2048;
+constexpr int kMaxExperts = 256;
+constexpr int kMaxGroups = 320;
+constexpr int kMoeThreads = 18 * 32;
+
+// ---------------------------------------------------------------- weight repacking (prepare time)
+// destination bit of (code i, field f) with fields m, e0, e1, s = code bits 0..3
+__constant__ uint8_t kBitPos[8][4] = {{6, 7, 8, 15},   {22, 23, 24, 31}, {3, 4, 5, 12},    {19, 20, 21, 28},
+                                      {0, 1, 2, 9},    {16, 17, 18, 25}, {10, 11, 13, 14}, {26, 27, 29, 30}};
+
+__global__ void moe_pack_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ sf,
+                                uint8_t* __restrict__ packed, int R, int K) {
+    const int kc = blockIdx.x, rt = blockIdx.y, e = blockIdx.z, r = threadIdx.x;
+    const int KC = K / 128, tiles = R / 128;
+    const size_t row = static_cast<size_t>(e) * R + rt * 128 + r;
+    uint8_t* blob = packed + ((static_cast<size_t>(e) * tiles + rt) * KC + kc) * kBlob;
+    for (int q = 0; q < 4; ++q) {
+        uint32_t w[4];
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t src = *reinterpret_cast<const uint32_t*>(codes + row * (K / 2) + (kc * 128 + q * 32 + j * 8) / 2);
+            uint32_t o = 0;
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t c = (src >> (4 * i)) & 0xF;
+                for (int f = 0; f < 4; ++f) o |= ((c >> f) & 1u) << kBitPos[i][f];
+            }
+            w[j] = o;
+        }
+        *reinterpret_cast<uint4*>(blob + q * 2048 + r * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    *reinterpret_cast<uint2*>(blob + kBlobScales + r * 8) =
+        *reinterpret_cast<const uint2*>(sf + row * (K / 16) + kc * 8);
+}
+
+// ---------------------------------------------------------------- dequantisation
+__device__ __forceinline__ uint32_t hmul2_bf16(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+// two E4M3 scale bytes (bits 0..7 and 8..15 of `two`) -> BF16x2 (s0 * 2^100, s1 * 2^100), exact.
+// byte << 4 read as BF16 is s * 2^-120 (subnormals included); two multiplications by 2^110.
+__device__ __forceinline__ uint32_t scale_pair(uint32_t two) {
+    const uint32_t raw = ((two & 0xFFu) << 4) | ((two & 0xFF00u) << 12);
+    return hmul2_bf16(hmul2_bf16(raw, 0x76807680u), 0x76807680u);
+}
+// 8 permuted codes -> 4 BF16x2 registers holding value * scale * 2^-26 (k ascending, low half first)
+__device__ __forceinline__ void dequant_word(uint32_t P, uint32_t s2, uint32_t* r) {
+    constexpr uint32_t M = 0x81C081C0u;
+    r[0] = hmul2_bf16(P & M, s2);
+    r[1] = hmul2_bf16((P << 3) & M, s2);
+    r[2] = hmul2_bf16((P << 6) & M, s2);
+    r[3] = hmul2_bf16(((P >> 4) & 0x00C000C0u) | ((P >> 5) & 0x01000100u) | ((P << 1) & 0x80008000u), s2);
+}
+// one thread's 32 codes (16 bytes) and their 2 block scales -> 16 registers
+__device__ __forceinline__ void dequant_quarter(const uint4 w, uint32_t pair, uint32_t (&r)[16]) {
+    const uint32_t s0 = __byte_perm(pair, 0, 0x1010), s1 = __byte_perm(pair, 0, 0x3232);
+    dequant_word(w.x, s0, r + 0);
+    dequant_word(w.y, s0, r + 4);
+    dequant_word(w.z, s1, r + 8);
+    dequant_word(w.w, s1, r + 12);
+}
+
+// Dequantise packed blocks into plain BF16 [rows, K] (value * scale, no global scale): test hook for
+// the bit-exactness of the in-kernel dequantisation.
+__global__ void moe_dequant_kernel(const uint8_t* __restrict__ packed, __nv_bfloat16* __restrict__ out, int R, int K) {
+    const int kc = blockIdx.x, rt = blockIdx.y, e = blockIdx.z, r = threadIdx.x;
+    const int KC = K / 128, tiles = R / 128;
+    const uint8_t* blob = packed + ((static_cast<size_t>(e) * tiles + rt) * KC + kc) * kBlob;
+    const uint2 sc = *reinterpret_cast<const uint2*>(blob + kBlobScales + r * 8);
+    const uint32_t pairs[4] = {scale_pair(sc.x), scale_pair(sc.x >> 16), scale_pair(sc.y), scale_pair(sc.y >> 16)};
+    __nv_bfloat16* dst = out + (static_cast<size_t>(e) * R + rt * 128 + r) * K + kc * 128;
+    for (int q = 0; q < 4; ++q) {
+        uint32_t v[16];
+        dequant_quarter(*reinterpret_cast<const uint4*>(blob + q * 2048 + r * 16), pairs[q], v);
+        for (int i = 0; i < 16; ++i) {
+            dst[q * 32 + 2 * i] = __float2bfloat16(bf16lo(v[i]) * 67108864.0f);
+            dst[q * 32 + 2 * i + 1] = __float2bfloat16(bf16hi(v[i]) * 67108864.0f);
+        }
+    }
+}
+
+// ---------------------------------------------------------------- grouped GEMM
+struct MoeGemmArgs {
+    const int* ids;          // [T, top_k]
+    const float* wts;        // [T, top_k]
+    const float* logits;     // [T, n_logits] or null
+    int n_logits;
+    int* ids_out;            // written by CTA 0 when routing from logits
+    float* wts_out;
+    int T, top_k, local_start, local_count;
+    const uint8_t* wpacked;
+    const float* gs;         // [local_count]
+    int R, K;                // rows and reduction length per expert
+    const __nv_bfloat16* x;  // gemm 1 B source
+    int ldx;
+    const float* x_ssq;
+    int x_ssq_parts;
+    float x_inv_dim, x_eps;
+    const float* hprev;      // gemm 2 B source: gemm-1 partials [s_prev][T*top_k][2I]
+    int s_prev, inner;
+    float* outp;             // [S][T*top_k][R]
+    int S;
+    int* status;
+};
+
+struct MoeShared {
+    uint64_t raw_full[kNRaw], raw_empty[kNRaw], a_full[kNA], a_empty[kNA], b_full[kNB], b_empty[kNB], d_full[2],
+        d_empty[2];
+    uint32_t tmem_slot;
+    int n_groups;
+    int counts[kMaxExperts];
+    int offs[kMaxExperts + 1];
+    unsigned short ids_s[kMaxPairs];
+    unsigned short pos_s[kMaxPairs];
+    unsigned short list[kMaxPairs];
+    unsigned short g_expert[kMaxGroups], g_off[kMaxGroups], g_n[kMaxGroups];
+    unsigned short seg_cnt[kMoeThreads / 32][kMaxExperts];  // pairs per (warp segment, expert)
+    float rs[kMaxPairs / 8];
+};
+
+// softmax -> top-k -> renormalise for one token, one warp.  Ties go to the lower expert id.
+__device__ void route_token(const float* logits, int n, int top_k, int lane, int* ids, float* wts) {
+    float v[8];
+    float mx = -3.0e38f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int e = lane + 32 * i;
+        v[i] = e < n ? __ldcg(logits + e) : -3.0e38f;
+        mx = fmaxf(mx, v[i]);
+    }
+    mx = warp_max(mx);
+    float sum = 0.0f;
+    int my_id = 0;
+    float my_p = 0.0f;
+    for (int k = 0; k < top_k; ++k) {
+        float best = -3.0e38f;
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (v[i] > best) best = v[i], bi = lane + 32 * i;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) best = ob, bi = oi;
+        }
+        const float pk = __expf(best - mx);
+        sum += pk;
+        if (lane == k) my_id = bi, my_p = pk;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (lane + 32 * i == bi) v[i] = -3.0e38f;
+    }
+    if (lane < top_k) {
+        ids[lane] = my_id;
+        wts[lane] = my_p / sum;
+    }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(MoeGemmArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) MoeShared sh;
+    __shared__ int r_ids[kMoeThreads / 32][8];
+    __shared__ float r_w[kMoeThreads / 32][8];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int where = (MODE == 1 ? MSK_K_MOE1 : MSK_K_MOE2) << 8;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t s_b = base + kNRaw * kBlob;
+    const int P = p.T * p.top_k;
+
+    if (warp == 0) {
+        tmem_alloc(smem_u32(&sh.tmem_slot), 512);
+        tmem_relinquish();
+    }
+    if (tid == 32) {
+        for (int i = 0; i < kNRaw; ++i) mbar_init(smem_u32(&sh.raw_full[i]), 1), mbar_init(smem_u32(&sh.raw_empty[i]), 4);
+        for (int i = 0; i < kNA; ++i) mbar_init(smem_u32(&sh.a_full[i]), 4), mbar_init(smem_u32(&sh.a_empty[i]), 1);
+        for (int i = 0; i < kNB; ++i) mbar_init(smem_u32(&sh.b_full[i]), 4), mbar_init(smem_u32(&sh.b_empty[i]), 1);
+        for (int i = 0; i < 2; ++i) mbar_init(smem_u32(&sh.d_full[i]), 1), mbar_init(smem_u32(&sh.d_empty[i]), 4);
+        fence_mbar_init();
+    }
+    pdl_wait();  // routing (and x / the gemm-1 partials) come from the previous kernel
+    pdl_launch_dependents();
+
+    // ---------------- routing: ids -> per-expert pair lists -> expert-groups
+    if (MODE == 1 && p.logits != nullptr) {
+        for (int t = warp; t < p.T; t += kMoeThreads / 32) {
+            route_token(p.logits + static_cast<size_t>(t) * p.n_logits, p.n_logits, p.top_k, lane, r_ids[warp], r_w[warp]);
+            __syncwarp();
+            if (lane < p.top_k) {
+                sh.ids_s[t * p.top_k + lane] = static_cast<unsigned short>(r_ids[warp][lane]);
+                if (blockIdx.x == 0) {
+                    p.ids_out[t * p.top_k + lane] = r_ids[warp][lane];
+                    p.wts_out[t * p.top_k + lane] = r_w[warp][lane];
+                }
+            }
+            __syncwarp();
+        }
+    } else {
+        for (int i = tid; i < P; i += kMoeThreads) {
+            const int id = __ldcg(p.ids + i);
+            sh.ids_s[i] = static_cast<unsigned short>(id < 0 || id > 65534 ? 65535 : id);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh.tmem_slot;
+    // Position of every pair inside its expert's list = number of earlier pairs of the same expert.
+    // The order must be the same in every CTA (an expert's list is cut into groups that different
+    // CTAs work on), so it is computed by counting, not with atomics: each warp ranks one contiguous
+    // segment of the pairs (match_any inside a 32-pair chunk, running counts across chunks), then the
+    // segments' counts are prefix-summed per expert.
+    constexpr int kWarps = kMoeThreads / 32;
+    const int seg = ((P + kWarps - 1) / kWarps + 31) & ~31;
+    for (int i = lane; i < kMaxExperts; i += 32) sh.seg_cnt[warp][i] = 0;
+    __syncwarp();
+    for (int c0 = warp * seg; c0 < min(P, (warp + 1) * seg); c0 += 32) {
+        const int i = c0 + lane;
+        int e = i < P ? static_cast<int>(sh.ids_s[i]) - p.local_start : -1;
+        if (e >= p.local_count) e = -1;
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        const int rank = __popc(same & ((1u << lane) - 1u));
+        const int before = e >= 0 ? sh.seg_cnt[warp][e] : 0;
+        __syncwarp();
+        if (e >= 0) {
+            sh.pos_s[i] = static_cast<unsigned short>(before + rank);
+            if (rank == 0) sh.seg_cnt[warp][e] = static_cast<unsigned short>(before + __popc(same));
+        }
+        __syncwarp();
+    }
+    __syncthreads();
+    for (int e = tid; e < p.local_count; e += kMoeThreads) {
+        int run = 0;
+        for (int w = 0; w < kWarps; ++w) {
+            const int c = sh.seg_cnt[w][e];
+            sh.seg_cnt[w][e] = static_cast<unsigned short>(run);
+            run += c;
+        }
+        sh.counts[e] = run;
+    }
+    if (MODE == 1 && p.x_ssq != nullptr) {
+        for (int t = tid; t < p.T; t += kMoeThreads) {
+            float s = 0.0f;
+            for (int part = 0; part < p.x_ssq_parts; ++part) s += __ldcg(p.x_ssq + part * p.T + t);
+            sh.rs[t] = rsqrtf(s * p.x_inv_dim + p.x_eps);
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int off = 0, ng = 0;
+        for (int e = 0; e < p.local_count; ++e) {
+            const int n = sh.counts[e];
+            sh.offs[e] = off;
+            for (int g = 0; g < n; g += kGroup) {
+                if (ng < kMaxGroups) {
+                    sh.g_expert[ng] = static_cast<unsigned short>(e);
+                    sh.g_off[ng] = static_cast<unsigned short>(off + g);
+                    sh.g_n[ng] = static_cast<unsigned short>(min(kGroup, n - g));
+                    ++ng;
+                } else {
+                    report(p.status, MSK_ERR_CAPACITY, where | 1, ng, kMaxGroups);
+                }
+            }
+            off += n;
+        }
+        sh.n_groups = ng;
+    }
+    __syncthreads();
+    for (int i = tid; i < P; i += kMoeThreads) {
+        const int e = static_cast<int>(sh.ids_s[i]) - p.local_start;
+        if (e >= 0 && e < p.local_count)
+            sh.list[sh.offs[e] + sh.seg_cnt[i / seg][e] + sh.pos_s[i]] = static_cast<unsigned short>(i);
+    }
+    __syncthreads();
+
+    const int tiles = p.R / 128, KC = p.K / 128, nch = KC / p.S;
+    const int per_group = tiles * p.S;
+    const int n_units = sh.n_groups * per_group;
+
+    if (warp == 0) {
+        // ------------------------------------------------ producer
+        if (lane == 0) {
+            int cc = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+                const int g = u / per_group, rem = u % per_group, tile = rem / p.S, ks = rem % p.S;
+                const uint8_t* src = p.wpacked + ((static_cast<size_t>(sh.g_expert[g]) * tiles + tile) * KC + ks * nch) * kBlob;
+                for (int c = 0; c < nch; ++c, ++cc) {
+                    const int s = cc % kNRaw;
+                    if (cc >= kNRaw) ok = mbar_wait(smem_u32(&sh.raw_empty[s]), ((cc / kNRaw) - 1) & 1, p.status, where | 2);
+                    if (!ok) break;
+                    mbar_expect_tx(smem_u32(&sh.raw_full[s]), kBlob);
+                    bulk_load(base + s * kBlob, src + static_cast<size_t>(c) * kBlob, kBlob, smem_u32(&sh.raw_full[s]));
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issue
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(128, kGroup, 1, 1, 0, 0);
+            int cc = 0, uc = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++uc) {
+                const int db = uc & 1;
+                if (uc >= 2) ok = mbar_wait(smem_u32(&sh.d_empty[db]), ((uc >> 1) - 1) & 1, p.status, where | 3);
+                tc_fence_after();
+                const uint32_t d = tmem + kNA * 64 + db * kGroup;
+                for (int c = 0; c < nch && ok; ++c, ++cc) {
+                    const int as = cc % kNA, bs = cc % kNB;
+                    ok = mbar_wait(smem_u32(&sh.a_full[as]), (cc / kNA) & 1, p.status, where | 4) &&
+                         mbar_wait(smem_u32(&sh.b_full[bs]), (cc / kNB) & 1, p.status, where | 5);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t b0 = umma_smem_desc(s_b + bs * kBSlot, 16, 1024, kSwizzle128);
+                    const uint64_t b1 = umma_smem_desc(s_b + bs * kBSlot + 4096, 16, 1024, kSwizzle128);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        umma_f16_ts(d, tmem + as * 64 + 8 * j, (j < 4 ? b0 : b1) + 2 * (j & 3), idesc, (c | j) != 0);
+                    umma_commit(smem_u32(&sh.a_empty[as]));
+                    umma_commit(smem_u32(&sh.b_empty[bs]));
+                }
+                if (ok) umma_commit(smem_u32(&sh.d_full[db]));
+            }
+        }
+        __syncwarp();
+    } else if (warp < 6) {
+        // ------------------------------------------------ epilogue
+        const int quarter = warp & 3, row = quarter * 32 + lane;
+        int uc = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++uc) {
+            const int g = u / per_group, rem = u % per_group, tile = rem / p.S, ks = rem % p.S;
+            const int db = uc & 1, e = sh.g_expert[g], off = sh.g_off[g], n = sh.g_n[g];
+            ok = mbar_wait(smem_u32(&sh.d_full[db]), (uc >> 1) & 1, p.status, where | 6);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t v[32];
+            const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + kNA * 64 + db * kGroup;
+            tmem_ld16(taddr, *reinterpret_cast<uint32_t(*)[16]>(&v[0]));
+            tmem_ld16(taddr + 16, *reinterpret_cast<uint32_t(*)[16]>(&v[16]));
+            tmem_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sh.d_empty[db]));
+            const float scale = __ldg(p.gs + e) * 67108864.0f;  // global scale * 2^26
+            float* dst = p.outp + (static_cast<size_t>(ks) * P) * p.R + tile * 128 + row;
+#pragma unroll
+            for (int j = 0; j < kGroup; ++j) {
+                if (j < n) {
+                    const int pair = sh.list[off + j];
+                    float val = __uint_as_float(v[j]) * scale;
+                    if (MODE == 1 && p.x_ssq != nullptr) val *= sh.rs[pair / p.top_k];
+                    dst[static_cast<size_t>(pair) * p.R] = val;
+                }
+            }
+        }
+    } else if (warp < 14) {
+        // ------------------------------------------------ dequant: codes + scales -> BF16 A operand in TMEM
+        const int quarter = warp & 3, grp = (warp - 6) >> 2, row = quarter * 32 + lane;
+        int cc = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+            for (int c = 0; c < nch; ++c, ++cc) {
+                if ((cc & 1) != grp) continue;
+                const int rs_ = cc % kNRaw, as = cc % kNA;
+                ok = mbar_wait(smem_u32(&sh.raw_full[rs_]), (cc / kNRaw) & 1, p.status, where | 7);
+                if (ok && cc >= kNA) ok = mbar_wait(smem_u32(&sh.a_empty[as]), ((cc / kNA) - 1) & 1, p.status, where | 8);
+                if (!ok) break;
+                tc_fence_after();
+                const uint8_t* raw = gbase + rs_ * kBlob;
+                const uint2 sc = *reinterpret_cast<const uint2*>(raw + kBlobScales + row * 8);
+                const uint32_t pairs[4] = {scale_pair(sc.x), scale_pair(sc.x >> 16), scale_pair(sc.y), scale_pair(sc.y >> 16)};
+                const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + as * 64;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint32_t r[16];
+                    dequant_quarter(*reinterpret_cast<const uint4*>(raw + q * 2048 + row * 16), pairs[q], r);
+                    tmem_st16(taddr + q * 16, r);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&sh.raw_empty[rs_]));
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&sh.a_full[as]));
+            }
+        }
+    } else {
+        // ------------------------------------------------ B staging
+        const int st = tid - 14 * 32;
+        int cc = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+            const int g = u / per_group, rem = u % per_group, ks = rem % p.S;
+            const int off = sh.g_off[g], n = sh.g_n[g];
+            for (int c = 0; c < nch; ++c, ++cc) {
+                const int bs = cc % kNB;
+                if (cc >= kNB) ok = mbar_wait(smem_u32(&sh.b_empty[bs]), ((cc / kNB) - 1) & 1, p.status, where | 9);
+                if (!ok) break;
+                const int k0 = (ks * nch + c) * 128;
+                uint8_t* slot = gbase + kNRaw * kBlob + bs * kBSlot;
+                for (int item = st; item < n * 16; item += 128) {
+                    const int j = item >> 4, pc = item & 15;
+                    const int pair = sh.list[off + j];
+                    uint4 v;
+                    if (MODE == 1) {
+                        v = __ldcg(reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(pair / p.top_k) * p.ldx + k0 + pc * 8));
+                    } else {
+                        float gte[8], up[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) gte[i] = 0.0f, up[i] = 0.0f;
+                        for (int s = 0; s < p.s_prev; ++s) {
+                            const float* hrow = p.hprev + (static_cast<size_t>(s) * P + pair) * (2 * p.inner) + k0 + pc * 8;
+                            const float4 a0 = __ldcg(reinterpret_cast<const float4*>(hrow));
+                            const float4 a1 = __ldcg(reinterpret_cast<const float4*>(hrow + 4));
+                            const float4 c0 = __ldcg(reinterpret_cast<const float4*>(hrow + p.inner));
+                            const float4 c1 = __ldcg(reinterpret_cast<const float4*>(hrow + p.inner + 4));
+                            gte[0] += a0.x, gte[1] += a0.y, gte[2] += a0.z, gte[3] += a0.w;
+                            gte[4] += a1.x, gte[5] += a1.y, gte[6] += a1.z, gte[7] += a1.w;
+                            up[0] += c0.x, up[1] += c0.y, up[2] += c0.z, up[3] += c0.w;
+                            up[4] += c1.x, up[5] += c1.y, up[6] += c1.z, up[7] += c1.w;
+                        }
+                        float o[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) o[i] = gte[i] / (1.0f + __expf(-gte[i])) * up[i];
+                        v = make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+                    }
+                    *reinterpret_cast<uint4*>(slot + (pc >> 3) * 4096 + swz128(j, (pc & 7) * 16)) = v;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&sh.b_full[bs]));
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+// ---------------------------------------------------------------- post-expert norm + weighted combine
+struct MoeCombineArgs {
+    const int* ids;
+    const float* wts;
+    int top_k, local_start, local_count, H, S, P;
+    const float* yp;            // [S][P][H]
+    const __nv_bfloat16* post_w;
+    float eps;
+    const float* resid;
+    int ldr;
+    void* out;
+    int out_fp32, ldo;
+};
+
+__global__ void __launch_bounds__(256) moe_combine_kernel(MoeCombineArgs p) {
+    __shared__ float red[8][8];
+    __shared__ float rnorm[8];
+    const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pdl_wait();
+    pdl_launch_dependents();
+    int local[8];
+    float w[8];
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+        local[s] = 0, w[s] = 0.0f;
+        if (s < p.top_k) {
+            const int e = __ldcg(p.ids + t * p.top_k + s) - p.local_start;
+            local[s] = e >= 0 && e < p.local_count;
+            w[s] = __ldcg(p.wts + t * p.top_k + s);
+        }
+    }
+    float ss[8];
+#pragma unroll
+    for (int s = 0; s < 8; ++s) ss[s] = 0.0f;
+    for (int d = tid * 4; d < p.H; d += 1024) {
+        const uint2 pw = *reinterpret_cast<const uint2*>(p.post_w + d);
+        const float f[4] = {1.0f + bf16lo(pw.x), 1.0f + bf16hi(pw.x), 1.0f + bf16lo(pw.y), 1.0f + bf16hi(pw.y)};
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            if (!local[s]) continue;
+            float4 y = make_float4(0, 0, 0, 0);
+            for (int k = 0; k < p.S; ++k) {
+                const float4 a = __ldcg(reinterpret_cast<const float4*>(p.yp + (static_cast<size_t>(k) * p.P + t * p.top_k + s) * p.H + d));
+                y.x += a.x, y.y += a.y, y.z += a.z, y.w += a.w;
+            }
+            y.x *= f[0], y.y *= f[1], y.z *= f[2], y.w *= f[3];
+            ss[s] += y.x * y.x + y.y * y.y + y.z * y.z + y.w * y.w;
+        }
+    }
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+        const float v = warp_sum(ss[s]);
+        if (lane == 0) red[warp][s] = v;
+    }
+    __syncthreads();
+    if (tid < 8) {
+        float v = 0.0f;
+        for (int k = 0; k < 8; ++k) v += red[k][tid];
+        rnorm[tid] = rsqrtf(v / p.H + p.eps);
+    }
+    __syncthreads();
+    for (int d = tid * 4; d < p.H; d += 1024) {
+        const uint2 pw = *reinterpret_cast<const uint2*>(p.post_w + d);
+        const float f[4] = {1.0f + bf16lo(pw.x), 1.0f + bf16hi(pw.x), 1.0f + bf16lo(pw.y), 1.0f + bf16hi(pw.y)};
+        float4 acc = make_float4(0, 0, 0, 0);
+        if (p.resid != nullptr) acc = __ldcg(reinterpret_cast<const float4*>(p.resid + static_cast<size_t>(t) * p.ldr + d));
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            if (!local[s]) continue;
+            float4 y = make_float4(0, 0, 0, 0);
+            for (int k = 0; k < p.S; ++k) {
+                const float4 a = __ldcg(reinterpret_cast<const float4*>(p.yp + (static_cast<size_t>(k) * p.P + t * p.top_k + s) * p.H + d));
+                y.x += a.x, y.y += a.y, y.z += a.z, y.w += a.w;
+            }
+            const float c = w[s] * rnorm[s];
+            acc.x += y.x * f[0] * c, acc.y += y.y * f[1] * c, acc.z += y.z * f[2] * c, acc.w += y.w * f[3] * c;
+        }
+        if (p.out_fp32) {
+            *reinterpret_cast<float4*>(static_cast<float*>(p.out) + static_cast<size_t>(t) * p.ldo + d) = acc;
+        } else {
+            *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(t) * p.ldo + d) =
+                make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+        }
+    }
+}
+
+template <typename Kern, typename Args>
+static int launch_pdl(Kern kern, dim3 grid, dim3 block, int smem, cudaStream_t stream, int pdl, const Args& args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, args) == cudaSuccess ? 0 : MSK_ERR_CUDA;
+}
+
+}  // namespace msk
+
+extern "C" int msk_moe_packed_bytes(int E, int H, int I, size_t* w13_bytes, size_t* w2_bytes) {
+    if (E < 1 || H % 128 != 0 || I % 128 != 0 || (2 * I) % 128 != 0) return MSK_ERR_UNSUPPORTED;
+    if (w13_bytes) *w13_bytes = static_cast<size_t>(E) * (2 * I / 128) * (H / 128) * msk::kBlob;
+    if (w2_bytes) *w2_bytes = static_cast<size_t>(E) * (H / 128) * (I / 128) * msk::kBlob;
+    return 0;
+}
+
+extern "C" int msk_moe_pack(const MskMoeWeights* w, void* w13_packed, void* w2_packed, void* stream) {
+    using namespace msk;
+    if (w == nullptr || !w->w13 || !w->w13_sf || !w->w2 || !w->w2_sf || !w13_packed || !w2_packed) return MSK_ERR_INVALID;
+    if (w->H % 128 != 0 || w->I % 128 != 0) return MSK_ERR_UNSUPPORTED;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    moe_pack_kernel<<<dim3(w->H / 128, 2 * w->I / 128, w->E), 128, 0, s>>>(
+        static_cast<const uint8_t*>(w->w13), static_cast<const uint8_t*>(w->w13_sf), static_cast<uint8_t*>(w13_packed),
+        2 * w->I, w->H);
+    moe_pack_kernel<<<dim3(w->I / 128, w->H / 128, w->E), 128, 0, s>>>(
+        static_cast<const uint8_t*>(w->w2), static_cast<const uint8_t*>(w->w2_sf), static_cast<uint8_t*>(w2_packed), w->H,
+        w->I);
+    return cudaGetLastError() == cudaSuccess ? 0 : MSK_ERR_CUDA;
+}
+
+extern "C" int msk_moe_dequant(const void* packed, void* out_bf16, int E, int R, int K, void* stream) {
+    using namespace msk;
+    if (!packed || !out_bf16 || R % 128 != 0 || K % 128 != 0) return MSK_ERR_INVALID;
+    moe_dequant_kernel<<<dim3(K / 128, R / 128, E), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(packed), static_cast<__nv_bfloat16*>(out_bf16), R, K);
+    return cudaGetLastError() == cudaSuccess ? 0 : MSK_ERR_CUDA;
+}
+
+extern "C" int msk_moe_scratch_bytes(int T, int top_k, int H, int I, int s1, int s2, size_t* h1_bytes, size_t* y_bytes) {
+    if (T < 1 || top_k < 1 || s1 < 1 || s2 < 1) return MSK_ERR_INVALID;
+    if (h1_bytes) *h1_bytes = static_cast<size_t>(s1) * T * top_k * 2 * I * sizeof(float);
+    if (y_bytes) *y_bytes = static_cast<size_t>(s2) * T * top_k * H * sizeof(float);
+    return 0;
+}
+
+extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream) {
+    using namespace msk;
+    if (q == nullptr || !q->x || !q->w13_packed || !q->w2_packed || !q->w13_gs || !q->w2_gs || !q->post_norm_w ||
+        !q->h1_part || !q->y_part || !q->out || !q->topk_ids || !q->topk_weights)
+        return MSK_ERR_INVALID;
+    const int P = q->T * q->top_k;
+    if (q->T < 1 || q->top_k < 1 || q->top_k > 8 || P > kMaxPairs || q->local_count < 1 || q->local_count > kMaxExperts || q->T > kMaxPairs / 8)
+        return MSK_ERR_UNSUPPORTED;
+    if (q->H % 128 != 0 || q->I % 128 != 0 || q->H % 4 != 0 || q->ldx % 8 != 0) return MSK_ERR_UNSUPPORTED;
+    if (q->logits != nullptr && (q->n_logits > 256 || q->n_logits < q->top_k)) return MSK_ERR_UNSUPPORTED;
+    const int s1 = q->s1 > 0 ? q->s1 : 1, s2 = q->s2 > 0 ? q->s2 : 1;
+    if ((q->H / 128) % s1 != 0 || (q->I / 128) % s2 != 0) return MSK_ERR_INVALID;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) != cudaSuccess) return MSK_ERR_CUDA;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int smem = 1024 + kNRaw * kBlob + kNB * kBSlot;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(moe_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+            cudaFuncSetAttribute(moe_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return MSK_ERR_CUDA;
+        configured = true;
+    }
+    MoeGemmArgs a{};
+    a.ids = q->topk_ids, a.wts = q->topk_weights, a.logits = q->logits, a.n_logits = q->n_logits;
+    a.ids_out = const_cast<int*>(q->topk_ids), a.wts_out = const_cast<float*>(q->topk_weights);
+    a.T = q->T, a.top_k = q->top_k, a.local_start = q->local_start, a.local_count = q->local_count;
+    a.wpacked = static_cast<const uint8_t*>(q->w13_packed), a.gs = q->w13_gs, a.R = 2 * q->I, a.K = q->H;
+    a.x = static_cast<const __nv_bfloat16*>(q->x), a.ldx = q->ldx;
+    a.x_ssq = q->x_ssq, a.x_ssq_parts = q->x_ssq_parts, a.x_inv_dim = q->x_inv_dim, a.x_eps = q->x_eps;
+    a.outp = q->h1_part, a.S = s1, a.status = status;
+    int rc = launch_pdl(moe_gemm_kernel<1>, dim3(sms), dim3(kMoeThreads), smem, s, q->pdl, a);
+    if (rc != 0) return rc;
+    MoeGemmArgs b{};
+    b.ids = q->topk_ids, b.wts = q->topk_weights, b.T = q->T, b.top_k = q->top_k;
+    b.local_start = q->local_start, b.local_count = q->local_count;
+    b.wpacked = static_cast<const uint8_t*>(q->w2_packed), b.gs = q->w2_gs, b.R = q->H, b.K = q->I;
+    b.hprev = q->h1_part, b.s_prev = s1, b.inner = q->I, b.outp = q->y_part, b.S = s2, b.status = status;
+    rc = launch_pdl(moe_gemm_kernel<2>, dim3(sms), dim3(kMoeThreads), smem, s, 1, b);
+    if (rc != 0) return rc;
+    MoeCombineArgs c{};
+    c.ids = q->topk_ids, c.wts = q->topk_weights, c.top_k = q->top_k, c.local_start = q->local_start;
+    c.local_count = q->local_count, c.H = q->H, c.S = s2, c.P = P, c.yp = q->y_part;
+    c.post_w = static_cast<const __nv_bfloat16*>(q->post_norm_w), c.eps = q->post_eps, c.resid = q->resid, c.ldr = q->ldr;
+    c.out = q->out, c.out_fp32 = q->out_fp32, c.ldo = q->ldo;
+    return launch_pdl(moe_combine_kernel, dim3(q->T), dim3(256), 0, s, 1, c);
+}

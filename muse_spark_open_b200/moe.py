@@ -1,0 +1,114 @@
+"""NVFP4 routed experts: the reference's per-op entry points over the C ABI.
+
+`prepare(weights) -> state` repacks the experts once (lossless: same E2M1 codes and E4M3 scales,
+re-ordered into 9216-byte blocks for the kernel's decoder); `kernel_fn(data, state) -> bf16 [T, H]`
+with the `Weights` / `Config` / `Inputs` fields of muse_moe_w4a16/submission.py:32-57 (ids and
+weights are inputs, experts outside [local_start, local_start + local_count) are skipped).
+Layer hooks like the reference's (submission.py:888-896): `data["pre_norm"] = (ssq [parts, T], dim,
+eps)` folds the pre-expert RMSNorm row scale into the first GEMM; `data["router_logits"]` moves
+softmax / top-8 / renormalisation into the GEMM CTAs (ids and weights are then outputs).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import abi
+
+POST_NORM_EPS = 1e-8
+MAX_TOKENS = 256
+
+
+def splits_for(tokens: int, h: int, inner: int) -> tuple[int, int]:
+    """K splits of the two GEMMs: more when few experts are touched, so every SM has work."""
+    s1 = 4 if tokens <= 2 else 2 if tokens <= 8 else 1
+    s2 = 2 if tokens <= 4 and (inner // 128) % 2 == 0 else 1
+    while (h // 128) % s1:
+        s1 //= 2
+    return max(s1, 1), s2
+
+
+def prepare(weights: dict, weights_start: int = 0) -> dict:
+    w13, w2 = weights["w13"], weights["w2"]
+    if not w13.is_cuda:
+        raise abi.MskError("prepare() needs CUDA weights")
+    e, r13, hk = w13.shape
+    h, inner = hk * 2, r13 // 2
+    lib = abi.lib()
+    n13, n2 = C.c_size_t(), C.c_size_t()
+    abi.check(lib.msk_moe_packed_bytes(e, h, inner, C.byref(n13), C.byref(n2)), "msk_moe_packed_bytes")
+    p13 = torch.empty(n13.value, dtype=torch.uint8, device=w13.device)
+    p2 = torch.empty(n2.value, dtype=torch.uint8, device=w13.device)
+    mw = abi.MoeWeights()
+    mw.w13, mw.w13_sf = abi.ptr(w13.contiguous()), abi.ptr(weights["w13_sf"].contiguous())
+    mw.w2, mw.w2_sf = abi.ptr(w2.contiguous()), abi.ptr(weights["w2_sf"].contiguous())
+    mw.E, mw.H, mw.I = e, h, inner
+    abi.check(lib.msk_moe_pack(C.byref(mw), abi.ptr(p13), abi.ptr(p2), abi.stream_ptr()), "msk_moe_pack")
+    torch.cuda.synchronize()
+    post = weights.get("post_norm_w", weights.get("post_expert_norm"))
+    return {"w13": p13, "w2": p2, "w13_gs": weights["w13_gs"].float().contiguous(),
+            "w2_gs": weights["w2_gs"].float().contiguous(), "post_w": post.contiguous(),
+            "E": e, "H": h, "I": inner, "weights_start": weights_start, "scratch": {}}
+
+
+def scratch(state: dict, tokens: int, top_k: int, s1: int, s2: int, device):
+    """The two FP32 partial buffers, kept per (tokens, splits) in `state` (allocated once, outside timing)."""
+    key = (tokens, top_k, s1, s2)
+    if key not in state["scratch"]:
+        h1 = torch.empty((s1, tokens * top_k, 2 * state["I"]), dtype=torch.float32, device=device)
+        y = torch.empty((s2, tokens * top_k, state["H"]), dtype=torch.float32, device=device)
+        state["scratch"][key] = (h1, y)
+    return state["scratch"][key]
+
+
+def forward(x, ids, wts, state, local_start, local_count, out=None, logits=None, pre_norm=None, resid=None,
+            splits=None, pdl=False):
+    t, h = x.shape
+    top_k = ids.shape[1]
+    if t > MAX_TOKENS:
+        raise abi.MskError(f"experts built for decode/verify steps of up to {MAX_TOKENS} tokens, got {t}")
+    s1, s2 = splits or splits_for(t, state["H"], state["I"])
+    h1, y = scratch(state, t, top_k, s1, s2, x.device)
+    if out is None:
+        out = torch.empty((t, h), dtype=torch.bfloat16, device=x.device)
+    p = abi.MoeParams()
+    p.x, p.ldx = abi.ptr(x), x.stride(0)
+    if pre_norm is not None:
+        ssq, dim, eps = pre_norm
+        p.x_ssq, p.x_ssq_parts, p.x_inv_dim, p.x_eps = abi.ptr(ssq), ssq.shape[0], 1.0 / dim, eps
+    p.topk_ids, p.topk_weights = abi.ptr(ids), abi.ptr(wts)
+    if logits is not None:
+        p.logits, p.n_logits = abi.ptr(logits), logits.shape[1]
+    p.T, p.top_k = t, top_k
+    first = local_start - state["weights_start"]
+    if first < 0 or first + local_count > state["E"]:
+        raise abi.MskError("local expert range outside the prepared weights")
+    blob13 = (2 * state["I"] // 128) * (state["H"] // 128) * 9216
+    blob2 = (state["H"] // 128) * (state["I"] // 128) * 9216
+    p.local_start, p.local_count = local_start, local_count
+    p.w13_packed, p.w2_packed = state["w13"].data_ptr() + first * blob13, state["w2"].data_ptr() + first * blob2
+    p.w13_gs, p.w2_gs = state["w13_gs"].data_ptr() + 4 * first, state["w2_gs"].data_ptr() + 4 * first
+    p.post_norm_w, p.post_eps, p.H, p.I = abi.ptr(state["post_w"]), POST_NORM_EPS, state["H"], state["I"]
+    p.h1_part, p.y_part, p.s1, p.s2 = abi.ptr(h1), abi.ptr(y), s1, s2
+    if resid is not None:
+        p.resid, p.ldr = abi.ptr(resid), resid.stride(0)
+    p.out, p.out_fp32, p.ldo, p.pdl = abi.ptr(out), int(out.dtype == torch.float32), out.stride(0), int(pdl)
+    st = abi.status_for(x.device)
+    abi.check(abi.lib().msk_moe_forward(C.byref(p), st.p, abi.stream_ptr()), "msk_moe_forward")
+    return out
+
+
+def kernel_fn(data: dict, state: dict) -> torch.Tensor:
+    cfg = data["config"]
+    x = data["hidden_states"]
+    logits = data.get("router_logits_dev")
+    return forward(x, data["topk_ids"], data["topk_weights"], state, cfg["local_start"], cfg["local_count"],
+                   logits=logits, pre_norm=data.get("pre_norm"))
+
+
+def dequant(packed: torch.Tensor, e: int, rows: int, k: int) -> torch.Tensor:
+    """Test hook: BF16 [e, rows, k] = e2m1 * block scale, as the kernels' decoder produces it."""
+    out = torch.empty((e, rows, k), dtype=torch.bfloat16, device=packed.device)
+    abi.check(abi.lib().msk_moe_dequant(abi.ptr(packed), abi.ptr(out), e, rows, k, abi.stream_ptr()), "msk_moe_dequant")
+    return out
