@@ -154,10 +154,69 @@ typedef struct {
     int ldr;
     void* out;                  /* [T, ldo] bf16, or fp32 when out_fp32 != 0 */
     int out_fp32, ldo;
+    void* out_copy;             /* optional bf16 [T, ldc] copy of the result */
+    int ldc;
     int pdl;
 } MskMoeParams;
 
 int msk_moe_forward(const MskMoeParams* p, int* status, void* stream);
+
+/* ---------------------------------------------------------------- whole decoder layer, decode step
+ * stream fp32 [T, H] -> input RMSNorm -> fused QKV+gate projection -> gated attention over the paged
+ * FP8 cache (new K/V written in place) -> o_proj + residual -> pre-expert RMSNorm -> FP32 router
+ * (softmax top-k renormalised, chosen inside the expert GEMM CTAs) -> NVFP4 experts, post-expert norm,
+ * weighted sum -> + residual.  T = B * L tokens.  Eight kernels chained with programmatic dependent
+ * launch; both RMSNorms are folded (row scale from sums of squares the producing kernel leaves).
+ * Stands in for muse_decode_layer/submission.py `kernel_fn` (:3978-4038) on the op list the benchmark
+ * names; `prepare` (same file) corresponds to msk_moe_pack plus buffer allocation by the caller.
+ *
+ * msk_layer_front runs everything up to the router logits (what an expert-parallel rank does before
+ * the token exchange); msk_layer_decode adds the experts and the second residual on one GPU.
+ */
+typedef struct {
+    int B, L, H, Hq, Hkv, d, page_size, num_pages, max_pages, window;
+    float qk_scale_factor, sm_scale, norm_eps;
+    const float* stream;           /* fp32 [T, H] residual stream in */
+    /* attention step metadata and cache, as MskAttnParams */
+    void* k_cache;
+    void* v_cache;
+    const float* k_scale;
+    const float* v_scale;
+    const int32_t* seq_lens;
+    const int32_t* page_table;
+    const int64_t* cache_loc;
+    const float* inv_freq;
+    /* weights */
+    const void* input_norm_w;      /* bf16 [H] (scale = 1 + w) */
+    const void* w_qkv;             /* bf16 [(2Hq+2Hkv)*d, H] */
+    const void* w_o;               /* bf16 [H, Hq*d] */
+    const void* pre_expert_norm_w; /* bf16 [H] */
+    const float* router_w;         /* fp32 [E, H] */
+    const float* router_bias;      /* fp32 [E] or NULL */
+    int E;
+    /* scratch owned by the caller (allocated once) */
+    void* xn0;                     /* bf16 [T, H] */
+    float* ssq0;                   /* fp32 [T] */
+    void* qkv;                     /* bf16 [T, (2Hq+2Hkv)*d] */
+    void* attn;                    /* bf16 [T, Hq*d] */
+    float* stream1;                /* fp32 [T, H] stream after attention */
+    void* xn1;                     /* bf16 [T, H] expert input before its row scale */
+    float* ssq1;                   /* fp32 [H/128, T] */
+    float* router_part;            /* fp32 [H/64, T, E] */
+    int32_t* router_ticket;        /* int32 [ceil(T/32)], zero before the first call */
+    float* logits;                 /* fp32 [T, E] */
+    int attn_chunks, attn_stages, qkv_splits, o_splits;
+    int pdl;                       /* also chain the first kernel to whatever precedes it */
+} MskLayerFront;
+
+int msk_layer_front(const MskLayerFront* p, int* status, void* stream);
+
+typedef struct {
+    MskLayerFront front;
+    MskMoeParams moe;              /* x, x_ssq, logits, resid, T, H are filled from `front` */
+} MskLayerParams;
+
+int msk_layer_decode(const MskLayerParams* p, int* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -59,12 +59,14 @@ def lib() -> C.CDLL:
         _lib.msk_moe_dequant.argtypes = [vp, vp, ci, ci, ci, vp]
         _lib.msk_moe_scratch_bytes.argtypes = [ci, ci, ci, ci, ci, ci, vp, vp]
         _lib.msk_moe_forward.argtypes = [vp, vp, vp]
+        _lib.msk_layer_front.argtypes = [vp, vp, vp]
+        _lib.msk_layer_decode.argtypes = [vp, vp, vp]
     return _lib
 
 
 # every symbol include/msk.h declares
 EXPORTS = ["msk_version", "msk_device_info", "msk_selftest_umma", "msk_proj_skinny", "msk_attn_decode",
-           "msk_moe_packed_bytes", "msk_moe_pack", "msk_moe_dequant", "msk_moe_scratch_bytes", "msk_moe_forward"]
+           "msk_moe_packed_bytes", "msk_moe_pack", "msk_moe_dequant", "msk_moe_scratch_bytes", "msk_moe_forward", "msk_layer_front", "msk_layer_decode"]
 
 
 def ptr(t: torch.Tensor | None) -> int | None:
@@ -142,5 +144,27 @@ class MoeParams(C.Structure):
         ("post_norm_w", C.c_void_p), ("post_eps", C.c_float), ("H", C.c_int), ("I", C.c_int),
         ("h1_part", C.c_void_p), ("y_part", C.c_void_p), ("s1", C.c_int), ("s2", C.c_int),
         ("resid", C.c_void_p), ("ldr", C.c_int), ("out", C.c_void_p), ("out_fp32", C.c_int), ("ldo", C.c_int),
+        ("out_copy", C.c_void_p), ("ldc", C.c_int), ("pdl", C.c_int),
+    ]
+
+
+class LayerFront(C.Structure):
+    _fields_ = [
+        ("B", C.c_int), ("L", C.c_int), ("H", C.c_int), ("Hq", C.c_int), ("Hkv", C.c_int), ("d", C.c_int),
+        ("page_size", C.c_int), ("num_pages", C.c_int), ("max_pages", C.c_int), ("window", C.c_int),
+        ("qk_scale_factor", C.c_float), ("sm_scale", C.c_float), ("norm_eps", C.c_float),
+        ("stream", C.c_void_p),
+        ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("k_scale", C.c_void_p), ("v_scale", C.c_void_p),
+        ("seq_lens", C.c_void_p), ("page_table", C.c_void_p), ("cache_loc", C.c_void_p), ("inv_freq", C.c_void_p),
+        ("input_norm_w", C.c_void_p), ("w_qkv", C.c_void_p), ("w_o", C.c_void_p), ("pre_expert_norm_w", C.c_void_p),
+        ("router_w", C.c_void_p), ("router_bias", C.c_void_p), ("E", C.c_int),
+        ("xn0", C.c_void_p), ("ssq0", C.c_void_p), ("qkv", C.c_void_p), ("attn", C.c_void_p), ("stream1", C.c_void_p),
+        ("xn1", C.c_void_p), ("ssq1", C.c_void_p), ("router_part", C.c_void_p), ("router_ticket", C.c_void_p),
+        ("logits", C.c_void_p),
+        ("attn_chunks", C.c_int), ("attn_stages", C.c_int), ("qkv_splits", C.c_int), ("o_splits", C.c_int),
         ("pdl", C.c_int),
     ]
+
+
+class LayerParams(C.Structure):
+    _fields_ = [("front", LayerFront), ("moe", MoeParams)]

@@ -1,0 +1,216 @@
+// The small kernels between the big ones of the decoder layer, and the layer's launch chain.
+//   prep_norm    x = bf16(rmsnorm(stream) * (1 + w)), one block per token (the rounding point of the
+//                reference); also leaves ssq[t] = sum stream^2.
+//   router       FP32 logits[t, e] = rs[t] * sum_k (stream1[t,k] * (1 + w[k])) * R[e, k] + bias[e] on
+//                CUDA cores (expert ids must not depend on tensor-core rounding).  Split over K; the last
+//                block to finish (ticket) adds the partials in a fixed order, so ids are reproducible.
+#include "msk.h"
+#include "ptx.cuh"
+
+namespace msk {
+
+__global__ void __launch_bounds__(256) prep_norm_kernel(const float* __restrict__ stream, const __nv_bfloat16* __restrict__ w,
+                                                        __nv_bfloat16* __restrict__ xn, float* __restrict__ ssq, int H,
+                                                        float eps) {
+    __shared__ float red[8];
+    __shared__ float rs_s;
+    const int t = blockIdx.x, tid = threadIdx.x;
+    pdl_wait();
+    pdl_launch_dependents();
+    constexpr int kMaxVec = 8;  // H <= 8192
+    float4 v[kMaxVec];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+        const int d = tid * 4 + i * 1024;
+        v[i] = make_float4(0, 0, 0, 0);
+        if (d < H) v[i] = __ldcg(reinterpret_cast<const float4*>(stream + static_cast<size_t>(t) * H + d));
+        ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    }
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    if (tid == 0) {
+        const float tot = ((red[0] + red[1]) + (red[2] + red[3])) + ((red[4] + red[5]) + (red[6] + red[7]));
+        ssq[t] = tot;
+        rs_s = 1.0f / sqrtf(tot / H + eps);
+    }
+    __syncthreads();
+    const float rs = rs_s;
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+        const int d = tid * 4 + i * 1024;
+        if (d < H) {
+            const uint2 pw = *reinterpret_cast<const uint2*>(w + d);
+            *reinterpret_cast<uint2*>(xn + static_cast<size_t>(t) * H + d) =
+                make_uint2(pack_bf16(v[i].x * rs * (1.0f + bf16lo(pw.x)), v[i].y * rs * (1.0f + bf16hi(pw.x))),
+                           pack_bf16(v[i].z * rs * (1.0f + bf16lo(pw.y)), v[i].w * rs * (1.0f + bf16hi(pw.y))));
+        }
+    }
+}
+
+struct RouterArgs {
+    const float* s1;        // [T, H]
+    const __nv_bfloat16* w; // [H]
+    const float* ssq;       // [parts, T]
+    int ssq_parts;
+    float eps;
+    const float* R;         // [E, H]
+    const float* bias;      // [E] or null
+    float* part;            // [KS, T, E]
+    int* ticket;            // [token groups]
+    float* logits;          // [T, E]
+    int T, H, E;
+};
+
+constexpr int kRouterK = 64;   // k per block
+constexpr int kRouterT = 32;   // tokens per block
+
+__global__ void __launch_bounds__(256) router_kernel(RouterArgs p) {
+    extern __shared__ float rsm[];
+    __shared__ int last;
+    float* Rs = rsm;                               // [E][kRouterK + 1]
+    float* hs = rsm + p.E * (kRouterK + 1);        // [kRouterT][kRouterK]
+    const int ks = blockIdx.x, tg = blockIdx.y, tid = threadIdx.x;
+    const int k0 = ks * kRouterK, t0 = tg * kRouterT;
+    const int nt = min(kRouterT, p.T - t0);
+    const int KS = gridDim.x;
+    for (int i = tid; i < p.E * kRouterK; i += 256) {  // router weights do not depend on the previous kernel
+        const int e = i / kRouterK, k = i % kRouterK;
+        Rs[e * (kRouterK + 1) + k] = p.R[static_cast<size_t>(e) * p.H + k0 + k];
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int i = tid; i < kRouterT * kRouterK; i += 256) {
+        const int t = i / kRouterK, k = i % kRouterK;
+        hs[i] = t < nt ? __ldcg(p.s1 + static_cast<size_t>(t0 + t) * p.H + k0 + k) * (1.0f + __bfloat162float(p.w[k0 + k])) : 0.0f;
+    }
+    __syncthreads();
+    for (int o = tid; o < nt * p.E; o += 256) {
+        const int t = o / p.E, e = o % p.E;
+        const float* r = Rs + e * (kRouterK + 1);
+        const float* h = hs + t * kRouterK;
+        float acc = 0.0f;
+#pragma unroll 8
+        for (int k = 0; k < kRouterK; ++k) acc = fmaf(h[k], r[k], acc);
+        p.part[(static_cast<size_t>(ks) * p.T + t0 + t) * p.E + e] = acc;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) last = atomicAdd(p.ticket + tg, 1) == KS - 1;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    for (int o = tid; o < nt * p.E; o += 256) {
+        const int t = o / p.E, e = o % p.E;
+        float acc = 0.0f;
+        for (int s = 0; s < KS; ++s) acc += __ldcg(p.part + (static_cast<size_t>(s) * p.T + t0 + t) * p.E + e);
+        float ss = 0.0f;
+        for (int q = 0; q < p.ssq_parts; ++q) ss += __ldcg(p.ssq + q * p.T + t0 + t);
+        acc *= rsqrtf(ss / p.H + p.eps);
+        if (p.bias != nullptr) acc += p.bias[e];
+        p.logits[static_cast<size_t>(t0 + t) * p.E + e] = acc;
+    }
+    if (tid == 0) p.ticket[tg] = 0;  // ready for the next call
+}
+
+template <typename Kern, typename Args>
+static int launch1(Kern kern, dim3 grid, dim3 block, int smem, cudaStream_t stream, int pdl, const Args& a) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, a) == cudaSuccess ? 0 : MSK_ERR_CUDA;
+}
+
+static int launch_prep(const float* stream, const void* w, void* xn, float* ssq, int T, int H, float eps, cudaStream_t s,
+                       int pdl) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(T);
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, prep_norm_kernel, stream, static_cast<const __nv_bfloat16*>(w),
+                              static_cast<__nv_bfloat16*>(xn), ssq, H, eps) == cudaSuccess
+               ? 0
+               : MSK_ERR_CUDA;
+}
+
+}  // namespace msk
+
+extern "C" int msk_layer_front(const MskLayerFront* f, int* status, void* stream) {
+    using namespace msk;
+    if (f == nullptr || !f->stream || !f->input_norm_w || !f->w_qkv || !f->w_o || !f->pre_expert_norm_w || !f->router_w ||
+        !f->xn0 || !f->ssq0 || !f->qkv || !f->attn || !f->stream1 || !f->xn1 || !f->ssq1 || !f->router_part ||
+        !f->router_ticket || !f->logits)
+        return MSK_ERR_INVALID;
+    const int T = f->B * f->L, H = f->H, nqkv = (2 * f->Hq + 2 * f->Hkv) * f->d, no = f->Hq * f->d;
+    if (T < 1 || T > 256 || H % 1024 != 0 || H > 8192 || f->E < 1 || f->E > 256) return MSK_ERR_UNSUPPORTED;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int rc = launch_prep(f->stream, f->input_norm_w, f->xn0, f->ssq0, T, H, f->norm_eps, s, f->pdl);
+    if (rc != 0) return rc;
+
+    MskProjParams q = {};
+    q.x = f->xn0, q.w = f->w_qkv, q.M = T, q.N = nqkv, q.K = H, q.splits = f->qkv_splits;
+    q.out = f->qkv, q.out_fp32 = 0, q.ldo = nqkv;
+    q.pdl = 1;
+    rc = msk_proj_skinny(&q, status, stream);
+    if (rc != 0) return rc;
+
+    MskAttnParams a = {};
+    a.qkv = f->qkv, a.ld_qkv = nqkv, a.out = f->attn, a.ld_out = no;
+    a.k_cache = f->k_cache, a.v_cache = f->v_cache, a.k_scale = f->k_scale, a.v_scale = f->v_scale;
+    a.seq_lens = f->seq_lens, a.page_table = f->page_table, a.max_pages = f->max_pages, a.cache_loc = f->cache_loc;
+    a.inv_freq = f->inv_freq, a.B = f->B, a.L = f->L, a.Hq = f->Hq, a.Hkv = f->Hkv, a.d = f->d;
+    a.page_size = f->page_size, a.num_pages = f->num_pages, a.window = f->window;
+    a.qk_scale_factor = f->qk_scale_factor, a.sm_scale = f->sm_scale;
+    a.chunks = f->attn_chunks, a.stages = f->attn_stages, a.pdl = 1;
+    rc = msk_attn_decode(&a, status, stream);
+    if (rc != 0) return rc;
+
+    MskProjParams o = {};
+    o.x = f->attn, o.w = f->w_o, o.M = T, o.N = H, o.K = no, o.splits = f->o_splits;
+    o.out = f->stream1, o.out_fp32 = 1, o.ldo = H;
+    o.resid = f->stream, o.ldr = H;
+    o.next_norm_w = f->pre_expert_norm_w, o.out_normed = f->xn1, o.ldn = H, o.out_ssq = f->ssq1, o.pdl = 1;
+    rc = msk_proj_skinny(&o, status, stream);
+    if (rc != 0) return rc;
+
+    RouterArgs r = {};
+    r.s1 = f->stream1, r.w = static_cast<const __nv_bfloat16*>(f->pre_expert_norm_w), r.ssq = f->ssq1;
+    r.ssq_parts = (H + 127) / 128, r.eps = f->norm_eps, r.R = f->router_w, r.bias = f->router_bias;
+    r.part = f->router_part, r.ticket = f->router_ticket, r.logits = f->logits, r.T = T, r.H = H, r.E = f->E;
+    const int rsmem = (f->E * (kRouterK + 1) + kRouterT * kRouterK) * 4;
+    static int configured = 0;
+    if (rsmem > configured) {
+        if (cudaFuncSetAttribute(router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, rsmem) != cudaSuccess)
+            return MSK_ERR_CUDA;
+        configured = rsmem;
+    }
+    return launch1(router_kernel, dim3(H / kRouterK, (T + kRouterT - 1) / kRouterT), dim3(256), rsmem, s, 1, r);
+}
+
+extern "C" int msk_layer_decode(const MskLayerParams* p, int* status, void* stream) {
+    if (p == nullptr) return MSK_ERR_INVALID;
+    int rc = msk_layer_front(&p->front, status, stream);
+    if (rc != 0) return rc;
+    MskMoeParams m = p->moe;
+    const MskLayerFront& f = p->front;
+    m.x = f.xn1, m.ldx = f.H;
+    m.x_ssq = f.ssq1, m.x_ssq_parts = (f.H + 127) / 128, m.x_inv_dim = 1.0f / f.H, m.x_eps = f.norm_eps;
+    m.logits = f.logits, m.n_logits = f.E;
+    m.T = f.B * f.L, m.H = f.H;
+    m.resid = f.stream1, m.ldr = f.H;
+    m.pdl = 1;
+    return msk_moe_forward(&m, status, stream);
+}

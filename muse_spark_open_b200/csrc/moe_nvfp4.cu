@@ -497,6 +497,8 @@ struct MoeCombineArgs {
     int ldr;
     void* out;
     int out_fp32, ldo;
+    __nv_bfloat16* out_copy;  // optional BF16 copy of the result
+    int ldc;
 };
 
 __global__ void __launch_bounds__(256) moe_combine_kernel(MoeCombineArgs p) {
@@ -568,6 +570,9 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(MoeCombineArgs p) {
             *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(t) * p.ldo + d) =
                 make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
         }
+        if (p.out_copy != nullptr)
+            *reinterpret_cast<uint2*>(p.out_copy + static_cast<size_t>(t) * p.ldc + d) =
+                make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
     }
 }
 
@@ -670,5 +675,6 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
     c.local_count = q->local_count, c.H = q->H, c.S = s2, c.P = P, c.yp = q->y_part;
     c.post_w = static_cast<const __nv_bfloat16*>(q->post_norm_w), c.eps = q->post_eps, c.resid = q->resid, c.ldr = q->ldr;
     c.out = q->out, c.out_fp32 = q->out_fp32, c.ldo = q->ldo;
+    c.out_copy = static_cast<__nv_bfloat16*>(q->out_copy), c.ldc = q->ldc;
     return launch_pdl(moe_combine_kernel, dim3(q->T), dim3(256), 0, s, 1, c);
 }

@@ -1,0 +1,118 @@
+"""The whole decoder layer's decode step: `prepare(weights) -> state`, `kernel_fn(data, state)`.
+
+Same call shape as muse_decode_layer/submission.py:3978-4038: `data` carries the FP32 residual
+`stream` [T, H], the attention step's cache and metadata (muse_attention_decode `Inputs` fields) and
+`config`; the result is `(hidden bf16 [T, H], stream fp32 [T, H], topk_ids int32 [T, 8])`, and the
+new K/V rows are written into `data["k_cache"]` / `data["v_cache"]` in place.  The op list is the
+benchmark's: input RMSNorm, QKV+gate projection, gated attention, o_proj, residual, pre-expert
+RMSNorm, FP32 router (softmax top-8 renormalised), NVFP4 experts, residual.
+All scratch lives in `state`, sized per token count on first use (outside timing), so the timed
+call allocates only its three outputs.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import abi, attention, moe
+
+RMS_EPS = 1e-5
+TOP_K = 8
+
+
+def prepare(weights: dict, local_start: int = 0, local_count: int | None = None) -> dict:
+    """weights: input_norm, qkv_gate, o, pre_expert_norm, router (fp32), router_bias (optional),
+    w13, w13_sf, w13_gs, w2, w2_sf, w2_gs, post_expert_norm (the experts given may be only this
+    rank's: then pass local_start / local_count)."""
+    if not weights["qkv_gate"].is_cuda:
+        raise abi.MskError("prepare() needs CUDA weights")
+    n_exp = weights["router"].shape[0]
+    st = {
+        "input_norm": weights["input_norm"].contiguous(), "qkv_gate": weights["qkv_gate"].contiguous(),
+        "o": weights["o"].contiguous(), "pre_expert_norm": weights["pre_expert_norm"].contiguous(),
+        "router": weights["router"].float().contiguous(),
+        "router_bias": weights["router_bias"].float().contiguous() if weights.get("router_bias") is not None else None,
+        "E": n_exp, "local_start": local_start,
+        "local_count": weights["w13"].shape[0] if local_count is None else local_count,
+        "moe": moe.prepare(weights, weights_start=local_start), "bufs": {},
+    }
+    return st
+
+
+def buffers(state: dict, t: int, device) -> dict:
+    if t not in state["bufs"]:
+        h = state["qkv_gate"].shape[1]
+        nqkv, no = state["qkv_gate"].shape[0], state["o"].shape[1]
+        e = state["E"]
+        f32, bf = torch.float32, torch.bfloat16
+        mk = lambda shape, dt: torch.empty(shape, dtype=dt, device=device)
+        state["bufs"][t] = {
+            "xn0": mk((t, h), bf), "ssq0": mk((t,), f32), "qkv": mk((t, nqkv), bf), "attn": mk((t, no), bf),
+            "stream1": mk((t, h), f32), "xn1": mk((t, h), bf), "ssq1": mk((h // 128, t), f32),
+            "router_part": mk((h // 64, t, e), f32),
+            "router_ticket": torch.zeros(((t + 31) // 32,), dtype=torch.int32, device=device),
+            "logits": mk((t, e), f32), "topk_w": mk((t, TOP_K), f32),
+        }
+    return state["bufs"][t]
+
+
+def fill_front(f: abi.LayerFront, data: dict, state: dict, buf: dict, tune: dict) -> None:
+    cfg = data["config"]
+    f.B, f.L, f.H = cfg["batch"], cfg["q_len"], state["qkv_gate"].shape[1]
+    f.Hq, f.Hkv, f.d = cfg["num_q_heads"], cfg["num_kv_heads"], cfg["head_dim"]
+    f.page_size, f.num_pages, f.max_pages = cfg["page_size"], data["k_cache"].shape[0], data["page_table"].shape[1]
+    f.window, f.qk_scale_factor, f.sm_scale, f.norm_eps = cfg["window"], cfg["qk_scale_factor"], cfg["sm_scale"], RMS_EPS
+    f.stream = abi.ptr(data["stream"])
+    f.k_cache, f.v_cache = abi.ptr(data["k_cache"]), abi.ptr(data["v_cache"])
+    f.k_scale, f.v_scale = abi.ptr(data["k_scale"]), abi.ptr(data["v_scale"])
+    f.seq_lens, f.page_table, f.cache_loc = abi.ptr(data["seq_lens"]), abi.ptr(data["page_table"]), abi.ptr(data["cache_loc"])
+    fr = attention.inv_freq(cfg["rope_theta"], cfg["head_dim"], data["stream"].device)
+    f.inv_freq = abi.ptr(fr) if fr is not None else None
+    f.input_norm_w, f.w_qkv, f.w_o = abi.ptr(state["input_norm"]), abi.ptr(state["qkv_gate"]), abi.ptr(state["o"])
+    f.pre_expert_norm_w, f.router_w = abi.ptr(state["pre_expert_norm"]), abi.ptr(state["router"])
+    f.router_bias = abi.ptr(state["router_bias"]) if state["router_bias"] is not None else None
+    f.E = state["E"]
+    for name in ("xn0", "ssq0", "qkv", "attn", "stream1", "xn1", "ssq1", "router_part", "router_ticket", "logits"):
+        setattr(f, name, abi.ptr(buf[name]))
+    f.attn_chunks, f.attn_stages = tune.get("attn_chunks", 0), tune.get("attn_stages", 0)
+    f.qkv_splits, f.o_splits, f.pdl = tune.get("qkv_splits", 0), tune.get("o_splits", 0), 0
+
+
+def front(data: dict, state: dict, **tune) -> dict:
+    """Everything up to the router logits (the part an expert-parallel rank runs before the exchange)."""
+    t = data["config"]["batch"] * data["config"]["q_len"]
+    buf = buffers(state, t, data["stream"].device)
+    f = abi.LayerFront()
+    fill_front(f, data, state, buf, tune)
+    st = abi.status_for(data["stream"].device)
+    abi.check(abi.lib().msk_layer_front(C.byref(f), st.p, abi.stream_ptr()), "msk_layer_front")
+    return buf
+
+
+def kernel_fn(data: dict, state: dict, **tune):
+    stream = data["stream"]
+    if stream.dtype != torch.float32 or not stream.is_cuda:
+        raise abi.MskError("stream must be a float32 CUDA tensor")
+    t, h = stream.shape
+    buf = buffers(state, t, stream.device)
+    ms = state["moe"]
+    s1, s2 = tune.get("moe_splits") or moe.splits_for(t, ms["H"], ms["I"])
+    h1, y = moe.scratch(ms, t, TOP_K, s1, s2, stream.device)
+    hidden = torch.empty((t, h), dtype=torch.bfloat16, device=stream.device)
+    out = torch.empty((t, h), dtype=torch.float32, device=stream.device)
+    ids = torch.empty((t, TOP_K), dtype=torch.int32, device=stream.device)
+    p = abi.LayerParams()
+    fill_front(p.front, data, state, buf, tune)
+    m = p.moe
+    m.topk_ids, m.topk_weights, m.top_k = abi.ptr(ids), abi.ptr(buf["topk_w"]), TOP_K
+    m.local_start, m.local_count = state["local_start"], state["local_count"]
+    m.w13_packed, m.w2_packed = abi.ptr(ms["w13"]), abi.ptr(ms["w2"])
+    m.w13_gs, m.w2_gs = abi.ptr(ms["w13_gs"]), abi.ptr(ms["w2_gs"])
+    m.post_norm_w, m.post_eps, m.I = abi.ptr(ms["post_w"]), moe.POST_NORM_EPS, ms["I"]
+    m.h1_part, m.y_part, m.s1, m.s2 = abi.ptr(h1), abi.ptr(y), s1, s2
+    m.out, m.out_fp32, m.ldo = abi.ptr(out), 1, h
+    m.out_copy, m.ldc = abi.ptr(hidden), h
+    st = abi.status_for(stream.device)
+    abi.check(abi.lib().msk_layer_decode(C.byref(p), st.p, abi.stream_ptr()), "msk_layer_decode")
+    return hidden, out, ids
