@@ -138,6 +138,8 @@ typedef struct {
     float* topk_weights;        /* [T, top_k] */
     const float* logits;        /* optional [T, n_logits]: softmax -> top-k -> renormalise inside the GEMM CTAs */
     int n_logits;
+    int ld_logits;              /* floats between token rows of logits; 0 = n_logits */
+    int x_ssq_tstride;          /* floats between tokens inside one part of x_ssq; 0 = 1 (parts are T*stride apart) */
     int T, top_k;               /* T <= 256, top_k <= 8 */
     int local_start, local_count; /* this GPU holds experts [local_start, local_start + local_count) */
     const void* w13_packed;
@@ -217,6 +219,19 @@ typedef struct {
 } MskLayerParams;
 
 int msk_layer_decode(const MskLayerParams* p, int* status, void* stream);
+
+/* ---------------------------------------------------------------- expert-parallel exchange helpers
+ * The reference runs one GPU and states its collectives as identities (muse_decode_layer/reference.py:8-10,
+ * :467 "the all-reduce: identity"); these kernels sit on either side of the real exchange that replaces
+ * that identity: rows packed by msk_ep_pack are gathered to every rank (dispatch), each rank runs
+ * msk_moe_forward over all tokens with its own experts, the FP32 partials go back to the tokens' home
+ * ranks (combine) and msk_ep_reduce adds them to the residual in rank order.
+ */
+int msk_ep_row_bytes(int H, int E);   /* 2H (x bf16) + 4E (logits fp32) + 16 (sum of squares, padding) */
+int msk_ep_pack(const void* xn, const float* logits, const float* ssq, int ssq_parts, void* rows, int T, int H, int E,
+                void* stream);
+int msk_ep_reduce(const float* stream1, const float* recv /* [ranks, T, H] */, int ranks, float* out, void* out_bf16,
+                  int T, int H, void* stream);
 
 #ifdef __cplusplus
 }

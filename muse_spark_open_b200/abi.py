@@ -61,12 +61,16 @@ def lib() -> C.CDLL:
         _lib.msk_moe_forward.argtypes = [vp, vp, vp]
         _lib.msk_layer_front.argtypes = [vp, vp, vp]
         _lib.msk_layer_decode.argtypes = [vp, vp, vp]
+        _lib.msk_ep_row_bytes.argtypes = [ci, ci]
+        _lib.msk_ep_pack.argtypes = [vp, vp, vp, ci, vp, ci, ci, ci, vp]
+        _lib.msk_ep_reduce.argtypes = [vp, vp, ci, vp, vp, ci, ci, vp]
     return _lib
 
 
 # every symbol include/msk.h declares
 EXPORTS = ["msk_version", "msk_device_info", "msk_selftest_umma", "msk_proj_skinny", "msk_attn_decode",
-           "msk_moe_packed_bytes", "msk_moe_pack", "msk_moe_dequant", "msk_moe_scratch_bytes", "msk_moe_forward", "msk_layer_front", "msk_layer_decode"]
+           "msk_moe_packed_bytes", "msk_moe_pack", "msk_moe_dequant", "msk_moe_scratch_bytes", "msk_moe_forward", "msk_layer_front", "msk_layer_decode",
+           "msk_ep_row_bytes", "msk_ep_pack", "msk_ep_reduce"]
 
 
 def ptr(t: torch.Tensor | None) -> int | None:
@@ -139,6 +143,7 @@ class MoeParams(C.Structure):
         ("x", C.c_void_p), ("ldx", C.c_int),
         ("x_ssq", C.c_void_p), ("x_ssq_parts", C.c_int), ("x_inv_dim", C.c_float), ("x_eps", C.c_float),
         ("topk_ids", C.c_void_p), ("topk_weights", C.c_void_p), ("logits", C.c_void_p), ("n_logits", C.c_int),
+        ("ld_logits", C.c_int), ("x_ssq_tstride", C.c_int),
         ("T", C.c_int), ("top_k", C.c_int), ("local_start", C.c_int), ("local_count", C.c_int),
         ("w13_packed", C.c_void_p), ("w2_packed", C.c_void_p), ("w13_gs", C.c_void_p), ("w2_gs", C.c_void_p),
         ("post_norm_w", C.c_void_p), ("post_eps", C.c_float), ("H", C.c_int), ("I", C.c_int),

@@ -127,7 +127,7 @@ struct MoeGemmArgs {
     const int* ids;          // [T, top_k]
     const float* wts;        // [T, top_k]
     const float* logits;     // [T, n_logits] or null
-    int n_logits;
+    int n_logits, ld_logits;
     int* ids_out;            // written by CTA 0 when routing from logits
     float* wts_out;
     int T, top_k, local_start, local_count;
@@ -137,7 +137,7 @@ struct MoeGemmArgs {
     const __nv_bfloat16* x;  // gemm 1 B source
     int ldx;
     const float* x_ssq;
-    int x_ssq_parts;
+    int x_ssq_parts, x_ssq_ts;
     float x_inv_dim, x_eps;
     const float* hprev;      // gemm 2 B source: gemm-1 partials [s_prev][T*top_k][2I]
     int s_prev, inner;
@@ -230,7 +230,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(MoeGemmArgs p)
     // ---------------- routing: ids -> per-expert pair lists -> expert-groups
     if (MODE == 1 && p.logits != nullptr) {
         for (int t = warp; t < p.T; t += kMoeThreads / 32) {
-            route_token(p.logits + static_cast<size_t>(t) * p.n_logits, p.n_logits, p.top_k, lane, r_ids[warp], r_w[warp]);
+            route_token(p.logits + static_cast<size_t>(t) * p.ld_logits, p.n_logits, p.top_k, lane, r_ids[warp], r_w[warp]);
             __syncwarp();
             if (lane < p.top_k) {
                 sh.ids_s[t * p.top_k + lane] = static_cast<unsigned short>(r_ids[warp][lane]);
@@ -287,7 +287,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(MoeGemmArgs p)
     if (MODE == 1 && p.x_ssq != nullptr) {
         for (int t = tid; t < p.T; t += kMoeThreads) {
             float s = 0.0f;
-            for (int part = 0; part < p.x_ssq_parts; ++part) s += __ldcg(p.x_ssq + part * p.T + t);
+            for (int part = 0; part < p.x_ssq_parts; ++part) s += __ldcg(p.x_ssq + (static_cast<size_t>(part) * p.T + t) * p.x_ssq_ts);
             sh.rs[t] = rsqrtf(s * p.x_inv_dim + p.x_eps);
         }
     }
@@ -660,6 +660,8 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
     a.wpacked = static_cast<const uint8_t*>(q->w13_packed), a.gs = q->w13_gs, a.R = 2 * q->I, a.K = q->H;
     a.x = static_cast<const __nv_bfloat16*>(q->x), a.ldx = q->ldx;
     a.x_ssq = q->x_ssq, a.x_ssq_parts = q->x_ssq_parts, a.x_inv_dim = q->x_inv_dim, a.x_eps = q->x_eps;
+    a.x_ssq_ts = q->x_ssq_tstride > 0 ? q->x_ssq_tstride : 1;
+    a.ld_logits = q->ld_logits > 0 ? q->ld_logits : q->n_logits;
     a.outp = q->h1_part, a.S = s1, a.status = status;
     int rc = launch_pdl(moe_gemm_kernel<1>, dim3(sms), dim3(kMoeThreads), smem, s, q->pdl, a);
     if (rc != 0) return rc;

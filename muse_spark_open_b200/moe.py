@@ -75,11 +75,12 @@ def forward(x, ids, wts, state, local_start, local_count, out=None, logits=None,
     p = abi.MoeParams()
     p.x, p.ldx = abi.ptr(x), x.stride(0)
     if pre_norm is not None:
-        ssq, dim, eps = pre_norm
-        p.x_ssq, p.x_ssq_parts, p.x_inv_dim, p.x_eps = abi.ptr(ssq), ssq.shape[0], 1.0 / dim, eps
+        ssq, dim, eps = pre_norm  # [parts, T] contiguous, or one value per token with any stride
+        p.x_ssq, p.x_inv_dim, p.x_eps = abi.ptr(ssq), 1.0 / dim, eps
+        p.x_ssq_parts, p.x_ssq_tstride = (ssq.shape[0], 1) if ssq.dim() == 2 else (1, ssq.stride(0))
     p.topk_ids, p.topk_weights = abi.ptr(ids), abi.ptr(wts)
     if logits is not None:
-        p.logits, p.n_logits = abi.ptr(logits), logits.shape[1]
+        p.logits, p.n_logits, p.ld_logits = abi.ptr(logits), logits.shape[1], logits.stride(0)
     p.T, p.top_k = t, top_k
     first = local_start - state["weights_start"]
     if first < 0 or first + local_count > state["E"]:
