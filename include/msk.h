@@ -163,6 +163,19 @@ typedef struct {
 
 int msk_moe_forward(const MskMoeParams* p, int* status, void* stream);
 
+/* msk_moe_forward for callers that can neither pass scratch nor let the library allocate (a server whose
+ * memory pool owns the whole device, a step inside a loop where an allocation would stall the GPU).
+ * No counterpart in the reference, whose kernel_fn allocates freely (muse_moe_w4a16/submission.py:882-886).
+ * `h1_part` and `y_part` of `p` are ignored: both partial buffers live in a 4 MiB array inside the
+ * library that each GPU holds from load to exit.  Accepted while
+ *     s1 * T * top_k * 2 * I + s2 * T * top_k * H  <=  1 048 576 floats
+ * (8 tokens at the benchmark's expert shapes with s1 = 4, s2 = 2); larger calls return -3 and run nothing.
+ * It calls no cudaMalloc / cudaFree and nothing that allocates.  The first call on a device looks up the
+ * array's device address (cudaGetSymbolAddress): make that call before any stream capture.  All calls
+ * on a device share the array; nothing in it has to be zero on entry and it keeps the last call's
+ * partials, so two calls whose kernels overlap on the GPU (different streams) race: run them in order. */
+int msk_moe_forward_static(const MskMoeParams* p, int* status, void* stream);
+
 /* ---------------------------------------------------------------- whole decoder layer, decode step
  * stream fp32 [T, H] -> input RMSNorm -> fused QKV+gate projection -> gated attention over the paged
  * FP8 cache (new K/V written in place) -> o_proj + residual -> pre-expert RMSNorm -> FP32 router

@@ -59,6 +59,7 @@ def lib() -> C.CDLL:
         _lib.msk_moe_dequant.argtypes = [vp, vp, ci, ci, ci, vp]
         _lib.msk_moe_scratch_bytes.argtypes = [ci, ci, ci, ci, ci, ci, vp, vp]
         _lib.msk_moe_forward.argtypes = [vp, vp, vp]
+        _lib.msk_moe_forward_static.argtypes = [vp, vp, vp]
         _lib.msk_layer_front.argtypes = [vp, vp, vp]
         _lib.msk_layer_decode.argtypes = [vp, vp, vp]
         _lib.msk_ep_row_bytes.argtypes = [ci, ci]
@@ -69,7 +70,7 @@ def lib() -> C.CDLL:
 
 # every symbol include/msk.h declares
 EXPORTS = ["msk_version", "msk_device_info", "msk_selftest_umma", "msk_proj_skinny", "msk_attn_decode",
-           "msk_moe_packed_bytes", "msk_moe_pack", "msk_moe_dequant", "msk_moe_scratch_bytes", "msk_moe_forward", "msk_layer_front", "msk_layer_decode",
+           "msk_moe_packed_bytes", "msk_moe_pack", "msk_moe_dequant", "msk_moe_scratch_bytes", "msk_moe_forward", "msk_moe_forward_static", "msk_layer_front", "msk_layer_decode",
            "msk_ep_row_bytes", "msk_ep_pack", "msk_ep_reduce"]
 
 

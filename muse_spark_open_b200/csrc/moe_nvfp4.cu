@@ -680,3 +680,42 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
     c.out_copy = static_cast<__nv_bfloat16*>(q->out_copy), c.ldc = q->ldc;
     return launch_pdl(moe_combine_kernel, dim3(q->T), dim3(256), 0, s, 1, c);
 }
+
+// ---------------------------------------------------------------- routed experts without caller scratch
+// Some hosts cannot hand this library scratch memory and cannot let it allocate either: an inference
+// server whose memory pool claimed the whole device at start-up (any later cudaMalloc fails or fragments
+// its arena), or a step that is already inside a latency-critical loop where an allocation would
+// synchronise the device.  For them the two FP32 partial buffers of msk_moe_forward live in the array
+// below, which every GPU that loads the library holds until the process exits.
+// Limit: s1 * T * top_k * 2I + s2 * T * top_k * H <= kStaticScratchFloats (4 MiB), e.g. 8 tokens at the
+// benchmark's expert shapes with s1 = 4, s2 = 2.
+constexpr size_t kStaticScratchFloats = 1u << 20;
+static __device__ __align__(256) float g_moe_static_scratch[kStaticScratchFloats];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_static_scratch_ptr[kMaxDevices] = {};  // device address of the array, per device
+}  // namespace
+
+extern "C" int msk_moe_forward_static(const MskMoeParams* q, int* status, void* stream) {
+    if (q == nullptr) return MSK_ERR_INVALID;
+    const size_t s1 = q->s1 > 0 ? q->s1 : 1, s2 = q->s2 > 0 ? q->s2 : 1;
+    if (q->T < 1 || q->top_k < 1 || q->H < 1 || q->I < 1) return MSK_ERR_INVALID;
+    const size_t pairs = static_cast<size_t>(q->T) * q->top_k;
+    const size_t h1_floats = s1 * pairs * 2 * q->I, y_floats = s2 * pairs * q->H;
+    if (h1_floats + y_floats > kStaticScratchFloats) return MSK_ERR_UNSUPPORTED;  // beyond the built-in scratch
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return MSK_ERR_CUDA;
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        // Set-up, once per device and with that device current.  In host code the array's name is only a
+        // stand-in; kernels need the address the runtime reports for the symbol on this device.
+        float* p = nullptr;
+        if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_moe_static_scratch) != cudaSuccess || p == nullptr)
+            return MSK_ERR_CUDA;
+        g_static_scratch_ptr[dev] = p;
+    }
+    MskMoeParams m = *q;
+    m.h1_part = g_static_scratch_ptr[dev];
+    m.y_part = g_static_scratch_ptr[dev] + h1_floats;
+    return msk_moe_forward(&m, status, stream);
+}

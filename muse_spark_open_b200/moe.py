@@ -113,3 +113,34 @@ def dequant(packed: torch.Tensor, e: int, rows: int, k: int) -> torch.Tensor:
     out = torch.empty((e, rows, k), dtype=torch.bfloat16, device=packed.device)
     abi.check(abi.lib().msk_moe_dequant(abi.ptr(packed), abi.ptr(out), e, rows, k, abi.stream_ptr()), "msk_moe_dequant")
     return out
+
+
+STATIC_SCRATCH_FLOATS = 1 << 20
+
+
+def forward_no_alloc(x, ids, wts, state, local_start, local_count, out, splits=None):
+    """The routed experts through `msk_moe_forward_static`: for hosts that cannot give the library scratch
+    memory and cannot let it allocate (their pool owns the device, or the step must not stall on an
+    allocation).  The partial buffers sit in a 4 MiB array inside the library, so the call is limited to
+    s1*T*k*2I + s2*T*k*H <= STATIC_SCRATCH_FLOATS; `out` is the caller's.  Calls share that array: keep
+    them in stream order.  Make the first call on a device outside any stream capture."""
+    t, h = x.shape
+    top_k = ids.shape[1]
+    s1, s2 = splits or splits_for(t, state["H"], state["I"])
+    if s1 * t * top_k * 2 * state["I"] + s2 * t * top_k * state["H"] > STATIC_SCRATCH_FLOATS:
+        raise abi.MskError("this step needs more scratch than the library's built-in 4 MiB: use forward()")
+    p = abi.MoeParams()
+    p.x, p.ldx = abi.ptr(x), x.stride(0)
+    p.topk_ids, p.topk_weights, p.T, p.top_k = abi.ptr(ids), abi.ptr(wts), t, top_k
+    first = local_start - state["weights_start"]
+    blob13 = (2 * state["I"] // 128) * (state["H"] // 128) * 9216
+    blob2 = (state["H"] // 128) * (state["I"] // 128) * 9216
+    p.local_start, p.local_count = local_start, local_count
+    p.w13_packed, p.w2_packed = state["w13"].data_ptr() + first * blob13, state["w2"].data_ptr() + first * blob2
+    p.w13_gs, p.w2_gs = state["w13_gs"].data_ptr() + 4 * first, state["w2_gs"].data_ptr() + 4 * first
+    p.post_norm_w, p.post_eps, p.H, p.I = abi.ptr(state["post_w"]), POST_NORM_EPS, state["H"], state["I"]
+    p.s1, p.s2 = s1, s2
+    p.out, p.out_fp32, p.ldo = abi.ptr(out), int(out.dtype == torch.float32), out.stride(0)
+    st = abi.status_for(x.device)
+    abi.check(abi.lib().msk_moe_forward_static(C.byref(p), st.p, abi.stream_ptr()), "msk_moe_forward_static")
+    return out
