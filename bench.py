@@ -237,7 +237,7 @@ def run_ours(args):
                 "d2h_bytes_per_step": d2h * world},
         "gpu_launches": launches * args.steps, "clocks": clocks,
     }
-    if world == 1:
+    if world == 1 and not args.skip_extras:
         hidden, stream_out, ids = out
         touched = int(torch.unique(ids).numel())
         buf = state["bufs"][r_count]
@@ -289,6 +289,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-extras", action="store_true",
+                    help="only the timed step (no per-kernel, per-batch or CPU legs): what a profiler launch list wants")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.steps > 5:
