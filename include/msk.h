@@ -125,8 +125,9 @@ int msk_moe_packed_bytes(int E, int H, int I, size_t* w13_bytes, size_t* w2_byte
 int msk_moe_pack(const MskMoeWeights* w, void* w13_packed, void* w2_packed, void* stream);
 /* Test hook: expand a packed buffer to BF16 [E, R, K] = e2m1 * e4m3 scale (no per-expert scale). */
 int msk_moe_dequant(const void* packed, void* out_bf16, int E, int R, int K, void* stream);
-/* Bytes of the two FP32 scratch buffers msk_moe_forward needs for T tokens. */
-int msk_moe_scratch_bytes(int T, int top_k, int H, int I, int s1, int s2, size_t* h1_bytes, size_t* y_bytes);
+/* Bytes of the scratch buffers msk_moe_forward needs for T tokens (x_sorted is 0 up to 32 tokens). */
+int msk_moe_scratch_bytes(int T, int top_k, int H, int I, int s1, int s2, size_t* h1_bytes, size_t* y_bytes,
+                          size_t* inter_bytes, size_t* x_sorted_bytes, size_t* route_bytes);
 
 typedef struct {
     const void* x;              /* bf16 [T, ldx] */
@@ -151,6 +152,9 @@ typedef struct {
     int H, I;
     float* h1_part;             /* scratch fp32 [s1, T*top_k, 2I] */
     float* y_part;              /* scratch fp32 [s2, T*top_k, H] */
+    void* inter_sorted;         /* scratch bf16 [T*top_k, I]: activations between the GEMMs, expert-list order */
+    void* x_sorted;             /* scratch bf16 [T*top_k, H]: gathered inputs; only needed for T > 32 */
+    int32_t* route_pub;         /* scratch int32 [2 + T*top_k]: the routing list gemm 1 publishes */
     int s1, s2;                 /* K splits of the two GEMMs (divide H/128 and I/128) */
     const float* resid;         /* optional fp32 [T, ldr] added to the result */
     int ldr;
@@ -166,10 +170,10 @@ int msk_moe_forward(const MskMoeParams* p, int* status, void* stream);
 /* msk_moe_forward for callers that can neither pass scratch nor let the library allocate (a server whose
  * memory pool owns the whole device, a step inside a loop where an allocation would stall the GPU).
  * No counterpart in the reference, whose kernel_fn allocates freely (muse_moe_w4a16/submission.py:882-886).
- * `h1_part` and `y_part` of `p` are ignored: both partial buffers live in a 4 MiB array inside the
- * library that each GPU holds from load to exit.  Accepted while
- *     s1 * T * top_k * 2 * I + s2 * T * top_k * H  <=  1 048 576 floats
- * (8 tokens at the benchmark's expert shapes with s1 = 4, s2 = 2); larger calls return -3 and run nothing.
+ * The scratch pointers of `p` are ignored: all scratch lives in a 4 MiB array inside the library that each
+ * GPU holds from load to exit.  Accepted while the five sizes msk_moe_scratch_bytes reports for the call,
+ * each rounded up to 256 bytes, sum to at most 4 194 304 bytes (8 tokens at the benchmark's expert shapes
+ * with s1 = 4, s2 = 2); larger calls return -3 and run nothing.
  * It calls no cudaMalloc / cudaFree and nothing that allocates.  The first call on a device looks up the
  * array's device address (cudaGetSymbolAddress): make that call before any stream capture.  All calls
  * on a device share the array; nothing in it has to be zero on entry and it keeps the last call's
@@ -217,8 +221,8 @@ typedef struct {
     float* stream1;                /* fp32 [T, H] stream after attention */
     void* xn1;                     /* bf16 [T, H] expert input before its row scale */
     float* ssq1;                   /* fp32 [H/128, T] */
-    float* router_part;            /* fp32 [H/64, T, E] */
-    int32_t* router_ticket;        /* int32 [ceil(T/32)], zero before the first call */
+    float* router_part;            /* fp32 [8, T, E] */
+    int32_t* router_ticket;        /* int32 [ceil(T/32) * ceil(E/32)], zero before the first call */
     float* logits;                 /* fp32 [T, E] */
     int attn_chunks, attn_stages, qkv_splits, o_splits;
     int pdl;                       /* also chain the first kernel to whatever precedes it */

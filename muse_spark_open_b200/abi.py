@@ -57,7 +57,7 @@ def lib() -> C.CDLL:
         _lib.msk_moe_packed_bytes.argtypes = [ci, ci, ci, vp, vp]
         _lib.msk_moe_pack.argtypes = [vp, vp, vp, vp]
         _lib.msk_moe_dequant.argtypes = [vp, vp, ci, ci, ci, vp]
-        _lib.msk_moe_scratch_bytes.argtypes = [ci, ci, ci, ci, ci, ci, vp, vp]
+        _lib.msk_moe_scratch_bytes.argtypes = [ci, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp]
         _lib.msk_moe_forward.argtypes = [vp, vp, vp]
         _lib.msk_moe_forward_static.argtypes = [vp, vp, vp]
         _lib.msk_layer_front.argtypes = [vp, vp, vp]
@@ -148,7 +148,8 @@ class MoeParams(C.Structure):
         ("T", C.c_int), ("top_k", C.c_int), ("local_start", C.c_int), ("local_count", C.c_int),
         ("w13_packed", C.c_void_p), ("w2_packed", C.c_void_p), ("w13_gs", C.c_void_p), ("w2_gs", C.c_void_p),
         ("post_norm_w", C.c_void_p), ("post_eps", C.c_float), ("H", C.c_int), ("I", C.c_int),
-        ("h1_part", C.c_void_p), ("y_part", C.c_void_p), ("s1", C.c_int), ("s2", C.c_int),
+        ("h1_part", C.c_void_p), ("y_part", C.c_void_p), ("inter_sorted", C.c_void_p), ("x_sorted", C.c_void_p),
+        ("route_pub", C.c_void_p), ("s1", C.c_int), ("s2", C.c_int),
         ("resid", C.c_void_p), ("ldr", C.c_int), ("out", C.c_void_p), ("out_fp32", C.c_int), ("ldo", C.c_int),
         ("out_copy", C.c_void_p), ("ldc", C.c_int), ("pdl", C.c_int),
     ]

@@ -237,6 +237,24 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
     const uint32_t trow = tmem + (static_cast<uint32_t>(warp * 32) << 16);
     bool ok = true;
 
+    // second half of a tile's work: wait for O^T = V^T . P^T, fold it into the running output, refill the ring
+    // slot.  It runs one iteration late (after the next tile's maxima), so the MMA's latency is hidden.
+    auto finish_tile = [&](int j) {
+        ok = mbar_wait(bar_o, j & 1, p.status, where | 6) && ok;
+        tc_fence_after();
+#pragma unroll
+        for (int c0 = 0; c0 < NR; c0 += 8) {
+            uint32_t v[8];
+            tmem_ld8(trow + 2 * NP + c0, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int g = 0; g < 8; ++g) o_acc[c0 + g] = o_acc[c0 + g] * alpha_s[c0 + g] + __uint_as_float(v[g]);
+        }
+        tc_fence_before();
+        if (tid == 0 && ok && j + nst < nt) issue_tile(j + nst);  // both MMAs that read slot j % nst are done
+        __syncwarp();
+    };
+
     if (tid == 0 && nt > 0) {
         ok = mbar_wait(full(0), 0, p.status, where | 3);
         tc_fence_after();
@@ -269,6 +287,7 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
                 if (lane == 0) wred[warp][c0 + g] = mx;
             }
         }
+        if (i > 0) finish_tile(i - 1);
         __syncthreads();
         if (tid < NR) {
             const float mo = m_s[tid];
@@ -323,20 +342,8 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
             umma_commit(bar_o);
         }
         __syncwarp();
-        ok = mbar_wait(bar_o, i & 1, p.status, where | 6) && ok;
-        tc_fence_after();
-#pragma unroll
-        for (int c0 = 0; c0 < NR; c0 += 8) {
-            uint32_t v[8];
-            tmem_ld8(trow + 2 * NP + c0, v);
-            tmem_wait_ld();
-#pragma unroll
-            for (int g = 0; g < 8; ++g) o_acc[c0 + g] = o_acc[c0 + g] * alpha_s[c0 + g] + __uint_as_float(v[g]);
-        }
-        tc_fence_before();
-        if (tid == 0 && ok && i + nst < nt) issue_tile(i + nst);  // both MMAs that read slot i % nst are done
-        __syncwarp();
     }
+    if (nt > 0) finish_tile(nt - 1);
     __syncthreads();
 
     // ---------------- the L new tokens: last CTA of the cluster, FP32 on CUDA cores
@@ -490,7 +497,7 @@ int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
     }
     if (C != 1 && C != 2 && C != 4 && C != 8) return MSK_ERR_INVALID;
     if ((tiles_max + C - 1) / C > kMaxTilesPerCta) return MSK_ERR_UNSUPPORTED;
-    int nst = q->stages > 0 ? q->stages : (L == 1 ? 2 : 3);
+    int nst = q->stages > 0 ? q->stages : 3;
     if (nst > kAttnMaxStages) nst = kAttnMaxStages;
     const int smem = 1024 + nst * kStageBytes + 4 * NP * 128 + NR * 128 * 4;
 

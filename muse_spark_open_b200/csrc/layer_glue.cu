@@ -2,8 +2,9 @@
 //   prep_norm    x = bf16(rmsnorm(stream) * (1 + w)), one block per token (the rounding point of the
 //                reference); also leaves ssq[t] = sum stream^2.
 //   router       FP32 logits[t, e] = rs[t] * sum_k (stream1[t,k] * (1 + w[k])) * R[e, k] + bias[e] on
-//                CUDA cores (expert ids must not depend on tensor-core rounding).  Split over K; the last
-//                block to finish (ticket) adds the partials in a fixed order, so ids are reproducible.
+//                CUDA cores (expert ids must not depend on tensor-core rounding).  Blocks of 32 tokens x 32
+//                experts x H/8 of K; the last block of a (token group, expert tile) to finish (ticket) adds
+//                the 8 partials in a fixed order, so ids are reproducible.
 #include "msk.h"
 #include "ptx.cuh"
 
@@ -63,55 +64,70 @@ struct RouterArgs {
     int T, H, E;
 };
 
-constexpr int kRouterK = 64;   // k per block
-constexpr int kRouterT = 32;   // tokens per block
+constexpr int kRouterK = 64;    // k per shared-memory sub-tile
+constexpr int kRouterT = 32;    // tokens per block
+constexpr int kRouterE = 32;    // experts per block
+constexpr int kRouterKS = 8;    // K splits (partials summed by the last block of each (token group, expert tile))
 
 __global__ void __launch_bounds__(256) router_kernel(RouterArgs p) {
-    extern __shared__ float rsm[];
+    __shared__ float Rs[kRouterE][kRouterK + 1];
+    __shared__ float hs[kRouterT][kRouterK];
     __shared__ int last;
-    float* Rs = rsm;                               // [E][kRouterK + 1]
-    float* hs = rsm + p.E * (kRouterK + 1);        // [kRouterT][kRouterK]
-    const int ks = blockIdx.x, tg = blockIdx.y, tid = threadIdx.x;
-    const int k0 = ks * kRouterK, t0 = tg * kRouterT;
-    const int nt = min(kRouterT, p.T - t0);
-    const int KS = gridDim.x;
-    for (int i = tid; i < p.E * kRouterK; i += 256) {  // router weights do not depend on the previous kernel
-        const int e = i / kRouterK, k = i % kRouterK;
-        Rs[e * (kRouterK + 1) + k] = p.R[static_cast<size_t>(e) * p.H + k0 + k];
-    }
+    const int ks = blockIdx.x, et = blockIdx.y, tg = blockIdx.z, tid = threadIdx.x;
+    const int t0 = tg * kRouterT, e0 = et * kRouterE;
+    const int nt = min(kRouterT, p.T - t0), ne = min(kRouterE, p.E - e0);
+    const int kper = p.H / kRouterKS;
+    const int tw = tid >> 5, el = tid & 31;  // warp w owns tokens w, w+8, w+16, w+24; lane = expert
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     pdl_wait();
     pdl_launch_dependents();
-    for (int i = tid; i < kRouterT * kRouterK; i += 256) {
-        const int t = i / kRouterK, k = i % kRouterK;
-        hs[i] = t < nt ? __ldcg(p.s1 + static_cast<size_t>(t0 + t) * p.H + k0 + k) * (1.0f + __bfloat162float(p.w[k0 + k])) : 0.0f;
+    for (int kb = ks * kper; kb < (ks + 1) * kper; kb += kRouterK) {
+        for (int i = tid; i < kRouterE * kRouterK; i += 256) {
+            const int e = i / kRouterK, k = i % kRouterK;
+            Rs[e][k] = e < ne ? p.R[static_cast<size_t>(e0 + e) * p.H + kb + k] : 0.0f;
+        }
+        for (int i = tid; i < kRouterT * kRouterK; i += 256) {
+            const int t = i / kRouterK, k = i % kRouterK;
+            hs[t][k] = t < nt ? __ldcg(p.s1 + static_cast<size_t>(t0 + t) * p.H + kb + k) * (1.0f + __bfloat162float(p.w[kb + k])) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int k = 0; k < kRouterK; ++k) {
+            const float r = Rs[el][k];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[j] = fmaf(hs[tw + 8 * j][k], r, acc[j]);
+        }
+        __syncthreads();
     }
-    __syncthreads();
-    for (int o = tid; o < nt * p.E; o += 256) {
-        const int t = o / p.E, e = o % p.E;
-        const float* r = Rs + e * (kRouterK + 1);
-        const float* h = hs + t * kRouterK;
-        float acc = 0.0f;
-#pragma unroll 8
-        for (int k = 0; k < kRouterK; ++k) acc = fmaf(h[k], r[k], acc);
-        p.part[(static_cast<size_t>(ks) * p.T + t0 + t) * p.E + e] = acc;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int t = tw + 8 * j;
+        if (t < nt && el < ne) p.part[(static_cast<size_t>(ks) * p.T + t0 + t) * p.E + e0 + el] = acc[j];
     }
     __threadfence();
     __syncthreads();
-    if (tid == 0) last = atomicAdd(p.ticket + tg, 1) == KS - 1;
+    if (tid == 0) last = atomicAdd(p.ticket + tg * gridDim.y + et, 1) == kRouterKS - 1;
     __syncthreads();
     if (!last) return;
     __threadfence();
-    for (int o = tid; o < nt * p.E; o += 256) {
-        const int t = o / p.E, e = o % p.E;
-        float acc = 0.0f;
-        for (int s = 0; s < KS; ++s) acc += __ldcg(p.part + (static_cast<size_t>(s) * p.T + t0 + t) * p.E + e);
-        float ss = 0.0f;
-        for (int q = 0; q < p.ssq_parts; ++q) ss += __ldcg(p.ssq + q * p.T + t0 + t);
-        acc *= rsqrtf(ss / p.H + p.eps);
-        if (p.bias != nullptr) acc += p.bias[e];
-        p.logits[static_cast<size_t>(t0 + t) * p.E + e] = acc;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int t = tw + 8 * j;
+        if (t < nt && el < ne) {
+            float v[kRouterKS];
+#pragma unroll
+            for (int s = 0; s < kRouterKS; ++s) v[s] = __ldcg(p.part + (static_cast<size_t>(s) * p.T + t0 + t) * p.E + e0 + el);
+            float sum = 0.0f;
+#pragma unroll
+            for (int s = 0; s < kRouterKS; ++s) sum += v[s];
+            float ss = 0.0f;
+            for (int q = 0; q < p.ssq_parts; ++q) ss += __ldcg(p.ssq + q * p.T + t0 + t);
+            sum *= rsqrtf(ss / p.H + p.eps);
+            if (p.bias != nullptr) sum += p.bias[e0 + el];
+            p.logits[static_cast<size_t>(t0 + t) * p.E + e0 + el] = sum;
+        }
     }
-    if (tid == 0) p.ticket[tg] = 0;  // ready for the next call
+    if (tid == 0) p.ticket[tg * gridDim.y + et] = 0;  // ready for the next call
 }
 
 template <typename Kern, typename Args>
@@ -155,7 +171,7 @@ extern "C" int msk_layer_front(const MskLayerFront* f, int* status, void* stream
         !f->router_ticket || !f->logits)
         return MSK_ERR_INVALID;
     const int T = f->B * f->L, H = f->H, nqkv = (2 * f->Hq + 2 * f->Hkv) * f->d, no = f->Hq * f->d;
-    if (T < 1 || T > 256 || H % 1024 != 0 || H > 8192 || f->E < 1 || f->E > 256) return MSK_ERR_UNSUPPORTED;
+    if (T < 1 || T > 256 || H % 1024 != 0 || H > 8192 || H % (kRouterKS * kRouterK) != 0 || f->E < 1 || f->E > 256) return MSK_ERR_UNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     int rc = launch_prep(f->stream, f->input_norm_w, f->xn0, f->ssq0, T, H, f->norm_eps, s, f->pdl);
     if (rc != 0) return rc;
@@ -190,14 +206,7 @@ extern "C" int msk_layer_front(const MskLayerFront* f, int* status, void* stream
     r.s1 = f->stream1, r.w = static_cast<const __nv_bfloat16*>(f->pre_expert_norm_w), r.ssq = f->ssq1;
     r.ssq_parts = (H + 127) / 128, r.eps = f->norm_eps, r.R = f->router_w, r.bias = f->router_bias;
     r.part = f->router_part, r.ticket = f->router_ticket, r.logits = f->logits, r.T = T, r.H = H, r.E = f->E;
-    const int rsmem = (f->E * (kRouterK + 1) + kRouterT * kRouterK) * 4;
-    static int configured = 0;
-    if (rsmem > configured) {
-        if (cudaFuncSetAttribute(router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, rsmem) != cudaSuccess)
-            return MSK_ERR_CUDA;
-        configured = rsmem;
-    }
-    return launch1(router_kernel, dim3(H / kRouterK, (T + kRouterT - 1) / kRouterT), dim3(256), rsmem, s, 1, r);
+    return launch1(router_kernel, dim3(kRouterKS, (f->E + kRouterE - 1) / kRouterE, (T + kRouterT - 1) / kRouterT), dim3(256), 0, s, 1, r);
 }
 
 extern "C" int msk_layer_decode(const MskLayerParams* p, int* status, void* stream) {

@@ -1,7 +1,8 @@
 // NVFP4 (w4a16) routed experts: grouped GEMMs with the routing done inside the GEMM CTAs.
 //
 //   gemm 1   h[pair, 2I] = x[token(pair)] . W13[expert(pair)]^T      (gate rows, then up rows)
-//   gemm 2   y[pair, H]  = bf16(silu(h_gate) * h_up) . W2[expert]^T
+//   act      inter[pair, I] = bf16(silu(h_gate) * h_up), rows in expert-list order
+//   gemm 2   y[pair, H]  = inter . W2[expert]^T
 //   combine  out[t] = sum over the token's local (expert) slots of w[t, slot] * rmsnorm(y * (1 + w_post))
 //
 // A "pair" is one (token, routed slot).  Every gemm CTA rebuilds the routing in shared memory (from
@@ -9,17 +10,18 @@
 // pair lists and walks the work units (expert-group of <= 32 pairs, 128-row tile, K split) that fall
 // to it, so every touched expert's weights stream through the SMs once.
 //
-// One persistent CTA per SM, 18 warps:
-//   warp 0        producer: one untiled bulk copy (TMA) per 128x128 weight block: 8 KB of bit-permuted
-//                 E2M1 codes + 1 KB of E4M3 block scales, repacked at prepare time so that a block is
-//                 one contiguous 9216-byte read and each thread's 16 bytes sit at a conflict-free slot.
+// One persistent CTA per SM, 14 warps:
+//   warp 0        producer: per 128x128 weight block one untiled bulk copy (TMA) of 8 KB of bit-permuted
+//                 E2M1 codes + 1 KB of E4M3 block scales (repacked at prepare time: one contiguous
+//                 9216-byte read, each thread's 16 bytes at a conflict-free slot), and two TMA boxes of the
+//                 B operand (32 rows x 64 k, 128-byte swizzle) into the same ring stage: x itself when the
+//                 step has at most 32 tokens (column = token), else x gathered in expert-list order by a
+//                 small kernel; for gemm 2 the activations the act kernel wrote in that order.
 //   warps 6..13   dequant: thread = weight row.  8 codes per word become 4 BF16x2 registers with 3
 //                 shift+mask steps (the permutation puts every code's bits where BF16 wants them,
 //                 magnitudes as BF16 subnormals * 2^-126), times the block scale (E4M3 * 2^100 as BF16)
 //                 with one HMUL2 each: exact E2M1 x E4M3 products * 2^-26, written straight into tensor
 //                 memory (tcgen05.st) as the A operand.  No BF16 round trip through shared memory.
-//   warps 14..17  stage the B operand: the expert-group's token rows of x (gemm 1) or silu(gate)*up
-//                 computed from the gemm-1 partials (gemm 2), K-major with the 128-byte swizzle.
 //   warp 1        one lane issues tcgen05.mma kind::f16, A from TMEM, B from shared memory, FP32
 //                 accumulators in TMEM (double-buffered per unit).
 //   warps 2..5    epilogue: tcgen05.ld, times global scale * 2^26 (and the folded pre-expert RMSNorm row
@@ -31,20 +33,22 @@
 
 #include "msk.h"
 #include "ptx.cuh"
+#include "tmap.cuh"
 
 namespace msk {
 
 constexpr int kBlob = 9216;        // one packed 128-row x 128-k weight block
 constexpr int kBlobScales = 8192;  // offset of the 128 x 8 block scales inside a blob
-constexpr int kNRaw = 16;          // raw ring slots
-constexpr int kNB = 4;             // B ring slots
-constexpr int kBSlot = 8192;       // 32 rows x 256 bytes
+constexpr int kBSlot = 8192;       // B tile of one stage: 32 rows x 256 bytes (two 128-byte-swizzled halves)
+constexpr int kStage = kBlob + kBSlot;
+constexpr int kNRaw = 11;          // ring stages (weight block + B tile)
 constexpr int kNA = 4;             // A slots in tensor memory, 64 columns each
 constexpr int kGroup = 32;         // pairs per expert-group (UMMA N)
 constexpr int kMaxPairs = 2048;
 constexpr int kMaxExperts = 256;
 constexpr int kMaxGroups = 320;
-constexpr int kMoeThreads = 18 * 32;
+constexpr int kMoeThreads = 14 * 32;
+constexpr int kRouteThreads = kMoeThreads, kRouteWarps = kRouteThreads / 32;
 
 // ---------------------------------------------------------------- weight repacking (prepare time)
 // destination bit of (code i, field f) with fields m, e0, e1, s = code bits 0..3
@@ -122,43 +126,27 @@ __global__ void moe_dequant_kernel(const uint8_t* __restrict__ packed, __nv_bflo
     }
 }
 
-// ---------------------------------------------------------------- grouped GEMM
-struct MoeGemmArgs {
-    const int* ids;          // [T, top_k]
-    const float* wts;        // [T, top_k]
-    const float* logits;     // [T, n_logits] or null
+// ---------------------------------------------------------------- routing tables (rebuilt by every CTA)
+struct RouteArgs {
+    const int* ids;       // [T, top_k] given expert ids (ignored when logits != null)
+    const float* logits;  // [T, ld_logits] router logits, or null
     int n_logits, ld_logits;
-    int* ids_out;            // written by CTA 0 when routing from logits
+    int* ids_out;         // published by CTA 0 when routing from logits
     float* wts_out;
     int T, top_k, local_start, local_count;
-    const uint8_t* wpacked;
-    const float* gs;         // [local_count]
-    int R, K;                // rows and reduction length per expert
-    const __nv_bfloat16* x;  // gemm 1 B source
-    int ldx;
-    const float* x_ssq;
-    int x_ssq_parts, x_ssq_ts;
-    float x_inv_dim, x_eps;
-    const float* hprev;      // gemm 2 B source: gemm-1 partials [s_prev][T*top_k][2I]
-    int s_prev, inner;
-    float* outp;             // [S][T*top_k][R]
-    int S;
-    int* status;
 };
 
-struct MoeShared {
-    uint64_t raw_full[kNRaw], raw_empty[kNRaw], a_full[kNA], a_empty[kNA], b_full[kNB], b_empty[kNB], d_full[2],
-        d_empty[2];
-    uint32_t tmem_slot;
-    int n_groups;
+struct RouteTables {
+    int n_groups, n_local;
     int counts[kMaxExperts];
     int offs[kMaxExperts + 1];
-    unsigned short ids_s[kMaxPairs];
+    unsigned short ids_s[kMaxPairs];   // expert id of every pair (65535 = none)
     unsigned short pos_s[kMaxPairs];
-    unsigned short list[kMaxPairs];
+    unsigned short list[kMaxPairs];    // pairs sorted by (local expert, pair index)
     unsigned short g_expert[kMaxGroups], g_off[kMaxGroups], g_n[kMaxGroups];
-    unsigned short seg_cnt[kMoeThreads / 32][kMaxExperts];  // pairs per (warp segment, expert)
-    float rs[kMaxPairs / 8];
+    unsigned short seg_cnt[kRouteWarps][kMaxExperts];  // pairs per (warp segment, expert)
+    int r_ids[kRouteWarps][8];
+    float r_w[kRouteWarps][8];
 };
 
 // softmax -> top-k -> renormalise for one token, one warp.  Ties go to the lower expert id.
@@ -200,143 +188,234 @@ __device__ void route_token(const float* logits, int n, int top_k, int lane, int
     }
 }
 
-template <int MODE>
-__global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(MoeGemmArgs p) {
-    extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) MoeShared sh;
-    __shared__ int r_ids[kMoeThreads / 32][8];
-    __shared__ float r_w[kMoeThreads / 32][8];
+// Builds the tables from ids (or logits).  Called by all kRouteThreads threads of a CTA; the result is
+// the same in every CTA and every kernel (pure counting, no atomics): an expert's list is cut into
+// groups that different CTAs and kernels work on, so its order must not depend on who built it.
+__device__ void build_routing(RouteTables& rt, const RouteArgs& a, int* status, int where) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int where = (MODE == 1 ? MSK_K_MOE1 : MSK_K_MOE2) << 8;
-    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t s_b = base + kNRaw * kBlob;
-    const int P = p.T * p.top_k;
-
-    if (warp == 0) {
-        tmem_alloc(smem_u32(&sh.tmem_slot), 512);
-        tmem_relinquish();
-    }
-    if (tid == 32) {
-        for (int i = 0; i < kNRaw; ++i) mbar_init(smem_u32(&sh.raw_full[i]), 1), mbar_init(smem_u32(&sh.raw_empty[i]), 4);
-        for (int i = 0; i < kNA; ++i) mbar_init(smem_u32(&sh.a_full[i]), 4), mbar_init(smem_u32(&sh.a_empty[i]), 1);
-        for (int i = 0; i < kNB; ++i) mbar_init(smem_u32(&sh.b_full[i]), 4), mbar_init(smem_u32(&sh.b_empty[i]), 1);
-        for (int i = 0; i < 2; ++i) mbar_init(smem_u32(&sh.d_full[i]), 1), mbar_init(smem_u32(&sh.d_empty[i]), 4);
-        fence_mbar_init();
-    }
-    pdl_wait();  // routing (and x / the gemm-1 partials) come from the previous kernel
-    pdl_launch_dependents();
-
-    // ---------------- routing: ids -> per-expert pair lists -> expert-groups
-    if (MODE == 1 && p.logits != nullptr) {
-        for (int t = warp; t < p.T; t += kMoeThreads / 32) {
-            route_token(p.logits + static_cast<size_t>(t) * p.ld_logits, p.n_logits, p.top_k, lane, r_ids[warp], r_w[warp]);
+    const int P = a.T * a.top_k;
+    if (a.logits != nullptr) {
+        for (int t = warp; t < a.T; t += kRouteWarps) {
+            route_token(a.logits + static_cast<size_t>(t) * a.ld_logits, a.n_logits, a.top_k, lane, rt.r_ids[warp], rt.r_w[warp]);
             __syncwarp();
-            if (lane < p.top_k) {
-                sh.ids_s[t * p.top_k + lane] = static_cast<unsigned short>(r_ids[warp][lane]);
-                if (blockIdx.x == 0) {
-                    p.ids_out[t * p.top_k + lane] = r_ids[warp][lane];
-                    p.wts_out[t * p.top_k + lane] = r_w[warp][lane];
+            if (lane < a.top_k) {
+                rt.ids_s[t * a.top_k + lane] = static_cast<unsigned short>(rt.r_ids[warp][lane]);
+                if (blockIdx.x == 0 && a.ids_out != nullptr) {
+                    a.ids_out[t * a.top_k + lane] = rt.r_ids[warp][lane];
+                    a.wts_out[t * a.top_k + lane] = rt.r_w[warp][lane];
                 }
             }
             __syncwarp();
         }
     } else {
-        for (int i = tid; i < P; i += kMoeThreads) {
-            const int id = __ldcg(p.ids + i);
-            sh.ids_s[i] = static_cast<unsigned short>(id < 0 || id > 65534 ? 65535 : id);
+        for (int i = tid; i < P; i += kRouteThreads) {
+            const int id = __ldcg(a.ids + i);
+            rt.ids_s[i] = static_cast<unsigned short>(id < 0 || id > 65534 ? 65535 : id);
         }
     }
-    tc_fence_before();
+    for (int i = lane; i < kMaxExperts; i += 32) rt.seg_cnt[warp][i] = 0;
     __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = sh.tmem_slot;
-    // Position of every pair inside its expert's list = number of earlier pairs of the same expert.
-    // The order must be the same in every CTA (an expert's list is cut into groups that different
-    // CTAs work on), so it is computed by counting, not with atomics: each warp ranks one contiguous
-    // segment of the pairs (match_any inside a 32-pair chunk, running counts across chunks), then the
-    // segments' counts are prefix-summed per expert.
-    constexpr int kWarps = kMoeThreads / 32;
-    const int seg = ((P + kWarps - 1) / kWarps + 31) & ~31;
-    for (int i = lane; i < kMaxExperts; i += 32) sh.seg_cnt[warp][i] = 0;
-    __syncwarp();
+    // position of a pair in its expert's list = number of earlier pairs of that expert: each warp ranks a
+    // contiguous segment (match_any inside 32-pair chunks), then the segments are prefix-summed per expert
+    const int seg = ((P + kRouteWarps - 1) / kRouteWarps + 31) & ~31;
     for (int c0 = warp * seg; c0 < min(P, (warp + 1) * seg); c0 += 32) {
         const int i = c0 + lane;
-        int e = i < P ? static_cast<int>(sh.ids_s[i]) - p.local_start : -1;
-        if (e >= p.local_count) e = -1;
+        int e = i < P ? static_cast<int>(rt.ids_s[i]) - a.local_start : -1;
+        if (e >= a.local_count) e = -1;
         const unsigned same = __match_any_sync(0xffffffffu, e);
         const int rank = __popc(same & ((1u << lane) - 1u));
-        const int before = e >= 0 ? sh.seg_cnt[warp][e] : 0;
+        const int before = e >= 0 ? rt.seg_cnt[warp][e] : 0;
         __syncwarp();
         if (e >= 0) {
-            sh.pos_s[i] = static_cast<unsigned short>(before + rank);
-            if (rank == 0) sh.seg_cnt[warp][e] = static_cast<unsigned short>(before + __popc(same));
+            rt.pos_s[i] = static_cast<unsigned short>(before + rank);
+            if (rank == 0) rt.seg_cnt[warp][e] = static_cast<unsigned short>(before + __popc(same));
         }
         __syncwarp();
     }
     __syncthreads();
-    for (int e = tid; e < p.local_count; e += kMoeThreads) {
+    for (int e = tid; e < a.local_count; e += kRouteThreads) {
         int run = 0;
-        for (int w = 0; w < kWarps; ++w) {
-            const int c = sh.seg_cnt[w][e];
-            sh.seg_cnt[w][e] = static_cast<unsigned short>(run);
+        for (int w = 0; w < kRouteWarps; ++w) {
+            const int c = rt.seg_cnt[w][e];
+            rt.seg_cnt[w][e] = static_cast<unsigned short>(run);
             run += c;
         }
-        sh.counts[e] = run;
-    }
-    if (MODE == 1 && p.x_ssq != nullptr) {
-        for (int t = tid; t < p.T; t += kMoeThreads) {
-            float s = 0.0f;
-            for (int part = 0; part < p.x_ssq_parts; ++part) s += __ldcg(p.x_ssq + (static_cast<size_t>(part) * p.T + t) * p.x_ssq_ts);
-            sh.rs[t] = rsqrtf(s * p.x_inv_dim + p.x_eps);
-        }
+        rt.counts[e] = run;
     }
     __syncthreads();
     if (tid == 0) {
         int off = 0, ng = 0;
-        for (int e = 0; e < p.local_count; ++e) {
-            const int n = sh.counts[e];
-            sh.offs[e] = off;
+        for (int e = 0; e < a.local_count; ++e) {
+            const int n = rt.counts[e];
+            rt.offs[e] = off;
             for (int g = 0; g < n; g += kGroup) {
                 if (ng < kMaxGroups) {
-                    sh.g_expert[ng] = static_cast<unsigned short>(e);
-                    sh.g_off[ng] = static_cast<unsigned short>(off + g);
-                    sh.g_n[ng] = static_cast<unsigned short>(min(kGroup, n - g));
+                    rt.g_expert[ng] = static_cast<unsigned short>(e);
+                    rt.g_off[ng] = static_cast<unsigned short>(off + g);
+                    rt.g_n[ng] = static_cast<unsigned short>(min(kGroup, n - g));
                     ++ng;
                 } else {
-                    report(p.status, MSK_ERR_CAPACITY, where | 1, ng, kMaxGroups);
+                    report(status, MSK_ERR_CAPACITY, where | 1, ng, kMaxGroups);
                 }
             }
             off += n;
         }
-        sh.n_groups = ng;
+        rt.n_groups = ng;
+        rt.n_local = off;
     }
     __syncthreads();
-    for (int i = tid; i < P; i += kMoeThreads) {
-        const int e = static_cast<int>(sh.ids_s[i]) - p.local_start;
-        if (e >= 0 && e < p.local_count)
-            sh.list[sh.offs[e] + sh.seg_cnt[i / seg][e] + sh.pos_s[i]] = static_cast<unsigned short>(i);
+    for (int i = tid; i < P; i += kRouteThreads) {
+        const int e = static_cast<int>(rt.ids_s[i]) - a.local_start;
+        if (e >= 0 && e < a.local_count) rt.list[rt.offs[e] + rt.seg_cnt[i / seg][e] + rt.pos_s[i]] = static_cast<unsigned short>(i);
     }
     __syncthreads();
+}
+
+// ---------------------------------------------------------------- B-operand helpers
+// gather (more than 32 tokens): x rows in expert-list order, so that an expert-group's B tile is one TMA box
+struct MoeGatherArgs {
+    RouteArgs route;
+    const __nv_bfloat16* x;
+    int ldx, H;
+    __nv_bfloat16* x_sorted;  // [T*top_k, H]
+    int* status;
+};
+
+__global__ void __launch_bounds__(kRouteThreads) moe_gather_kernel(MoeGatherArgs p) {
+    __shared__ RouteTables rt;
+    pdl_wait();
+    pdl_launch_dependents();
+    RouteArgs ra = p.route;
+    ra.ids_out = nullptr;
+    build_routing(rt, ra, p.status, MSK_K_MOE1 << 8);
+    const int tid = threadIdx.x;
+    for (int r = blockIdx.x; r < rt.n_local; r += gridDim.x) {
+        const int tok = rt.list[r] / p.route.top_k;
+        const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(tok) * p.ldx);
+        uint4* dst = reinterpret_cast<uint4*>(p.x_sorted + static_cast<size_t>(r) * p.H);
+        for (int i = tid; i < p.H / 8; i += kRouteThreads) dst[i] = __ldcg(src + i);
+    }
+}
+
+// activation between the two GEMMs: inter[r] = bf16(silu(gate) * up) of the r-th pair in expert-list order
+struct MoeActArgs {
+    const int* route_pub;  // [0] = local pairs, [2 + r] = pair of sorted row r (published by gemm 1)
+    const float* h1;       // [s1][P][2I]
+    int s1, P, inner;
+    __nv_bfloat16* inter;  // [P, I]
+};
+
+__global__ void __launch_bounds__(256) moe_act_kernel(MoeActArgs p) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int n_local = __ldcg(p.route_pub);
+    for (int r = blockIdx.x; r < n_local; r += gridDim.x) {
+        const int pair = __ldcg(p.route_pub + 2 + r);
+        for (int k = threadIdx.x * 4; k < p.inner; k += 1024) {
+            float4 g = make_float4(0, 0, 0, 0), u = make_float4(0, 0, 0, 0);
+            for (int s = 0; s < p.s1; ++s) {
+                const float* row = p.h1 + (static_cast<size_t>(s) * p.P + pair) * (2 * p.inner) + k;
+                const float4 a = __ldcg(reinterpret_cast<const float4*>(row));
+                const float4 c = __ldcg(reinterpret_cast<const float4*>(row + p.inner));
+                g.x += a.x, g.y += a.y, g.z += a.z, g.w += a.w;
+                u.x += c.x, u.y += c.y, u.z += c.z, u.w += c.w;
+            }
+            const float o0 = g.x / (1.0f + __expf(-g.x)) * u.x, o1 = g.y / (1.0f + __expf(-g.y)) * u.y;
+            const float o2 = g.z / (1.0f + __expf(-g.z)) * u.z, o3 = g.w / (1.0f + __expf(-g.w)) * u.w;
+            *reinterpret_cast<uint2*>(p.inter + static_cast<size_t>(r) * p.inner + k) = make_uint2(pack_bf16(o0, o1), pack_bf16(o2, o3));
+        }
+    }
+}
+
+// ---------------------------------------------------------------- grouped GEMM
+struct MoeGemmArgs {
+    RouteArgs route;
+    const uint8_t* wpacked;
+    const float* gs;   // [local_count]
+    int R, K;          // rows and reduction length per expert
+    int direct;        // gemm 1 with <= 32 tokens: B rows are the tokens themselves (column = token)
+    const float* x_ssq;
+    int x_ssq_parts, x_ssq_ts;
+    float x_inv_dim, x_eps;
+    int* route_pub;    // gemm 1, CTA 0: [0] local pairs, [1] groups, [2 + r] pair of sorted row r
+    float* outp;       // [S][T*top_k][R]
+    int S;
+    int* status;
+};
+
+struct MoeBars {
+    uint64_t raw_full[kNRaw], raw_empty[kNRaw], a_full[kNA], a_empty[kNA], d_full[2], d_empty[2];
+    uint32_t tmem_slot;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_b, MoeGemmArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) MoeBars bar;
+    __shared__ RouteTables rt;
+    __shared__ float rs_s[kMaxPairs / 8];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int where = (MODE == 1 ? MSK_K_MOE1 : MSK_K_MOE2) << 8;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
+    const int P = p.route.T * p.route.top_k;
+
+    if (warp == 0) {
+        tmem_alloc(smem_u32(&bar.tmem_slot), 512);
+        tmem_relinquish();
+    }
+    if (tid == 32) {
+        // a ring stage (weight block + B tile) is free again when the 4 dequant warps have read the block and
+        // the MMAs that read the B tile have completed
+        for (int i = 0; i < kNRaw; ++i) mbar_init(smem_u32(&bar.raw_full[i]), 1), mbar_init(smem_u32(&bar.raw_empty[i]), 5);
+        for (int i = 0; i < kNA; ++i) mbar_init(smem_u32(&bar.a_full[i]), 4), mbar_init(smem_u32(&bar.a_empty[i]), 1);
+        for (int i = 0; i < 2; ++i) mbar_init(smem_u32(&bar.d_full[i]), 1), mbar_init(smem_u32(&bar.d_empty[i]), 4);
+        fence_mbar_init();
+    }
+    if (tid == 0) prefetch_tmap(&tm_b);
+    pdl_wait();  // routing, x and the gemm-1 activations come from the previous kernels
+    pdl_launch_dependents();
+    build_routing(rt, p.route, p.status, where);
+    if (MODE == 1 && p.x_ssq != nullptr) {
+        for (int t = tid; t < p.route.T; t += kMoeThreads) {
+            float s = 0.0f;
+            for (int part = 0; part < p.x_ssq_parts; ++part)
+                s += __ldcg(p.x_ssq + (static_cast<size_t>(part) * p.route.T + t) * p.x_ssq_ts);
+            rs_s[t] = rsqrtf(s * p.x_inv_dim + p.x_eps);
+        }
+    }
+    if (MODE == 1 && blockIdx.x == 0 && p.route_pub != nullptr) {
+        if (tid == 0) p.route_pub[0] = rt.n_local, p.route_pub[1] = rt.n_groups;
+        for (int r = tid; r < rt.n_local; r += kMoeThreads) p.route_pub[2 + r] = rt.list[r];
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = bar.tmem_slot;
 
     const int tiles = p.R / 128, KC = p.K / 128, nch = KC / p.S;
     const int per_group = tiles * p.S;
-    const int n_units = sh.n_groups * per_group;
+    const int n_units = rt.n_groups * per_group;
 
     if (warp == 0) {
-        // ------------------------------------------------ producer
+        // ------------------------------------------------ producer: weight block (bulk copy) + B tile (2 TMA boxes)
         if (lane == 0) {
             int cc = 0;
             bool ok = true;
             for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
                 const int g = u / per_group, rem = u % per_group, tile = rem / p.S, ks = rem % p.S;
-                const uint8_t* src = p.wpacked + ((static_cast<size_t>(sh.g_expert[g]) * tiles + tile) * KC + ks * nch) * kBlob;
+                const uint8_t* src = p.wpacked + ((static_cast<size_t>(rt.g_expert[g]) * tiles + tile) * KC + ks * nch) * kBlob;
+                const int row0 = p.direct ? 0 : rt.g_off[g];
                 for (int c = 0; c < nch; ++c, ++cc) {
                     const int s = cc % kNRaw;
-                    if (cc >= kNRaw) ok = mbar_wait(smem_u32(&sh.raw_empty[s]), ((cc / kNRaw) - 1) & 1, p.status, where | 2);
+                    if (cc >= kNRaw) ok = mbar_wait(smem_u32(&bar.raw_empty[s]), ((cc / kNRaw) - 1) & 1, p.status, where | 2);
                     if (!ok) break;
-                    mbar_expect_tx(smem_u32(&sh.raw_full[s]), kBlob);
-                    bulk_load(base + s * kBlob, src + static_cast<size_t>(c) * kBlob, kBlob, smem_u32(&sh.raw_full[s]));
+                    const uint32_t full = smem_u32(&bar.raw_full[s]), dst = base + s * kStage;
+                    const int k0 = (ks * nch + c) * 128;
+                    mbar_expect_tx(full, kStage);
+                    bulk_load(dst, src + static_cast<size_t>(c) * kBlob, kBlob, full);
+                    tma_load_2d(dst + kBlob, &tm_b, full, k0, row0);
+                    tma_load_2d(dst + kBlob + 4096, &tm_b, full, k0 + 64, row0);
                 }
             }
         }
@@ -349,24 +428,25 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(MoeGemmArgs p)
             bool ok = true;
             for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++uc) {
                 const int db = uc & 1;
-                if (uc >= 2) ok = mbar_wait(smem_u32(&sh.d_empty[db]), ((uc >> 1) - 1) & 1, p.status, where | 3);
+                if (uc >= 2) ok = mbar_wait(smem_u32(&bar.d_empty[db]), ((uc >> 1) - 1) & 1, p.status, where | 3);
                 tc_fence_after();
                 const uint32_t d = tmem + kNA * 64 + db * kGroup;
                 for (int c = 0; c < nch && ok; ++c, ++cc) {
-                    const int as = cc % kNA, bs = cc % kNB;
-                    ok = mbar_wait(smem_u32(&sh.a_full[as]), (cc / kNA) & 1, p.status, where | 4) &&
-                         mbar_wait(smem_u32(&sh.b_full[bs]), (cc / kNB) & 1, p.status, where | 5);
+                    const int as = cc % kNA, s = cc % kNRaw;
+                    ok = mbar_wait(smem_u32(&bar.raw_full[s]), (cc / kNRaw) & 1, p.status, where | 5) &&
+                         mbar_wait(smem_u32(&bar.a_full[as]), (cc / kNA) & 1, p.status, where | 4);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint64_t b0 = umma_smem_desc(s_b + bs * kBSlot, 16, 1024, kSwizzle128);
-                    const uint64_t b1 = umma_smem_desc(s_b + bs * kBSlot + 4096, 16, 1024, kSwizzle128);
+                    const uint32_t bb = base + s * kStage + kBlob;
+                    const uint64_t b0 = umma_smem_desc(bb, 16, 1024, kSwizzle128);
+                    const uint64_t b1 = umma_smem_desc(bb + 4096, 16, 1024, kSwizzle128);
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
                         umma_f16_ts(d, tmem + as * 64 + 8 * j, (j < 4 ? b0 : b1) + 2 * (j & 3), idesc, (c | j) != 0);
-                    umma_commit(smem_u32(&sh.a_empty[as]));
-                    umma_commit(smem_u32(&sh.b_empty[bs]));
+                    umma_commit(smem_u32(&bar.a_empty[as]));
+                    umma_commit(smem_u32(&bar.raw_empty[s]));
                 }
-                if (ok) umma_commit(smem_u32(&sh.d_full[db]));
+                if (ok) umma_commit(smem_u32(&bar.d_full[db]));
             }
         }
         __syncwarp();
@@ -377,8 +457,18 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(MoeGemmArgs p)
         bool ok = true;
         for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++uc) {
             const int g = u / per_group, rem = u % per_group, tile = rem / p.S, ks = rem % p.S;
-            const int db = uc & 1, e = sh.g_expert[g], off = sh.g_off[g], n = sh.g_n[g];
-            ok = mbar_wait(smem_u32(&sh.d_full[db]), (uc >> 1) & 1, p.status, where | 6);
+            const int db = uc & 1, e = rt.g_expert[g], off = rt.g_off[g], n = rt.g_n[g];
+            // the pair whose result sits in accumulator column `lane`
+            int mypair = -1;
+            if (p.direct) {
+                if (lane < p.route.T)
+                    for (int sl = 0; sl < p.route.top_k; ++sl)
+                        if (static_cast<int>(rt.ids_s[lane * p.route.top_k + sl]) == e + p.route.local_start) mypair = lane * p.route.top_k + sl;
+            } else if (lane < n) {
+                mypair = rt.list[off + lane];
+            }
+            const float myscale = (MODE == 1 && p.x_ssq != nullptr && mypair >= 0) ? rs_s[mypair / p.route.top_k] : 1.0f;
+            ok = mbar_wait(smem_u32(&bar.d_full[db]), (uc >> 1) & 1, p.status, where | 6);
             if (!ok) break;
             tc_fence_after();
             uint32_t v[32];
@@ -388,20 +478,17 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(MoeGemmArgs p)
             tmem_wait_ld();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&sh.d_empty[db]));
+            if (lane == 0) mbar_arrive(smem_u32(&bar.d_empty[db]));
             const float scale = __ldg(p.gs + e) * 67108864.0f;  // global scale * 2^26
             float* dst = p.outp + (static_cast<size_t>(ks) * P) * p.R + tile * 128 + row;
 #pragma unroll
-            for (int j = 0; j < kGroup; ++j) {
-                if (j < n) {
-                    const int pair = sh.list[off + j];
-                    float val = __uint_as_float(v[j]) * scale;
-                    if (MODE == 1 && p.x_ssq != nullptr) val *= sh.rs[pair / p.top_k];
-                    dst[static_cast<size_t>(pair) * p.R] = val;
-                }
+            for (int c = 0; c < kGroup; ++c) {
+                const int pr = __shfl_sync(0xffffffffu, mypair, c);
+                const float sc = __shfl_sync(0xffffffffu, myscale, c);
+                if (pr >= 0) dst[static_cast<size_t>(pr) * p.R] = __uint_as_float(v[c]) * scale * sc;
             }
         }
-    } else if (warp < 14) {
+    } else {
         // ------------------------------------------------ dequant: codes + scales -> BF16 A operand in TMEM
         const int quarter = warp & 3, grp = (warp - 6) >> 2, row = quarter * 32 + lane;
         int cc = 0;
@@ -409,12 +496,12 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(MoeGemmArgs p)
         for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
             for (int c = 0; c < nch; ++c, ++cc) {
                 if ((cc & 1) != grp) continue;
-                const int rs_ = cc % kNRaw, as = cc % kNA;
-                ok = mbar_wait(smem_u32(&sh.raw_full[rs_]), (cc / kNRaw) & 1, p.status, where | 7);
-                if (ok && cc >= kNA) ok = mbar_wait(smem_u32(&sh.a_empty[as]), ((cc / kNA) - 1) & 1, p.status, where | 8);
+                const int s = cc % kNRaw, as = cc % kNA;
+                ok = mbar_wait(smem_u32(&bar.raw_full[s]), (cc / kNRaw) & 1, p.status, where | 7);
+                if (ok && cc >= kNA) ok = mbar_wait(smem_u32(&bar.a_empty[as]), ((cc / kNA) - 1) & 1, p.status, where | 8);
                 if (!ok) break;
                 tc_fence_after();
-                const uint8_t* raw = gbase + rs_ * kBlob;
+                const uint8_t* raw = gbase + s * kStage;
                 const uint2 sc = *reinterpret_cast<const uint2*>(raw + kBlobScales + row * 8);
                 const uint32_t pairs[4] = {scale_pair(sc.x), scale_pair(sc.x >> 16), scale_pair(sc.y), scale_pair(sc.y >> 16)};
                 const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + as * 64;
@@ -425,58 +512,11 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(MoeGemmArgs p)
                     tmem_st16(taddr + q * 16, r);
                 }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&sh.raw_empty[rs_]));
+                if (lane == 0) mbar_arrive(smem_u32(&bar.raw_empty[s]));
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&sh.a_full[as]));
-            }
-        }
-    } else {
-        // ------------------------------------------------ B staging
-        const int st = tid - 14 * 32;
-        int cc = 0;
-        bool ok = true;
-        for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-            const int g = u / per_group, rem = u % per_group, ks = rem % p.S;
-            const int off = sh.g_off[g], n = sh.g_n[g];
-            for (int c = 0; c < nch; ++c, ++cc) {
-                const int bs = cc % kNB;
-                if (cc >= kNB) ok = mbar_wait(smem_u32(&sh.b_empty[bs]), ((cc / kNB) - 1) & 1, p.status, where | 9);
-                if (!ok) break;
-                const int k0 = (ks * nch + c) * 128;
-                uint8_t* slot = gbase + kNRaw * kBlob + bs * kBSlot;
-                for (int item = st; item < n * 16; item += 128) {
-                    const int j = item >> 4, pc = item & 15;
-                    const int pair = sh.list[off + j];
-                    uint4 v;
-                    if (MODE == 1) {
-                        v = __ldcg(reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(pair / p.top_k) * p.ldx + k0 + pc * 8));
-                    } else {
-                        float gte[8], up[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) gte[i] = 0.0f, up[i] = 0.0f;
-                        for (int s = 0; s < p.s_prev; ++s) {
-                            const float* hrow = p.hprev + (static_cast<size_t>(s) * P + pair) * (2 * p.inner) + k0 + pc * 8;
-                            const float4 a0 = __ldcg(reinterpret_cast<const float4*>(hrow));
-                            const float4 a1 = __ldcg(reinterpret_cast<const float4*>(hrow + 4));
-                            const float4 c0 = __ldcg(reinterpret_cast<const float4*>(hrow + p.inner));
-                            const float4 c1 = __ldcg(reinterpret_cast<const float4*>(hrow + p.inner + 4));
-                            gte[0] += a0.x, gte[1] += a0.y, gte[2] += a0.z, gte[3] += a0.w;
-                            gte[4] += a1.x, gte[5] += a1.y, gte[6] += a1.z, gte[7] += a1.w;
-                            up[0] += c0.x, up[1] += c0.y, up[2] += c0.z, up[3] += c0.w;
-                            up[4] += c1.x, up[5] += c1.y, up[6] += c1.z, up[7] += c1.w;
-                        }
-                        float o[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) o[i] = gte[i] / (1.0f + __expf(-gte[i])) * up[i];
-                        v = make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
-                    }
-                    *reinterpret_cast<uint4*>(slot + (pc >> 3) * 4096 + swz128(j, (pc & 7) * 16)) = v;
-                }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&sh.b_full[bs]));
+                if (lane == 0) mbar_arrive(smem_u32(&bar.a_full[as]));
             }
         }
     }
@@ -591,6 +631,22 @@ static int launch_pdl(Kern kern, dim3 grid, dim3 block, int smem, cudaStream_t s
     return cudaLaunchKernelEx(&cfg, kern, args) == cudaSuccess ? 0 : MSK_ERR_CUDA;
 }
 
+template <typename Kern, typename Args>
+static int launch_pdl2(Kern kern, dim3 grid, dim3 block, int smem, cudaStream_t stream, int pdl, const CUtensorMap& tm,
+                       const Args& args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, tm, args) == cudaSuccess ? 0 : MSK_ERR_CUDA;
+}
+
 }  // namespace msk
 
 extern "C" int msk_moe_packed_bytes(int E, int H, int I, size_t* w13_bytes, size_t* w2_bytes) {
@@ -622,30 +678,38 @@ extern "C" int msk_moe_dequant(const void* packed, void* out_bf16, int E, int R,
     return cudaGetLastError() == cudaSuccess ? 0 : MSK_ERR_CUDA;
 }
 
-extern "C" int msk_moe_scratch_bytes(int T, int top_k, int H, int I, int s1, int s2, size_t* h1_bytes, size_t* y_bytes) {
+extern "C" int msk_moe_scratch_bytes(int T, int top_k, int H, int I, int s1, int s2, size_t* h1_bytes, size_t* y_bytes,
+                                     size_t* inter_bytes, size_t* x_sorted_bytes, size_t* route_bytes) {
     if (T < 1 || top_k < 1 || s1 < 1 || s2 < 1) return MSK_ERR_INVALID;
-    if (h1_bytes) *h1_bytes = static_cast<size_t>(s1) * T * top_k * 2 * I * sizeof(float);
-    if (y_bytes) *y_bytes = static_cast<size_t>(s2) * T * top_k * H * sizeof(float);
+    const size_t P = static_cast<size_t>(T) * top_k;
+    if (h1_bytes) *h1_bytes = s1 * P * 2 * I * sizeof(float);
+    if (y_bytes) *y_bytes = s2 * P * H * sizeof(float);
+    if (inter_bytes) *inter_bytes = P * I * 2;
+    if (x_sorted_bytes) *x_sorted_bytes = T > msk::kGroup ? P * H * 2 : 0;
+    if (route_bytes) *route_bytes = (2 + P) * sizeof(int);
     return 0;
 }
 
 extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream) {
     using namespace msk;
     if (q == nullptr || !q->x || !q->w13_packed || !q->w2_packed || !q->w13_gs || !q->w2_gs || !q->post_norm_w ||
-        !q->h1_part || !q->y_part || !q->out || !q->topk_ids || !q->topk_weights)
+        !q->h1_part || !q->y_part || !q->inter_sorted || !q->route_pub || !q->out || !q->topk_ids || !q->topk_weights)
         return MSK_ERR_INVALID;
     const int P = q->T * q->top_k;
-    if (q->T < 1 || q->top_k < 1 || q->top_k > 8 || P > kMaxPairs || q->local_count < 1 || q->local_count > kMaxExperts || q->T > kMaxPairs / 8)
+    if (q->T < 1 || q->top_k < 1 || q->top_k > 8 || P > kMaxPairs || q->local_count < 1 || q->local_count > kMaxExperts ||
+        q->T > kMaxPairs / 8)
         return MSK_ERR_UNSUPPORTED;
-    if (q->H % 128 != 0 || q->I % 128 != 0 || q->H % 4 != 0 || q->ldx % 8 != 0) return MSK_ERR_UNSUPPORTED;
+    if (q->H % 128 != 0 || q->I % 128 != 0 || q->ldx % 8 != 0) return MSK_ERR_UNSUPPORTED;
     if (q->logits != nullptr && (q->n_logits > 256 || q->n_logits < q->top_k)) return MSK_ERR_UNSUPPORTED;
+    const int direct = q->T <= kGroup;
+    if (!direct && q->x_sorted == nullptr) return MSK_ERR_INVALID;
     const int s1 = q->s1 > 0 ? q->s1 : 1, s2 = q->s2 > 0 ? q->s2 : 1;
     if ((q->H / 128) % s1 != 0 || (q->I / 128) % s2 != 0) return MSK_ERR_INVALID;
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) != cudaSuccess) return MSK_ERR_CUDA;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int smem = 1024 + kNRaw * kBlob + kNB * kBSlot;
+    const int smem = 1024 + kNRaw * kStage;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(moe_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
@@ -653,25 +717,53 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
             return MSK_ERR_CUDA;
         configured = true;
     }
+    RouteArgs ra{};
+    ra.ids = q->topk_ids, ra.logits = q->logits, ra.n_logits = q->n_logits;
+    ra.ld_logits = q->ld_logits > 0 ? q->ld_logits : q->n_logits;
+    ra.ids_out = q->topk_ids, ra.wts_out = q->topk_weights;
+    ra.T = q->T, ra.top_k = q->top_k, ra.local_start = q->local_start, ra.local_count = q->local_count;
+
+    // B operands by TMA: gemm 1 reads x itself (<= 32 tokens) or its rows gathered in expert-list order;
+    // gemm 2 reads the activations the act kernel writes in that same order.  Box = 32 rows x 64 k.
+    CUtensorMap tm_b1, tm_b2;
+    int rc = direct ? make_tmap_bf16_2d(&tm_b1, q->x, q->T, q->H, q->ldx, kGroup)
+                    : make_tmap_bf16_2d(&tm_b1, q->x_sorted, P, q->H, q->H, kGroup);
+    if (rc == 0) rc = make_tmap_bf16_2d(&tm_b2, q->inter_sorted, P, q->I, q->I, kGroup);
+    if (rc != 0) return rc;
+
+    int pdl = q->pdl;
+    if (!direct) {
+        MoeGatherArgs g{};
+        g.route = ra, g.x = static_cast<const __nv_bfloat16*>(q->x), g.ldx = q->ldx, g.H = q->H;
+        g.x_sorted = static_cast<__nv_bfloat16*>(q->x_sorted), g.status = status;
+        rc = launch_pdl(moe_gather_kernel, dim3(sms), dim3(kRouteThreads), 0, s, pdl, g);
+        if (rc != 0) return rc;
+        pdl = 1;
+    }
     MoeGemmArgs a{};
-    a.ids = q->topk_ids, a.wts = q->topk_weights, a.logits = q->logits, a.n_logits = q->n_logits;
-    a.ids_out = const_cast<int*>(q->topk_ids), a.wts_out = const_cast<float*>(q->topk_weights);
-    a.T = q->T, a.top_k = q->top_k, a.local_start = q->local_start, a.local_count = q->local_count;
-    a.wpacked = static_cast<const uint8_t*>(q->w13_packed), a.gs = q->w13_gs, a.R = 2 * q->I, a.K = q->H;
-    a.x = static_cast<const __nv_bfloat16*>(q->x), a.ldx = q->ldx;
+    a.route = ra;
+    a.wpacked = static_cast<const uint8_t*>(q->w13_packed), a.gs = q->w13_gs, a.R = 2 * q->I, a.K = q->H, a.direct = direct;
     a.x_ssq = q->x_ssq, a.x_ssq_parts = q->x_ssq_parts, a.x_inv_dim = q->x_inv_dim, a.x_eps = q->x_eps;
     a.x_ssq_ts = q->x_ssq_tstride > 0 ? q->x_ssq_tstride : 1;
-    a.ld_logits = q->ld_logits > 0 ? q->ld_logits : q->n_logits;
-    a.outp = q->h1_part, a.S = s1, a.status = status;
-    int rc = launch_pdl(moe_gemm_kernel<1>, dim3(sms), dim3(kMoeThreads), smem, s, q->pdl, a);
+    a.route_pub = q->route_pub, a.outp = q->h1_part, a.S = s1, a.status = status;
+    rc = launch_pdl2(moe_gemm_kernel<1>, dim3(sms), dim3(kMoeThreads), smem, s, pdl, tm_b1, a);
     if (rc != 0) return rc;
+
+    MoeActArgs act{};
+    act.route_pub = q->route_pub, act.h1 = q->h1_part, act.s1 = s1, act.P = P, act.inner = q->I;
+    act.inter = static_cast<__nv_bfloat16*>(q->inter_sorted);
+    rc = launch_pdl(moe_act_kernel, dim3(P < 2 * sms ? P : 2 * sms), dim3(256), 0, s, 1, act);
+    if (rc != 0) return rc;
+
     MoeGemmArgs b{};
-    b.ids = q->topk_ids, b.wts = q->topk_weights, b.T = q->T, b.top_k = q->top_k;
-    b.local_start = q->local_start, b.local_count = q->local_count;
-    b.wpacked = static_cast<const uint8_t*>(q->w2_packed), b.gs = q->w2_gs, b.R = q->H, b.K = q->I;
-    b.hprev = q->h1_part, b.s_prev = s1, b.inner = q->I, b.outp = q->y_part, b.S = s2, b.status = status;
-    rc = launch_pdl(moe_gemm_kernel<2>, dim3(sms), dim3(kMoeThreads), smem, s, 1, b);
+    b.route = ra;
+    b.route.logits = nullptr;  // gemm 1 has published the ids
+    b.route.ids_out = nullptr, b.route.wts_out = nullptr;
+    b.wpacked = static_cast<const uint8_t*>(q->w2_packed), b.gs = q->w2_gs, b.R = q->H, b.K = q->I, b.direct = 0;
+    b.outp = q->y_part, b.S = s2, b.status = status;
+    rc = launch_pdl2(moe_gemm_kernel<2>, dim3(sms), dim3(kMoeThreads), smem, s, 1, tm_b2, b);
     if (rc != 0) return rc;
+
     MoeCombineArgs c{};
     c.ids = q->topk_ids, c.wts = q->topk_weights, c.top_k = q->top_k, c.local_start = q->local_start;
     c.local_count = q->local_count, c.H = q->H, c.S = s2, c.P = P, c.yp = q->y_part;
@@ -685,10 +777,11 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
 // Some hosts cannot hand this library scratch memory and cannot let it allocate either: an inference
 // server whose memory pool claimed the whole device at start-up (any later cudaMalloc fails or fragments
 // its arena), or a step that is already inside a latency-critical loop where an allocation would
-// synchronise the device.  For them the two FP32 partial buffers of msk_moe_forward live in the array
+// synchronise the device.  For them all the scratch of msk_moe_forward (the FP32 partials, the activations between the GEMMs,
+// the routing list) lives in the array
 // below, which every GPU that loads the library holds until the process exits.
-// Limit: s1 * T * top_k * 2I + s2 * T * top_k * H <= kStaticScratchFloats (4 MiB), e.g. 8 tokens at the
-// benchmark's expert shapes with s1 = 4, s2 = 2.
+// Limit: everything msk_moe_scratch_bytes reports for the call, each part rounded up to 256 bytes, must fit
+// in 4 MiB (e.g. 8 tokens at the benchmark's expert shapes with s1 = 4, s2 = 2).
 constexpr size_t kStaticScratchFloats = 1u << 20;
 static __device__ __align__(256) float g_moe_static_scratch[kStaticScratchFloats];
 
@@ -701,9 +794,16 @@ extern "C" int msk_moe_forward_static(const MskMoeParams* q, int* status, void* 
     if (q == nullptr) return MSK_ERR_INVALID;
     const size_t s1 = q->s1 > 0 ? q->s1 : 1, s2 = q->s2 > 0 ? q->s2 : 1;
     if (q->T < 1 || q->top_k < 1 || q->H < 1 || q->I < 1) return MSK_ERR_INVALID;
-    const size_t pairs = static_cast<size_t>(q->T) * q->top_k;
-    const size_t h1_floats = s1 * pairs * 2 * q->I, y_floats = s2 * pairs * q->H;
-    if (h1_floats + y_floats > kStaticScratchFloats) return MSK_ERR_UNSUPPORTED;  // beyond the built-in scratch
+    size_t part[5];
+    if (msk_moe_scratch_bytes(q->T, q->top_k, q->H, q->I, static_cast<int>(s1), static_cast<int>(s2), &part[0], &part[1], &part[2],
+                              &part[3], &part[4]) != 0)
+        return MSK_ERR_INVALID;
+    size_t off[5], total = 0;
+    for (int i = 0; i < 5; ++i) {
+        off[i] = total;
+        total += (part[i] + 255) / 256 * 256;
+    }
+    if (total > kStaticScratchFloats * sizeof(float)) return MSK_ERR_UNSUPPORTED;  // beyond the built-in scratch
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return MSK_ERR_CUDA;
     if (g_static_scratch_ptr[dev] == nullptr) {
@@ -715,7 +815,11 @@ extern "C" int msk_moe_forward_static(const MskMoeParams* q, int* status, void* 
         g_static_scratch_ptr[dev] = p;
     }
     MskMoeParams m = *q;
-    m.h1_part = g_static_scratch_ptr[dev];
-    m.y_part = g_static_scratch_ptr[dev] + h1_floats;
+    char* basep = reinterpret_cast<char*>(g_static_scratch_ptr[dev]);
+    m.h1_part = reinterpret_cast<float*>(basep + off[0]);
+    m.y_part = reinterpret_cast<float*>(basep + off[1]);
+    m.inter_sorted = basep + off[2];
+    m.x_sorted = part[3] ? basep + off[3] : nullptr;
+    m.route_pub = reinterpret_cast<int32_t*>(basep + off[4]);
     return msk_moe_forward(&m, status, stream);
 }

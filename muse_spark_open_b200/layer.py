@@ -50,8 +50,8 @@ def buffers(state: dict, t: int, device) -> dict:
         state["bufs"][t] = {
             "xn0": mk((t, h), bf), "ssq0": mk((t,), f32), "qkv": mk((t, nqkv), bf), "attn": mk((t, no), bf),
             "stream1": mk((t, h), f32), "xn1": mk((t, h), bf), "ssq1": mk((h // 128, t), f32),
-            "router_part": mk((h // 64, t, e), f32),
-            "router_ticket": torch.zeros(((t + 31) // 32,), dtype=torch.int32, device=device),
+            "router_part": mk((8, t, e), f32),
+            "router_ticket": torch.zeros((((t + 31) // 32) * ((e + 31) // 32),), dtype=torch.int32, device=device),
             "logits": mk((t, e), f32), "topk_w": mk((t, TOP_K), f32),
         }
     return state["bufs"][t]
@@ -98,7 +98,7 @@ def kernel_fn(data: dict, state: dict, **tune):
     buf = buffers(state, t, stream.device)
     ms = state["moe"]
     s1, s2 = tune.get("moe_splits") or moe.splits_for(t, ms["H"], ms["I"])
-    h1, y = moe.scratch(ms, t, TOP_K, s1, s2, stream.device)
+    h1, y, inter, xs, pub = moe.scratch(ms, t, TOP_K, s1, s2, stream.device)
     hidden = torch.empty((t, h), dtype=torch.bfloat16, device=stream.device)
     out = torch.empty((t, h), dtype=torch.float32, device=stream.device)
     ids = torch.empty((t, TOP_K), dtype=torch.int32, device=stream.device)
@@ -111,6 +111,7 @@ def kernel_fn(data: dict, state: dict, **tune):
     m.w13_gs, m.w2_gs = abi.ptr(ms["w13_gs"]), abi.ptr(ms["w2_gs"])
     m.post_norm_w, m.post_eps, m.I = abi.ptr(ms["post_w"]), moe.POST_NORM_EPS, ms["I"]
     m.h1_part, m.y_part, m.s1, m.s2 = abi.ptr(h1), abi.ptr(y), s1, s2
+    m.inter_sorted, m.x_sorted, m.route_pub = abi.ptr(inter), abi.ptr(xs), abi.ptr(pub)
     m.out, m.out_fp32, m.ldo = abi.ptr(out), 1, h
     m.out_copy, m.ldc = abi.ptr(hidden), h
     st = abi.status_for(stream.device)

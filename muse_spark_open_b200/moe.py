@@ -53,12 +53,16 @@ def prepare(weights: dict, weights_start: int = 0) -> dict:
 
 
 def scratch(state: dict, tokens: int, top_k: int, s1: int, s2: int, device):
-    """The two FP32 partial buffers, kept per (tokens, splits) in `state` (allocated once, outside timing)."""
+    """The scratch buffers (FP32 partials, activations, gathered inputs, routing list), kept per (tokens, splits) in `state` (allocated once, outside timing)."""
     key = (tokens, top_k, s1, s2)
     if key not in state["scratch"]:
-        h1 = torch.empty((s1, tokens * top_k, 2 * state["I"]), dtype=torch.float32, device=device)
-        y = torch.empty((s2, tokens * top_k, state["H"]), dtype=torch.float32, device=device)
-        state["scratch"][key] = (h1, y)
+        pairs = tokens * top_k
+        h1 = torch.empty((s1, pairs, 2 * state["I"]), dtype=torch.float32, device=device)
+        y = torch.empty((s2, pairs, state["H"]), dtype=torch.float32, device=device)
+        inter = torch.empty((pairs, state["I"]), dtype=torch.bfloat16, device=device)
+        xs = torch.empty((pairs, state["H"]), dtype=torch.bfloat16, device=device) if tokens > 32 else None
+        pub = torch.zeros((2 + pairs,), dtype=torch.int32, device=device)
+        state["scratch"][key] = (h1, y, inter, xs, pub)
     return state["scratch"][key]
 
 
@@ -69,7 +73,7 @@ def forward(x, ids, wts, state, local_start, local_count, out=None, logits=None,
     if t > MAX_TOKENS:
         raise abi.MskError(f"experts built for decode/verify steps of up to {MAX_TOKENS} tokens, got {t}")
     s1, s2 = splits or splits_for(t, state["H"], state["I"])
-    h1, y = scratch(state, t, top_k, s1, s2, x.device)
+    h1, y, inter, xs, pub = scratch(state, t, top_k, s1, s2, x.device)
     if out is None:
         out = torch.empty((t, h), dtype=torch.bfloat16, device=x.device)
     p = abi.MoeParams()
@@ -92,6 +96,7 @@ def forward(x, ids, wts, state, local_start, local_count, out=None, logits=None,
     p.w13_gs, p.w2_gs = state["w13_gs"].data_ptr() + 4 * first, state["w2_gs"].data_ptr() + 4 * first
     p.post_norm_w, p.post_eps, p.H, p.I = abi.ptr(state["post_w"]), POST_NORM_EPS, state["H"], state["I"]
     p.h1_part, p.y_part, p.s1, p.s2 = abi.ptr(h1), abi.ptr(y), s1, s2
+    p.inter_sorted, p.x_sorted, p.route_pub = abi.ptr(inter), abi.ptr(xs), abi.ptr(pub)
     if resid is not None:
         p.resid, p.ldr = abi.ptr(resid), resid.stride(0)
     p.out, p.out_fp32, p.ldo, p.pdl = abi.ptr(out), int(out.dtype == torch.float32), out.stride(0), int(pdl)
@@ -127,7 +132,7 @@ def forward_no_alloc(x, ids, wts, state, local_start, local_count, out, splits=N
     t, h = x.shape
     top_k = ids.shape[1]
     s1, s2 = splits or splits_for(t, state["H"], state["I"])
-    if s1 * t * top_k * 2 * state["I"] + s2 * t * top_k * state["H"] > STATIC_SCRATCH_FLOATS:
+    if 4 * (s1 * t * top_k * 2 * state["I"] + s2 * t * top_k * state["H"]) + 2 * t * top_k * state["I"] + 4096 > 4 * STATIC_SCRATCH_FLOATS:
         raise abi.MskError("this step needs more scratch than the library's built-in 4 MiB: use forward()")
     p = abi.MoeParams()
     p.x, p.ldx = abi.ptr(x), x.stride(0)
