@@ -10,21 +10,22 @@
 // pair lists and walks the work units (expert-group of <= 32 pairs, 128-row tile, K split) that fall
 // to it, so every touched expert's weights stream through the SMs once.
 //
-// One persistent CTA per SM, 14 warps:
+// One persistent CTA per SM, 17 warps:
 //   warp 0        producer: per 128x128 weight block one untiled bulk copy (TMA) of 8 KB of bit-permuted
 //                 E2M1 codes + 1 KB of E4M3 block scales (repacked at prepare time: one contiguous
 //                 9216-byte read, each thread's 16 bytes at a conflict-free slot), and two TMA boxes of the
 //                 B operand (32 rows x 64 k, 128-byte swizzle) into the same ring stage: x itself when the
 //                 step has at most 32 tokens (column = token), else x gathered in expert-list order by a
 //                 small kernel; for gemm 2 the activations the act kernel wrote in that order.
-//   warps 6..13   dequant: thread = weight row.  8 codes per word become 4 BF16x2 registers with 3
+//   warps 9..16   dequant: thread = weight row.  8 codes per word become 4 BF16x2 registers with 3
 //                 shift+mask steps (the permutation puts every code's bits where BF16 wants them,
 //                 magnitudes as BF16 subnormals * 2^-126), times the block scale (E4M3 * 2^100 as BF16)
 //                 with one HMUL2 each: exact E2M1 x E4M3 products * 2^-26, written straight into tensor
 //                 memory (tcgen05.st) as the A operand.  No BF16 round trip through shared memory.
-//   warp 1        one lane issues tcgen05.mma kind::f16, A from TMEM, B from shared memory, FP32
-//                 accumulators in TMEM (double-buffered per unit).
-//   warps 2..5    epilogue: tcgen05.ld, times global scale * 2^26 (and the folded pre-expert RMSNorm row
+//   warps 1..4    one lane each issues tcgen05.mma kind::f16, A from TMEM, B from shared memory.  One thread
+//                 can issue only about one MMA per 100 clocks whatever N is, so four warps issue in parallel,
+//                 each into its own FP32 accumulator in TMEM (double-buffered per unit).
+//   warps 5..8    epilogue: adds the four accumulators, tcgen05.ld, times global scale * 2^26 (and the folded pre-expert RMSNorm row
 //                 scale), plain stores into this K split's FP32 partial buffer.  K splits are summed in a
 //                 fixed order by the consumer, so results are bitwise reproducible and no buffer has to
 //                 be zeroed between calls.
@@ -47,7 +48,8 @@ constexpr int kGroup = 32;         // pairs per expert-group (UMMA N)
 constexpr int kMaxPairs = 2048;
 constexpr int kMaxExperts = 256;
 constexpr int kMaxGroups = 320;
-constexpr int kMoeThreads = 14 * 32;
+constexpr int kIssuers = 4;         // MMA-issuing warps (one lane each); a single thread issues one tcgen05.mma per ~100 clk
+constexpr int kMoeThreads = 17 * 32;
 constexpr int kRouteThreads = kMoeThreads, kRouteWarps = kRouteThreads / 32;
 
 // ---------------------------------------------------------------- weight repacking (prepare time)
@@ -369,7 +371,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
         // the MMAs that read the B tile have completed
         for (int i = 0; i < kNRaw; ++i) mbar_init(smem_u32(&bar.raw_full[i]), 1), mbar_init(smem_u32(&bar.raw_empty[i]), 5);
         for (int i = 0; i < kNA; ++i) mbar_init(smem_u32(&bar.a_full[i]), 4), mbar_init(smem_u32(&bar.a_empty[i]), 1);
-        for (int i = 0; i < 2; ++i) mbar_init(smem_u32(&bar.d_full[i]), 1), mbar_init(smem_u32(&bar.d_empty[i]), 4);
+        for (int i = 0; i < 2; ++i) mbar_init(smem_u32(&bar.d_full[i]), kIssuers), mbar_init(smem_u32(&bar.d_empty[i]), 4);
         fence_mbar_init();
     }
     if (tid == 0) prefetch_tmap(&tm_b);
@@ -420,21 +422,26 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
-        // ------------------------------------------------ MMA issue
+    } else if (warp <= kIssuers) {
+        // ------------------------------------------------ MMA issue: warp w + 1 owns A slot w, i.e. the chunks
+        // with running index = w (mod 4), and its own accumulator; the epilogue adds the four.
         if (lane == 0) {
+            const int w = warp - 1;
             const uint32_t idesc = umma_idesc(128, kGroup, 1, 1, 0, 0);
             int cc = 0, uc = 0;
             bool ok = true;
             for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++uc) {
                 const int db = uc & 1;
                 if (uc >= 2) ok = mbar_wait(smem_u32(&bar.d_empty[db]), ((uc >> 1) - 1) & 1, p.status, where | 3);
+                if (!ok) break;
                 tc_fence_after();
-                const uint32_t d = tmem + kNA * 64 + db * kGroup;
+                const uint32_t d = tmem + kNA * 64 + (db * kIssuers + w) * kGroup;
+                bool first = true;
                 for (int c = 0; c < nch && ok; ++c, ++cc) {
-                    const int as = cc % kNA, s = cc % kNRaw;
+                    if ((cc & 3) != w) continue;
+                    const int s = cc % kNRaw;
                     ok = mbar_wait(smem_u32(&bar.raw_full[s]), (cc / kNRaw) & 1, p.status, where | 5) &&
-                         mbar_wait(smem_u32(&bar.a_full[as]), (cc / kNA) & 1, p.status, where | 4);
+                         mbar_wait(smem_u32(&bar.a_full[w]), (cc / kNA) & 1, p.status, where | 4);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t bb = base + s * kStage + kBlob;
@@ -442,20 +449,23 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
                     const uint64_t b1 = umma_smem_desc(bb + 4096, 16, 1024, kSwizzle128);
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
-                        umma_f16_ts(d, tmem + as * 64 + 8 * j, (j < 4 ? b0 : b1) + 2 * (j & 3), idesc, (c | j) != 0);
-                    umma_commit(smem_u32(&bar.a_empty[as]));
+                        umma_f16_ts(d, tmem + w * 64 + 8 * j, (j < 4 ? b0 : b1) + 2 * (j & 3), idesc, !(first && j == 0));
+                    first = false;
+                    umma_commit(smem_u32(&bar.a_empty[w]));
                     umma_commit(smem_u32(&bar.raw_empty[s]));
                 }
-                if (ok) umma_commit(smem_u32(&bar.d_full[db]));
+                if (!ok) break;
+                if (first) mbar_arrive(smem_u32(&bar.d_full[db]));  // no chunk of this unit fell to this warp
+                else umma_commit(smem_u32(&bar.d_full[db]));
             }
         }
         __syncwarp();
-    } else if (warp < 6) {
+    } else if (warp < kIssuers + 5) {
         // ------------------------------------------------ epilogue
         const int quarter = warp & 3, row = quarter * 32 + lane;
-        int uc = 0;
+        int uc = 0, cc0 = 0;
         bool ok = true;
-        for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++uc) {
+        for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++uc, cc0 += nch) {
             const int g = u / per_group, rem = u % per_group, tile = rem / p.S, ks = rem % p.S;
             const int db = uc & 1, e = rt.g_expert[g], off = rt.g_off[g], n = rt.g_n[g];
             // the pair whose result sits in accumulator column `lane`
@@ -471,11 +481,20 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
             ok = mbar_wait(smem_u32(&bar.d_full[db]), (uc >> 1) & 1, p.status, where | 6);
             if (!ok) break;
             tc_fence_after();
-            uint32_t v[32];
-            const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + kNA * 64 + db * kGroup;
-            tmem_ld16(taddr, *reinterpret_cast<uint32_t(*)[16]>(&v[0]));
-            tmem_ld16(taddr + 16, *reinterpret_cast<uint32_t(*)[16]>(&v[16]));
-            tmem_wait_ld();
+            float v[32];
+#pragma unroll
+            for (int c = 0; c < 32; ++c) v[c] = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kIssuers; ++w) {
+                if (nch < 4 && ((w - cc0) & 3) >= nch) continue;  // that warp had no chunk of this unit
+                uint32_t t[32];
+                const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + kNA * 64 + (db * kIssuers + w) * kGroup;
+                tmem_ld16(taddr, *reinterpret_cast<uint32_t(*)[16]>(&t[0]));
+                tmem_ld16(taddr + 16, *reinterpret_cast<uint32_t(*)[16]>(&t[16]));
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 32; ++c) v[c] += __uint_as_float(t[c]);
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bar.d_empty[db]));
@@ -485,12 +504,12 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
             for (int c = 0; c < kGroup; ++c) {
                 const int pr = __shfl_sync(0xffffffffu, mypair, c);
                 const float sc = __shfl_sync(0xffffffffu, myscale, c);
-                if (pr >= 0) dst[static_cast<size_t>(pr) * p.R] = __uint_as_float(v[c]) * scale * sc;
+                if (pr >= 0) dst[static_cast<size_t>(pr) * p.R] = v[c] * scale * sc;
             }
         }
     } else {
         // ------------------------------------------------ dequant: codes + scales -> BF16 A operand in TMEM
-        const int quarter = warp & 3, grp = (warp - 6) >> 2, row = quarter * 32 + lane;
+        const int quarter = warp & 3, grp = (warp - (kIssuers + 5)) >> 2, row = quarter * 32 + lane;
         int cc = 0;
         bool ok = true;
         for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
