@@ -69,6 +69,10 @@ typedef struct {
 
 int msk_proj_skinny(const MskProjParams* p, int* status, void* stream);
 
+/* Tuning aid (no reference counterpart): clusters of `splits` CTAs with `smem_bytes` of dynamic shared
+ * memory that fit on the device at once. */
+int msk_proj_max_active_clusters(int splits, int smem_bytes);
+
 /* ---------------------------------------------------------------- gated attention decode / verify
  * One decode step (L = 1) or one 8-token verify block (L = 8, causal inside the block) of gated
  * attention over a paged FP8-E4M3 KV cache: per-head RMSNorm of q and k, q * qk_scale_factor,

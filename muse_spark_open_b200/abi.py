@@ -53,6 +53,7 @@ def lib() -> C.CDLL:
         _lib.msk_device_info.argtypes = [vp, vp]
         _lib.msk_selftest_umma.argtypes = [ci, vp, vp, vp, ci, vp, vp]
         _lib.msk_proj_skinny.argtypes = [vp, vp, vp]
+        _lib.msk_proj_max_active_clusters.argtypes = [ci, ci]
         _lib.msk_attn_decode.argtypes = [vp, vp, vp]
         _lib.msk_moe_packed_bytes.argtypes = [ci, ci, ci, vp, vp]
         _lib.msk_moe_pack.argtypes = [vp, vp, vp, vp]
@@ -69,7 +70,7 @@ def lib() -> C.CDLL:
 
 
 # every symbol include/msk.h declares
-EXPORTS = ["msk_version", "msk_device_info", "msk_selftest_umma", "msk_proj_skinny", "msk_attn_decode",
+EXPORTS = ["msk_version", "msk_device_info", "msk_selftest_umma", "msk_proj_skinny", "msk_proj_max_active_clusters", "msk_attn_decode",
            "msk_moe_packed_bytes", "msk_moe_pack", "msk_moe_dequant", "msk_moe_scratch_bytes", "msk_moe_forward", "msk_moe_forward_static", "msk_layer_front", "msk_layer_decode",
            "msk_ep_row_bytes", "msk_ep_pack", "msk_ep_reduce"]
 

@@ -10,10 +10,13 @@
 //            N = 8 L query rows (row = 8 * token + head-in-group), K = head_dim 128.
 //            The FP8 cache bytes are the A operand as they are (exact, no conversion); the query,
 //            rounded to BF16 like the reference, is split into two E4M3 terms q = hi + lo
-//            (two accumulating passes), which keeps BF16-level precision on FP8 tensor cores.
+//            stacked as 2 x 8 L rows of one B tile (the second term times 16, its columns are scaled back when
+//            read), which keeps BF16-level precision on FP8 tensor cores with a single pass over K.
 //   softmax  thread = key: tcgen05.ld its row of S^T, scale, window / causal mask, running maximum
 //            per query row (redux.sync over the warp, shared memory over the 4 warps), p = 2^(s-m)
-//            split into an E4M3 and an E5M2 term, written as the K-major B operand P[row, key].
+//            split into two E4M3 terms the same way, written as the K-major B operand P[row, key].
+//            A single thread can issue only about one tcgen05.mma per 100 clocks whatever N is, so 4 (decode)
+//            or 2 (verify) warps issue, each into its own accumulator columns, summed when read.
 //   MMA 2    O^T[d, row] = V^T[d, key] . P[row, key]; V stays as stored (MN-major A operand).
 //   acc      thread = d: o[row] = o[row] * alpha[row] + O^T[d, row]  (FP32 registers).
 // The L new tokens never travel through global memory: the last CTA of the cluster applies
@@ -105,15 +108,20 @@ template <int L>
 __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUtensorMap tm_k,
                                                    const __grid_constant__ CUtensorMap tm_v, AttnArgs p) {
     constexpr int NR = 8 * L;                 // query rows per KV head
-    constexpr int NP = NR < 16 ? 16 : NR;     // UMMA N
-    constexpr uint32_t kCols = NP <= 16 ? 64 : 256;  // S0 | S1 | O, NP columns each
+    constexpr int NP = 2 * NR;                // UMMA N: rows [0, NR) hold the first split term, [NR, 2 NR) the second
+    constexpr int ISS = L == 1 ? 4 : 2;       // MMA-issuing warps (one thread issues only ~1 MMA per 100 clocks)
+    constexpr int SBUF = L == 1 ? 2 : 1;      // score buffers in TMEM (2: the next tile's scores are computed ahead)
+    constexpr uint32_t kCols = L == 1 ? 256 : 512;  // SBUF * ISS * NP score columns, then ISS * NP output columns
+    constexpr uint32_t kOCol = SBUF * ISS * NP;
     constexpr int QP_BYTES = NP * 128;
+    constexpr float kLoScale = 16.0f;         // the second split term is stored times 16 (keeps small residuals in range)
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bars[kAttnMaxStages + 3];
     __shared__ uint32_t tmem_slot;
     __shared__ int page_ids[kMaxTilesPerCta * 2];
-    __shared__ float m_s[NR], alpha_s[NR], wred[4][NR], mrg_m[NR], mrg_l[NR];
+    __shared__ __align__(16) float wred[4][NR];  // per-warp maxima of the current tile
+    __shared__ float m_s[NR], alpha_s[NR], mrg_m[NR], mrg_l[NR];
     __shared__ float sc_tail[NR][L];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -122,10 +130,10 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
     const int nst = p.nstages;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t s_qhi = base + nst * kStageBytes, s_qlo = s_qhi + QP_BYTES, s_phi = s_qlo + QP_BYTES,
-                   s_plo = s_phi + QP_BYTES, s_mrg = s_plo + QP_BYTES;
-    uint8_t* g_qhi = gbase + nst * kStageBytes;
-    float* mrg_o = reinterpret_cast<float*>(g_qhi + 4 * QP_BYTES);  // [NR][128]
+    const uint32_t s_q = base + nst * kStageBytes, s_p = s_q + QP_BYTES, s_mrg = s_p + QP_BYTES;
+    uint8_t* g_q = gbase + nst * kStageBytes;
+    uint8_t* g_p = g_q + QP_BYTES;
+    float* mrg_o = reinterpret_cast<float*>(g_q + 2 * QP_BYTES);  // [NR][128]
     auto full = [&](int s) { return smem_u32(&bars[s]); };
     const uint32_t bar_s0 = smem_u32(&bars[kAttnMaxStages]), bar_s1 = smem_u32(&bars[kAttnMaxStages + 1]),
                    bar_o = smem_u32(&bars[kAttnMaxStages + 2]);
@@ -137,9 +145,9 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
     }
     if (tid == 32) {
         for (int s = 0; s < nst; ++s) mbar_init(full(s), 1);
-        mbar_init(bar_s0, 1);
-        mbar_init(bar_s1, 1);
-        mbar_init(bar_o, 1);
+        mbar_init(bar_s0, ISS);
+        mbar_init(bar_s1, ISS);
+        mbar_init(bar_o, ISS);
         fence_mbar_init();
     }
     const int seq = p.seq_lens[b];
@@ -165,7 +173,7 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
         }
         page_ids[i] = id;
     }
-    for (int i = tid; i < 4 * QP_BYTES / 16; i += 128) reinterpret_cast<uint4*>(g_qhi)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < 2 * QP_BYTES / 16; i += 128) reinterpret_cast<uint4*>(g_q)[i] = make_uint4(0, 0, 0, 0);
     if (tid < NR) m_s[tid] = kNeg;
     tc_fence_before();
     __syncthreads();
@@ -183,18 +191,27 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
             tma_load_4d(vb + j * p.page_size * 128, &tm_v, full(s), 0, h, 0, id);
         }
     };
-    auto issue_mma1 = [&](int i) {  // thread 0: S^T = K . (q_hi + q_lo)^T into S buffer i & 1
+    const bool issuer = lane == 0 && warp < ISS;
+    auto sbar = [&](int i) { return (SBUF == 2 && (i & 1)) ? bar_s1 : bar_s0; };
+    auto issue_mma1 = [&](int i) {  // issuing warp w: S_w^T = K[:, its k-steps] . q^T, score buffer i % SBUF
         const uint32_t kb = base + (i % nst) * kStageBytes;
         const uint32_t idesc = umma_idesc(128, NP, 0, 0, 0, 0);
         const uint64_t ad = umma_smem_desc(kb, 16, 1024, kSwizzle128);
-        const uint64_t bh = umma_smem_desc(s_qhi, 16, 1024, kSwizzle128);
-        const uint64_t bl = umma_smem_desc(s_qlo, 16, 1024, kSwizzle128);
-        const uint32_t d = tmem + (i & 1) * NP;
+        const uint64_t bq = umma_smem_desc(s_q, 16, 1024, kSwizzle128);
+        const uint32_t d = tmem + ((i % SBUF) * ISS + warp) * NP;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) umma_f8_ss(d, ad + 2 * k, bh + 2 * k, idesc, k != 0);
+        for (int k = warp; k < 4; k += ISS) umma_f8_ss(d, ad + 2 * k, bq + 2 * k, idesc, k != warp);
+        umma_commit(sbar(i));
+    };
+    auto issue_mma2 = [&](int i) {  // issuing warp w: O_w^T = V^T[:, its 32-key steps] . P^T
+        const uint32_t vb = base + (i % nst) * kStageBytes + kTileKeys * 128;
+        const uint32_t idesc = umma_idesc(128, NP, 0, 0, 1, 0);
+        const uint64_t bp = umma_smem_desc(s_p, 16, 1024, kSwizzle128);
+        const uint32_t d = tmem + kOCol + warp * NP;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) umma_f8_ss(d, ad + 2 * k, bl + 2 * k, idesc, 1);
-        umma_commit((i & 1) ? bar_s1 : bar_s0);
+        for (int k = warp; k < 4; k += ISS)
+            umma_f8_ss(d, umma_smem_desc(vb + 4096 * k, 1024, 1024, kSwizzle128), bp + 2 * k, idesc, k != warp);
+        umma_commit(bar_o);
     };
 
     if (tid == 0) {
@@ -219,12 +236,12 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
         for (int i = 0; i < 4; ++i) {
             const float q = __bfloat162float(__float2bfloat16(x[i])) * qs;
             const uint32_t bh = f_to_e4m3(q);
-            const uint32_t bl = f_to_e4m3(q - e4m3_to_f(bh));
+            const uint32_t bl = f_to_e4m3((q - e4m3_to_f(bh)) * kLoScale);
             hi |= bh << (8 * i);
             lo |= bl << (8 * i);
         }
-        *reinterpret_cast<uint32_t*>(g_qhi + swz128(n, 4 * lane)) = hi;
-        *reinterpret_cast<uint32_t*>(g_qhi + QP_BYTES + swz128(n, 4 * lane)) = lo;
+        *reinterpret_cast<uint32_t*>(g_q + swz128(n, 4 * lane)) = hi;
+        *reinterpret_cast<uint32_t*>(g_q + swz128(NR + n, 4 * lane)) = lo;
     }
     fence_proxy_async_smem();
     __syncthreads();
@@ -236,7 +253,29 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
     const float s_scale = k_scale * p.sm_scale * 1.4426950408889634f / qs;
     const uint32_t trow = tmem + (static_cast<uint32_t>(warp * 32) << 16);
     bool ok = true;
+    // decode keeps the running maxima and the rescale factors replicated in every thread's registers
+    float m_r[L == 1 ? 8 : 1], alpha_r[L == 1 ? 8 : 1];
+#pragma unroll
+    for (int g = 0; g < (L == 1 ? 8 : 1); ++g) m_r[g] = kNeg, alpha_r[g] = 1.0f;
 
+    // scores of 8 query rows (c0 .. c0+7) for this thread's key: both split terms, all issuing warps' partials
+    auto load_scores = [&](int i, int c0, float (&sc)[8]) {
+        uint32_t hi[ISS][8], lo[ISS][8];
+#pragma unroll
+        for (int w = 0; w < ISS; ++w) {
+            const uint32_t col = trow + ((i % SBUF) * ISS + w) * NP + c0;
+            tmem_ld8(col, hi[w]);
+            tmem_ld8(col + NR, lo[w]);
+        }
+        tmem_wait_ld();
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            float a = 0.0f, b = 0.0f;
+#pragma unroll
+            for (int w = 0; w < ISS; ++w) a += __uint_as_float(hi[w][g]), b += __uint_as_float(lo[w][g]);
+            sc[g] = a + b * (1.0f / kLoScale);
+        }
+    };
     // second half of a tile's work: wait for O^T = V^T . P^T, fold it into the running output, refill the ring
     // slot.  It runs one iteration late (after the next tile's maxima), so the MMA's latency is hidden.
     auto finish_tile = [&](int j) {
@@ -244,52 +283,79 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
         tc_fence_after();
 #pragma unroll
         for (int c0 = 0; c0 < NR; c0 += 8) {
-            uint32_t v[8];
-            tmem_ld8(trow + 2 * NP + c0, v);
+            uint32_t hi[ISS][8], lo[ISS][8];
+#pragma unroll
+            for (int w = 0; w < ISS; ++w) {
+                tmem_ld8(trow + kOCol + w * NP + c0, hi[w]);
+                tmem_ld8(trow + kOCol + w * NP + NR + c0, lo[w]);
+            }
             tmem_wait_ld();
 #pragma unroll
-            for (int g = 0; g < 8; ++g) o_acc[c0 + g] = o_acc[c0 + g] * alpha_s[c0 + g] + __uint_as_float(v[g]);
+            for (int g = 0; g < 8; ++g) {
+                float a = 0.0f, b = 0.0f;
+#pragma unroll
+                for (int w = 0; w < ISS; ++w) a += __uint_as_float(hi[w][g]), b += __uint_as_float(lo[w][g]);
+                const float al = L == 1 ? alpha_r[g] : alpha_s[c0 + g];
+                o_acc[c0 + g] = o_acc[c0 + g] * al + (a + b * (1.0f / kLoScale));
+            }
         }
         tc_fence_before();
         if (tid == 0 && ok && j + nst < nt) issue_tile(j + nst);  // both MMAs that read slot j % nst are done
         __syncwarp();
     };
 
-    if (tid == 0 && nt > 0) {
+    if (issuer && nt > 0) {
         ok = mbar_wait(full(0), 0, p.status, where | 3);
         tc_fence_after();
         if (ok) issue_mma1(0);
     }
     __syncwarp();
     for (int i = 0; i < nt; ++i) {
-        if (tid == 0 && ok && i + 1 < nt) {
+        if (SBUF == 2 && issuer && ok && i + 1 < nt) {  // next tile's scores, computed while this tile's softmax runs
             ok = mbar_wait(full((i + 1) % nst), ((i + 1) / nst) & 1, p.status, where | 4);
             tc_fence_after();
             if (ok) issue_mma1(i + 1);
         }
         __syncwarp();
-        ok = mbar_wait((i & 1) ? bar_s1 : bar_s0, (i >> 1) & 1, p.status, where | 5) && ok;
+        ok = mbar_wait(sbar(i), (SBUF == 2 ? (i >> 1) : i) & 1, p.status, where | 5) && ok;
         tc_fence_after();
         const int pos = (t_begin + i) * kTileKeys + tid;  // this thread's key position
-        const uint32_t srow = trow + (i & 1) * NP;
+        float skeep[L == 1 ? 8 : 1];
         // pass 1: tile maximum per query row
 #pragma unroll
         for (int c0 = 0; c0 < NR; c0 += 8) {
-            uint32_t v[8];
-            tmem_ld8(srow + c0, v);
-            tmem_wait_ld();
+            float sc[8];
+            load_scores(i, c0, sc);
             const int j = c0 >> 3;
             const bool vis = pos < seq && (W == 0 || pos > seq + j - W);
 #pragma unroll
             for (int g = 0; g < 8; ++g) {
-                const float s = vis ? __uint_as_float(v[g]) * s_scale : kNeg;
-                const float mx = redux_max(s);
+                const float sv = vis ? sc[g] * s_scale : kNeg;
+                if (L == 1) skeep[g] = sv;
+                const float mx = redux_max(sv);
                 if (lane == 0) wred[warp][c0 + g] = mx;
             }
         }
         if (i > 0) finish_tile(i - 1);
         __syncthreads();
-        if (tid < NR) {
+        if constexpr (L == 1) {
+            // every thread folds the four warps' maxima itself: no second barrier, no shared-memory round trip
+            const float4* w4 = reinterpret_cast<const float4*>(&wred[0][0]);
+            float tm[8];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float4 a = w4[2 * w], b4 = w4[2 * w + 1];
+                const float v8[8] = {a.x, a.y, a.z, a.w, b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+                for (int g = 0; g < 8; ++g) tm[g] = w == 0 ? v8[g] : fmaxf(tm[g], v8[g]);
+            }
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                const float mn = fmaxf(tm[g], m_r[g]);
+                alpha_r[g] = ex2(m_r[g] - mn);
+                m_r[g] = mn;
+            }
+        } else if (tid < NR) {
             const float mo = m_s[tid];
             const float mn = fmaxf(fmaxf(fmaxf(wred[0][tid], wred[1][tid]), fmaxf(wred[2][tid], wred[3][tid])), mo);
             alpha_s[tid] = ex2(mo - mn);
@@ -301,49 +367,47 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
 #pragma unroll
             for (int c = 0; c < 8; ++c) reinterpret_cast<uint4*>(vrow)[c] = make_uint4(0, 0, 0, 0);
         }
-        __syncthreads();
-        // pass 2: p = 2^(s - m), split into an E4M3 and an E5M2 term, P[row][key] bytes
+        if constexpr (L != 1) __syncthreads();
+        // pass 2: p = 2^(s - m) as two E4M3 terms (the second times 16), bytes of the B operand P[row][key]
 #pragma unroll
         for (int c0 = 0; c0 < NR; c0 += 8) {
-            uint32_t v[8];
-            tmem_ld8(srow + c0, v);
-            tmem_wait_ld();
+            float sc[8];
+            if (L != 1) load_scores(i, c0, sc);
             const int j = c0 >> 3;
             const bool vis = pos < seq && (W == 0 || pos > seq + j - W);
 #pragma unroll
             for (int g = 0; g < 8; ++g) {
                 const int n = c0 + g;
-                const float pr = vis ? ex2(__uint_as_float(v[g]) * s_scale - m_s[n]) : 0.0f;
-                l_part[n] = l_part[n] * alpha_s[n] + pr;
+                const float sv = L == 1 ? skeep[g] : (vis ? sc[g] * s_scale : kNeg);
+                const float pr = vis ? ex2(sv - (L == 1 ? m_r[g] : m_s[n])) : 0.0f;
+                l_part[n] = l_part[n] * (L == 1 ? alpha_r[g] : alpha_s[n]) + pr;
                 const float ps = pr * kPScale;
                 const uint32_t bh = f_to_e4m3(ps);
-                const uint32_t bl = f_to_e5m2(ps - e4m3_to_f(bh));
-                const uint32_t off = swz128(n, tid);
-                g_qhi[2 * QP_BYTES + off] = static_cast<uint8_t>(bh);
-                g_qhi[3 * QP_BYTES + off] = static_cast<uint8_t>(bl);
+                const uint32_t bl = f_to_e4m3((ps - e4m3_to_f(bh)) * kLoScale);
+                g_p[swz128(n, tid)] = static_cast<uint8_t>(bh);
+                g_p[swz128(NR + n, tid)] = static_cast<uint8_t>(bl);
             }
         }
         tc_fence_before();
         fence_proxy_async_smem();
         __syncthreads();
-        if (tid == 0 && ok) {  // O^T = V^T . (p_hi + p_lo)^T
+        if (issuer && ok) {
             tc_fence_after();
-            const uint32_t vb = base + (i % nst) * kStageBytes + kTileKeys * 128;
-            const uint32_t ih = umma_idesc(128, NP, 0, 0, 1, 0), il = umma_idesc(128, NP, 0, 1, 1, 0);
-            const uint64_t bh = umma_smem_desc(s_phi, 16, 1024, kSwizzle128);
-            const uint64_t bl = umma_smem_desc(s_plo, 16, 1024, kSwizzle128);
-            const uint32_t d = tmem + 2 * NP;
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-                umma_f8_ss(d, umma_smem_desc(vb + 4096 * k, 1024, 1024, kSwizzle128), bh + 2 * k, ih, k != 0);
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-                umma_f8_ss(d, umma_smem_desc(vb + 4096 * k, 1024, 1024, kSwizzle128), bl + 2 * k, il, 1);
-            umma_commit(bar_o);
+            issue_mma2(i);
+            if (SBUF == 1 && i + 1 < nt) {  // one score buffer: the next tile's scores can only start now
+                ok = mbar_wait(full((i + 1) % nst), ((i + 1) / nst) & 1, p.status, where | 4);
+                tc_fence_after();
+                if (ok) issue_mma1(i + 1);
+            }
         }
         __syncwarp();
     }
     if (nt > 0) finish_tile(nt - 1);
+    if constexpr (L == 1) {
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+            if (tid == g) m_s[g] = m_r[g];
+    }
     __syncthreads();
 
     // ---------------- the L new tokens: last CTA of the cluster, FP32 on CUDA cores
@@ -483,23 +547,23 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
 
 template <int L>
 int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
-    constexpr int NR = 8 * L, NP = NR < 16 ? 16 : NR;
+    constexpr int NR = 8 * L, NP = 2 * NR;
     const int tile_cap = (q->max_pages * q->page_size + kTileKeys - 1) / kTileKeys;
     int tiles_max = tile_cap;
     if (q->window > 0) tiles_max = min(tiles_max, q->window / kTileKeys + 2);
     if (tiles_max < 1) tiles_max = 1;
     int C = q->chunks;
     if (C <= 0) {
-        int want = (2 * 148 + q->B * q->Hkv - 1) / (q->B * q->Hkv);  // aim at two CTAs per SM
+        int want = (2 * 148) / (q->B * q->Hkv);  // two resident CTAs per SM
         if (want > tiles_max) want = tiles_max;
         C = 1;
-        while (C < want && C < 8) C *= 2;
+        while (2 * C <= want && C < 8) C *= 2;
     }
     if (C != 1 && C != 2 && C != 4 && C != 8) return MSK_ERR_INVALID;
     if ((tiles_max + C - 1) / C > kMaxTilesPerCta) return MSK_ERR_UNSUPPORTED;
     int nst = q->stages > 0 ? q->stages : 3;
     if (nst > kAttnMaxStages) nst = kAttnMaxStages;
-    const int smem = 1024 + nst * kStageBytes + 4 * NP * 128 + NR * 128 * 4;
+    const int smem = 1024 + nst * kStageBytes + 2 * NP * 128 + NR * 128 * 4;
 
     CUtensorMap tm_k, tm_v;
     const uint64_t dims[4] = {128, static_cast<uint64_t>(q->Hkv), static_cast<uint64_t>(q->page_size),

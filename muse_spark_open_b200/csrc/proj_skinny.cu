@@ -270,3 +270,26 @@ extern "C" int msk_proj_skinny(const MskProjParams* q, int* status, void* stream
     cudaError_t e = cudaLaunchKernelEx(&cfg, proj_skinny_kernel, tm_w, tm_x, a);
     return e == cudaSuccess ? 0 : MSK_ERR_CUDA;
 }
+
+// Tuning aid: how many clusters of `splits` CTAs with `smem_bytes` of dynamic shared memory the device
+// can keep resident at once (cudaOccupancyMaxActiveClusters).  Negative on error.
+extern "C" int msk_proj_max_active_clusters(int splits, int smem_bytes) {
+    using namespace msk;
+    if (splits < 1 || splits > 8 || smem_bytes < 0) return MSK_ERR_INVALID;
+    if (cudaFuncSetAttribute(proj_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess)
+        return MSK_ERR_CUDA;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(splits, 148, 1);
+    cfg.blockDim = dim3(128, 1, 1);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, proj_skinny_kernel, &cfg) != cudaSuccess) return MSK_ERR_CUDA;
+    return n;
+}
