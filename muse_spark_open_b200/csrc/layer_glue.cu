@@ -3,8 +3,8 @@
 //                reference); also leaves ssq[t] = sum stream^2.
 //   router       FP32 logits[t, e] = rs[t] * sum_k (stream1[t,k] * (1 + w[k])) * R[e, k] + bias[e] on
 //                CUDA cores (expert ids must not depend on tensor-core rounding).  Blocks of 32 tokens x 32
-//                experts x H/8 of K; the last block of a (token group, expert tile) to finish (ticket) adds
-//                the 8 partials in a fixed order, so ids are reproducible.
+//                experts x H/32 of K; the last block of a (token group, expert tile) to finish (ticket) adds
+//                the 32 partials in a fixed order, so ids are reproducible.
 #include "msk.h"
 #include "ptx.cuh"
 
@@ -67,7 +67,7 @@ struct RouterArgs {
 constexpr int kRouterK = 64;    // k per shared-memory sub-tile
 constexpr int kRouterT = 32;    // tokens per block
 constexpr int kRouterE = 32;    // experts per block
-constexpr int kRouterKS = 8;    // K splits (partials summed by the last block of each (token group, expert tile))
+constexpr int kRouterKS = 32;   // K splits (partials summed by the last block of each (token group, expert tile))
 
 __global__ void __launch_bounds__(256) router_kernel(RouterArgs p) {
     __shared__ float Rs[kRouterE][kRouterK + 1];
@@ -76,7 +76,8 @@ __global__ void __launch_bounds__(256) router_kernel(RouterArgs p) {
     const int ks = blockIdx.x, et = blockIdx.y, tg = blockIdx.z, tid = threadIdx.x;
     const int t0 = tg * kRouterT, e0 = et * kRouterE;
     const int nt = min(kRouterT, p.T - t0), ne = min(kRouterE, p.E - e0);
-    const int kper = p.H / kRouterKS;
+    const int KS = gridDim.x;  // K splits: at most kRouterKS, fewer when H is small
+    const int kper = p.H / KS;
     const int tw = tid >> 5, el = tid & 31;  // warp w owns tokens w, w+8, w+16, w+24; lane = expert
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     pdl_wait();
@@ -106,7 +107,7 @@ __global__ void __launch_bounds__(256) router_kernel(RouterArgs p) {
     }
     __threadfence();
     __syncthreads();
-    if (tid == 0) last = atomicAdd(p.ticket + tg * gridDim.y + et, 1) == kRouterKS - 1;
+    if (tid == 0) last = atomicAdd(p.ticket + tg * gridDim.y + et, 1) == KS - 1;
     __syncthreads();
     if (!last) return;
     __threadfence();
@@ -114,12 +115,9 @@ __global__ void __launch_bounds__(256) router_kernel(RouterArgs p) {
     for (int j = 0; j < 4; ++j) {
         const int t = tw + 8 * j;
         if (t < nt && el < ne) {
-            float v[kRouterKS];
-#pragma unroll
-            for (int s = 0; s < kRouterKS; ++s) v[s] = __ldcg(p.part + (static_cast<size_t>(s) * p.T + t0 + t) * p.E + e0 + el);
             float sum = 0.0f;
-#pragma unroll
-            for (int s = 0; s < kRouterKS; ++s) sum += v[s];
+#pragma unroll 8
+            for (int s = 0; s < KS; ++s) sum += __ldcg(p.part + (static_cast<size_t>(s) * p.T + t0 + t) * p.E + e0 + el);
             float ss = 0.0f;
             for (int q = 0; q < p.ssq_parts; ++q) ss += __ldcg(p.ssq + q * p.T + t0 + t);
             sum *= rsqrtf(ss / p.H + p.eps);
@@ -171,7 +169,7 @@ extern "C" int msk_layer_front(const MskLayerFront* f, int* status, void* stream
         !f->router_ticket || !f->logits)
         return MSK_ERR_INVALID;
     const int T = f->B * f->L, H = f->H, nqkv = (2 * f->Hq + 2 * f->Hkv) * f->d, no = f->Hq * f->d;
-    if (T < 1 || T > 256 || H % 1024 != 0 || H > 8192 || H % (kRouterKS * kRouterK) != 0 || f->E < 1 || f->E > 256) return MSK_ERR_UNSUPPORTED;
+    if (T < 1 || T > 256 || H % 1024 != 0 || H > 8192 || f->E < 1 || f->E > 256) return MSK_ERR_UNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     int rc = launch_prep(f->stream, f->input_norm_w, f->xn0, f->ssq0, T, H, f->norm_eps, s, f->pdl);
     if (rc != 0) return rc;
@@ -206,7 +204,9 @@ extern "C" int msk_layer_front(const MskLayerFront* f, int* status, void* stream
     r.s1 = f->stream1, r.w = static_cast<const __nv_bfloat16*>(f->pre_expert_norm_w), r.ssq = f->ssq1;
     r.ssq_parts = (H + 127) / 128, r.eps = f->norm_eps, r.R = f->router_w, r.bias = f->router_bias;
     r.part = f->router_part, r.ticket = f->router_ticket, r.logits = f->logits, r.T = T, r.H = H, r.E = f->E;
-    return launch1(router_kernel, dim3(kRouterKS, (f->E + kRouterE - 1) / kRouterE, (T + kRouterT - 1) / kRouterT), dim3(256), 0, s, 1, r);
+    int ks = kRouterKS;
+    while (H % (ks * kRouterK) != 0) ks /= 2;
+    return launch1(router_kernel, dim3(ks, (f->E + kRouterE - 1) / kRouterE, (T + kRouterT - 1) / kRouterT), dim3(256), 0, s, 1, r);
 }
 
 extern "C" int msk_layer_decode(const MskLayerParams* p, int* status, void* stream) {

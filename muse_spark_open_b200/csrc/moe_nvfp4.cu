@@ -560,8 +560,14 @@ struct MoeCombineArgs {
     int ldc;
 };
 
-__global__ void __launch_bounds__(256) moe_combine_kernel(MoeCombineArgs p) {
-    __shared__ float red[8][8];
+// One CTA per token, 512 threads, each owning 4 output channels per 2048 of H: all the token's slots and K
+// splits are loaded back to back (memory-level parallelism instead of a dependent loop), kept in registers
+// for the second pass.
+constexpr int kCombineThreads = 512;
+
+template <int ITERS>  // ITERS * 2048 >= H
+__global__ void __launch_bounds__(kCombineThreads) moe_combine_kernel(MoeCombineArgs p) {
+    __shared__ float red[kCombineThreads / 32][8];
     __shared__ float rnorm[8];
     const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     pdl_wait();
@@ -577,20 +583,29 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(MoeCombineArgs p) {
             w[s] = __ldcg(p.wts + t * p.top_k + s);
         }
     }
+    float4 z[ITERS][8];
     float ss[8];
 #pragma unroll
     for (int s = 0; s < 8; ++s) ss[s] = 0.0f;
-    for (int d = tid * 4; d < p.H; d += 1024) {
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int d = (tid + it * kCombineThreads) * 4;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) z[it][s] = make_float4(0, 0, 0, 0);
+        if (d >= p.H) continue;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            if (!local[s]) continue;
+            for (int k = 0; k < p.S; ++k) {
+                const float4 a = __ldcg(reinterpret_cast<const float4*>(p.yp + (static_cast<size_t>(k) * p.P + t * p.top_k + s) * p.H + d));
+                z[it][s].x += a.x, z[it][s].y += a.y, z[it][s].z += a.z, z[it][s].w += a.w;
+            }
+        }
         const uint2 pw = *reinterpret_cast<const uint2*>(p.post_w + d);
         const float f[4] = {1.0f + bf16lo(pw.x), 1.0f + bf16hi(pw.x), 1.0f + bf16lo(pw.y), 1.0f + bf16hi(pw.y)};
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
-            if (!local[s]) continue;
-            float4 y = make_float4(0, 0, 0, 0);
-            for (int k = 0; k < p.S; ++k) {
-                const float4 a = __ldcg(reinterpret_cast<const float4*>(p.yp + (static_cast<size_t>(k) * p.P + t * p.top_k + s) * p.H + d));
-                y.x += a.x, y.y += a.y, y.z += a.z, y.w += a.w;
-            }
+            float4& y = z[it][s];
             y.x *= f[0], y.y *= f[1], y.z *= f[2], y.w *= f[3];
             ss[s] += y.x * y.x + y.y * y.y + y.z * y.z + y.w * y.w;
         }
@@ -603,25 +618,21 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(MoeCombineArgs p) {
     __syncthreads();
     if (tid < 8) {
         float v = 0.0f;
-        for (int k = 0; k < 8; ++k) v += red[k][tid];
+        for (int k = 0; k < kCombineThreads / 32; ++k) v += red[k][tid];
         rnorm[tid] = rsqrtf(v / p.H + p.eps);
     }
     __syncthreads();
-    for (int d = tid * 4; d < p.H; d += 1024) {
-        const uint2 pw = *reinterpret_cast<const uint2*>(p.post_w + d);
-        const float f[4] = {1.0f + bf16lo(pw.x), 1.0f + bf16hi(pw.x), 1.0f + bf16lo(pw.y), 1.0f + bf16hi(pw.y)};
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int d = (tid + it * kCombineThreads) * 4;
+        if (d >= p.H) continue;
         float4 acc = make_float4(0, 0, 0, 0);
         if (p.resid != nullptr) acc = __ldcg(reinterpret_cast<const float4*>(p.resid + static_cast<size_t>(t) * p.ldr + d));
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
             if (!local[s]) continue;
-            float4 y = make_float4(0, 0, 0, 0);
-            for (int k = 0; k < p.S; ++k) {
-                const float4 a = __ldcg(reinterpret_cast<const float4*>(p.yp + (static_cast<size_t>(k) * p.P + t * p.top_k + s) * p.H + d));
-                y.x += a.x, y.y += a.y, y.z += a.z, y.w += a.w;
-            }
             const float c = w[s] * rnorm[s];
-            acc.x += y.x * f[0] * c, acc.y += y.y * f[1] * c, acc.z += y.z * f[2] * c, acc.w += y.w * f[3] * c;
+            acc.x += z[it][s].x * c, acc.y += z[it][s].y * c, acc.z += z[it][s].z * c, acc.w += z[it][s].w * c;
         }
         if (p.out_fp32) {
             *reinterpret_cast<float4*>(static_cast<float*>(p.out) + static_cast<size_t>(t) * p.ldo + d) = acc;
@@ -718,7 +729,7 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
     if (q->T < 1 || q->top_k < 1 || q->top_k > 8 || P > kMaxPairs || q->local_count < 1 || q->local_count > kMaxExperts ||
         q->T > kMaxPairs / 8)
         return MSK_ERR_UNSUPPORTED;
-    if (q->H % 128 != 0 || q->I % 128 != 0 || q->ldx % 8 != 0) return MSK_ERR_UNSUPPORTED;
+    if (q->H % 128 != 0 || q->I % 128 != 0 || q->ldx % 8 != 0 || q->H > 16 * kCombineThreads) return MSK_ERR_UNSUPPORTED;
     if (q->logits != nullptr && (q->n_logits > 256 || q->n_logits < q->top_k)) return MSK_ERR_UNSUPPORTED;
     const int direct = q->T <= kGroup;
     if (!direct && q->x_sorted == nullptr) return MSK_ERR_INVALID;
@@ -789,7 +800,8 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
     c.post_w = static_cast<const __nv_bfloat16*>(q->post_norm_w), c.eps = q->post_eps, c.resid = q->resid, c.ldr = q->ldr;
     c.out = q->out, c.out_fp32 = q->out_fp32, c.ldo = q->ldo;
     c.out_copy = static_cast<__nv_bfloat16*>(q->out_copy), c.ldc = q->ldc;
-    return launch_pdl(moe_combine_kernel, dim3(q->T), dim3(256), 0, s, 1, c);
+    if (q->H <= 2 * kCombineThreads * 4) return launch_pdl(moe_combine_kernel<2>, dim3(q->T), dim3(kCombineThreads), 0, s, 1, c);
+    return launch_pdl(moe_combine_kernel<4>, dim3(q->T), dim3(kCombineThreads), 0, s, 1, c);
 }
 
 // ---------------------------------------------------------------- routed experts without caller scratch

@@ -37,7 +37,7 @@ def expert_forward(x: torch.Tensor, weights, e: int, round_inter: bool = False) 
     return inter @ w2.T
 
 
-def ref_kernel(data, weights, fp32_out: bool = False) -> torch.Tensor:
+def ref_kernel(data, weights, fp32_out: bool = False, round_inter: bool = False) -> torch.Tensor:
     """out[t] = sum over local (t, slot) pairs of topk_weight * post_norm(expert(x[t]));  bf16 [T,H].
 
     Tokens with no local pair stay zero (reference.py:93-107).
@@ -51,7 +51,7 @@ def ref_kernel(data, weights, fp32_out: bool = False) -> torch.Tensor:
         if not lo <= e < hi:
             continue
         tok, slot = (ids == e).nonzero(as_tuple=True)
-        y = expert_forward(x[tok], weights, e - cfg.get("weights_start", 0))
+        y = expert_forward(x[tok], weights, e - cfg.get("weights_start", 0), round_inter=round_inter)
         out.index_add_(0, tok, post_expert_norm(y, weights["post_norm_w"]) * data["topk_weights"][tok, slot, None])
     return out if fp32_out else out.to(torch.bfloat16)
 
