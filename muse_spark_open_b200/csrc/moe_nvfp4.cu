@@ -17,14 +17,15 @@
 //                 B operand (32 rows x 64 k, 128-byte swizzle) into the same ring stage: x itself when the
 //                 step has at most 32 tokens (column = token), else x gathered in expert-list order by a
 //                 small kernel; for gemm 2 the activations the act kernel wrote in that order.
-//   warps 9..16   dequant: thread = weight row.  8 codes per word become 4 BF16x2 registers with 3
+//   warps 9..16   dequant (two groups of four warps, one chunk per group at a time): thread = weight row.  8 codes per word become 4 BF16x2 registers with 3
 //                 shift+mask steps (the permutation puts every code's bits where BF16 wants them,
 //                 magnitudes as BF16 subnormals * 2^-126), times the block scale (E4M3 * 2^100 as BF16)
 //                 with one HMUL2 each: exact E2M1 x E4M3 products * 2^-26, written straight into tensor
 //                 memory (tcgen05.st) as the A operand.  No BF16 round trip through shared memory.
 //   warps 1..4    one lane each issues tcgen05.mma kind::f16, A from TMEM, B from shared memory.  One thread
-//                 can issue only about one MMA per 100 clocks whatever N is, so four warps issue in parallel,
-//                 each into its own FP32 accumulator in TMEM (double-buffered per unit).
+//                 can issue only about one MMA per 100 clocks whatever N is, so four warps issue in parallel
+//                 (2 of a chunk's 8 K steps each), each into its own FP32 accumulator in TMEM
+//                 (double-buffered per unit).
 //   warps 5..8    epilogue: adds the four accumulators, tcgen05.ld, times global scale * 2^26 (and the folded pre-expert RMSNorm row
 //                 scale), plain stores into this K split's FP32 partial buffer.  K splits are summed in a
 //                 fixed order by the consumer, so results are bitwise reproducible and no buffer has to
@@ -49,7 +50,8 @@ constexpr int kMaxPairs = 2048;
 constexpr int kMaxExperts = 256;
 constexpr int kMaxGroups = 320;
 constexpr int kIssuers = 4;         // MMA-issuing warps (one lane each); a single thread issues one tcgen05.mma per ~100 clk
-constexpr int kMoeThreads = 17 * 32;
+constexpr int kDqGroups = 2;        // dequant warp groups (4 warps each); group g takes the chunks with index = g (mod 2)
+constexpr int kMoeThreads = (1 + kIssuers + 4 + 4 * kDqGroups) * 32;
 constexpr int kRouteThreads = kMoeThreads, kRouteWarps = kRouteThreads / 32;
 
 // ---------------------------------------------------------------- weight repacking (prepare time)
@@ -368,9 +370,9 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
     }
     if (tid == 32) {
         // a ring stage (weight block + B tile) is free again when the 4 dequant warps have read the block and
-        // the MMAs that read the B tile have completed
-        for (int i = 0; i < kNRaw; ++i) mbar_init(smem_u32(&bar.raw_full[i]), 1), mbar_init(smem_u32(&bar.raw_empty[i]), 5);
-        for (int i = 0; i < kNA; ++i) mbar_init(smem_u32(&bar.a_full[i]), 4), mbar_init(smem_u32(&bar.a_empty[i]), 1);
+        // every issuing warp's MMAs that read the B tile have completed
+        for (int i = 0; i < kNRaw; ++i) mbar_init(smem_u32(&bar.raw_full[i]), 1), mbar_init(smem_u32(&bar.raw_empty[i]), 4 + kIssuers);
+        for (int i = 0; i < kNA; ++i) mbar_init(smem_u32(&bar.a_full[i]), 4), mbar_init(smem_u32(&bar.a_empty[i]), kIssuers);
         for (int i = 0; i < 2; ++i) mbar_init(smem_u32(&bar.d_full[i]), kIssuers), mbar_init(smem_u32(&bar.d_empty[i]), 4);
         fence_mbar_init();
     }
@@ -423,8 +425,9 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
         }
         __syncwarp();
     } else if (warp <= kIssuers) {
-        // ------------------------------------------------ MMA issue: warp w + 1 owns A slot w, i.e. the chunks
-        // with running index = w (mod 4), and its own accumulator; the epilogue adds the four.
+        // ------------------------------------------------ MMA issue: every issuing warp takes 2 of the 8 K steps of
+        // every chunk (so an A slot in TMEM is free again after 2 issue times, not 8) and adds them into its own
+        // accumulator; the epilogue adds the four.
         if (lane == 0) {
             const int w = warp - 1;
             const uint32_t idesc = umma_idesc(128, kGroup, 1, 1, 0, 0);
@@ -436,27 +439,20 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d = tmem + kNA * 64 + (db * kIssuers + w) * kGroup;
-                bool first = true;
                 for (int c = 0; c < nch && ok; ++c, ++cc) {
-                    if ((cc & 3) != w) continue;
-                    const int s = cc % kNRaw;
+                    const int s = cc % kNRaw, as = cc % kNA;
                     ok = mbar_wait(smem_u32(&bar.raw_full[s]), (cc / kNRaw) & 1, p.status, where | 5) &&
-                         mbar_wait(smem_u32(&bar.a_full[w]), (cc / kNA) & 1, p.status, where | 4);
+                         mbar_wait(smem_u32(&bar.a_full[as]), (cc / kNA) & 1, p.status, where | 4);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t bb = base + s * kStage + kBlob;
-                    const uint64_t b0 = umma_smem_desc(bb, 16, 1024, kSwizzle128);
-                    const uint64_t b1 = umma_smem_desc(bb + 4096, 16, 1024, kSwizzle128);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        umma_f16_ts(d, tmem + w * 64 + 8 * j, (j < 4 ? b0 : b1) + 2 * (j & 3), idesc, !(first && j == 0));
-                    first = false;
-                    umma_commit(smem_u32(&bar.a_empty[w]));
+                    const uint32_t bb = base + s * kStage + kBlob + (w >> 1) * 4096;  // K steps 2w, 2w+1 sit in half w / 2
+                    const uint64_t bd = umma_smem_desc(bb, 16, 1024, kSwizzle128) + 4 * (w & 1);
+                    umma_f16_ts(d, tmem + as * 64 + 16 * w, bd, idesc, c != 0);
+                    umma_f16_ts(d, tmem + as * 64 + 16 * w + 8, bd + 2, idesc, 1);
+                    umma_commit(smem_u32(&bar.a_empty[as]));
                     umma_commit(smem_u32(&bar.raw_empty[s]));
                 }
-                if (!ok) break;
-                if (first) mbar_arrive(smem_u32(&bar.d_full[db]));  // no chunk of this unit fell to this warp
-                else umma_commit(smem_u32(&bar.d_full[db]));
+                if (ok) umma_commit(smem_u32(&bar.d_full[db]));
             }
         }
         __syncwarp();
@@ -486,7 +482,6 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
             for (int c = 0; c < 32; ++c) v[c] = 0.0f;
 #pragma unroll
             for (int w = 0; w < kIssuers; ++w) {
-                if (nch < 4 && ((w - cc0) & 3) >= nch) continue;  // that warp had no chunk of this unit
                 uint32_t t[32];
                 const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + kNA * 64 + (db * kIssuers + w) * kGroup;
                 tmem_ld16(taddr, *reinterpret_cast<uint32_t(*)[16]>(&t[0]));
@@ -514,7 +509,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
         bool ok = true;
         for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
             for (int c = 0; c < nch; ++c, ++cc) {
-                if ((cc & 1) != grp) continue;
+                if (cc % kDqGroups != grp) continue;
                 const int s = cc % kNRaw, as = cc % kNA;
                 ok = mbar_wait(smem_u32(&bar.raw_full[s]), (cc / kNRaw) & 1, p.status, where | 7);
                 if (ok && cc >= kNA) ok = mbar_wait(smem_u32(&bar.a_empty[as]), ((cc / kNA) - 1) & 1, p.status, where | 8);

@@ -208,9 +208,9 @@ extern "C" int msk_proj_skinny(const MskProjParams* q, int* status, void* stream
     const int tiles = (q->N + 127) / 128, KT = q->K / 64;
     int S = q->splits;
     if (S <= 0) {
-        S = sms / tiles;
-        if (S < 1) S = 1;
-        if (S > 8) S = 8;
+        // a power of two: clusters of 3, 5, 6 or 7 CTAs leave SMs unused (they cannot span GPCs)
+        S = 1;
+        while (2 * S * tiles <= sms && S < 8) S *= 2;
     }
     if (S > 8) return MSK_ERR_UNSUPPORTED;
     if (S > KT) S = KT;

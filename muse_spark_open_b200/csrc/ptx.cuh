@@ -67,7 +67,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-
 // Wait budget for any single wait, in SM clock cycles (about half a second).  Legitimate waits
 // here last microseconds.
 constexpr long long kWaitBudgetCycles = 1000ll * 1000 * 1000;
