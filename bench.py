@@ -107,9 +107,11 @@ def cpu_sample(weights_cpu, n_req, threads):
     seqs = seq_lens_all()[:n_req].tolist()
     data = olayer.make_input(n_req, seqs, SEED + 1, hidden=HIDDEN, hq=HQ, hkv=HKV, d=HEAD, page=PAGE, window=0,
                              rope_theta=0.0)
+    reps = 8  # one step of n_req requests is under a second on a many-core host: repeat it
     t0 = time.perf_counter()
-    olayer.ref_kernel(data, weights_cpu)
-    return time.perf_counter() - t0
+    for _ in range(reps):
+        olayer.ref_kernel(data, weights_cpu)
+    return (time.perf_counter() - t0) / reps
 
 
 def run_reference(args):
@@ -129,7 +131,7 @@ def run_reference(args):
         "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic", "config": {"workload": workload_name(args.gpus)},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": f"one layer step for the first {n_req} of the {REQUESTS} requests per timed step"},
+                         "sample": f"8 layer steps for the first {n_req} of the {REQUESTS} requests per timed step"},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -276,7 +278,7 @@ def run_ours(args):
         n_req = 64
         sec = cpu_sample(w_cpu, n_req, threads)
         line["cpu_baseline"] = {"value": n_req / sec, "unit": UNIT, "cores": threads, "kind": "port",
-                                "sample": f"one layer step for the first {n_req} of the {REQUESTS} requests ({sec:.1f} s)"}
+                                "sample": f"8 layer steps for the first {n_req} of the {REQUESTS} requests ({8 * sec:.1f} s of CPU time)"}
     print(json.dumps(line))
     if world > 1:
         dist.barrier()
