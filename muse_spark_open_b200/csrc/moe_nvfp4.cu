@@ -247,25 +247,45 @@ __device__ void build_routing(RouteTables& rt, const RouteArgs& a, int* status, 
         rt.counts[e] = run;
     }
     __syncthreads();
-    if (tid == 0) {
-        int off = 0, ng = 0;
-        for (int e = 0; e < a.local_count; ++e) {
-            const int n = rt.counts[e];
-            rt.offs[e] = off;
-            for (int g = 0; g < n; g += kGroup) {
-                if (ng < kMaxGroups) {
-                    rt.g_expert[ng] = static_cast<unsigned short>(e);
-                    rt.g_off[ng] = static_cast<unsigned short>(off + g);
-                    rt.g_n[ng] = static_cast<unsigned short>(min(kGroup, n - g));
-                    ++ng;
-                } else {
-                    report(status, MSK_ERR_CAPACITY, where | 1, ng, kMaxGroups);
-                }
-            }
-            off += n;
+    if (warp == 0) {
+        // offsets and expert-groups by a warp scan: lane l owns experts 8 l .. 8 l + 7.  (One thread walking all
+        // the experts costs ~200 clocks per expert: dependent single-thread issue.)
+        int n_[8], sum_n = 0, sum_g = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = lane * 8 + i;
+            n_[i] = e < a.local_count ? rt.counts[e] : 0;
+            sum_n += n_[i];
+            sum_g += (n_[i] + kGroup - 1) / kGroup;
         }
-        rt.n_groups = ng;
-        rt.n_local = off;
+        int inc_n = sum_n, inc_g = sum_g;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int vn = __shfl_up_sync(0xffffffffu, inc_n, o), vg = __shfl_up_sync(0xffffffffu, inc_g, o);
+            if (lane >= o) inc_n += vn, inc_g += vg;
+        }
+        int off = inc_n - sum_n, gi = inc_g - sum_g;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = lane * 8 + i;
+            if (e < a.local_count) {
+                rt.offs[e] = off;
+                for (int g = 0; g < n_[i]; g += kGroup, ++gi) {
+                    if (gi < kMaxGroups) {
+                        rt.g_expert[gi] = static_cast<unsigned short>(e);
+                        rt.g_off[gi] = static_cast<unsigned short>(off + g);
+                        rt.g_n[gi] = static_cast<unsigned short>(min(kGroup, n_[i] - g));
+                    } else {
+                        report(status, MSK_ERR_CAPACITY, where | 1, gi, kMaxGroups);
+                    }
+                }
+                off += n_[i];
+            }
+        }
+        if (lane == 31) {
+            rt.n_groups = min(inc_g, kMaxGroups);
+            rt.n_local = inc_n;
+        }
     }
     __syncthreads();
     for (int i = tid; i < P; i += kRouteThreads) {
