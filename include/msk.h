@@ -224,8 +224,8 @@ typedef struct {
     void* attn;                    /* bf16 [T, Hq*d] */
     float* stream1;                /* fp32 [T, H] stream after attention */
     void* xn1;                     /* bf16 [T, H] expert input before its row scale */
-    float* ssq1;                   /* fp32 [H/128, T] */
-    float* router_part;            /* fp32 [32, T, E] */
+    float* ssq1;                   /* fp32 [H/128 + 1, T]: per-128-column partial sums of squares, last row their total */
+    float* router_part;            /* fp32 [H/128, T, E] */
     int32_t* router_ticket;        /* int32 [ceil(T/32) * ceil(E/32)], zero before the first call */
     float* logits;                 /* fp32 [T, E] */
     int attn_chunks, attn_stages, qkv_splits, o_splits;

@@ -3,8 +3,8 @@
 //                reference); also leaves ssq[t] = sum stream^2.
 //   router       FP32 logits[t, e] = rs[t] * sum_k (stream1[t,k] * (1 + w[k])) * R[e, k] + bias[e] on
 //                CUDA cores (expert ids must not depend on tensor-core rounding).  Blocks of 32 tokens x 32
-//                experts x H/32 of K; the last block of a (token group, expert tile) to finish (ticket) adds
-//                the 32 partials in a fixed order, so ids are reproducible.
+//                experts x 128 of K; the last block of a (token group, expert tile) to finish (ticket) adds
+//                the H/128 partials in a fixed order, so ids are reproducible.
 #include "msk.h"
 #include "ptx.cuh"
 
@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(256) prep_norm_kernel(const float* __restrict_
 struct RouterArgs {
     const float* s1;        // [T, H]
     const __nv_bfloat16* w; // [H]
-    const float* ssq;       // [parts, T]
+    float* ssq;             // [parts + 1, T]; the last row receives the totals
     int ssq_parts;
     float eps;
     const float* R;         // [E, H]
@@ -64,41 +64,36 @@ struct RouterArgs {
     int T, H, E;
 };
 
-constexpr int kRouterK = 64;    // k per shared-memory sub-tile
+constexpr int kRouterK = 128;   // k per block (one load phase)
 constexpr int kRouterT = 32;    // tokens per block
 constexpr int kRouterE = 32;    // experts per block
-constexpr int kRouterKS = 32;   // K splits (partials summed by the last block of each (token group, expert tile))
 
 __global__ void __launch_bounds__(256) router_kernel(RouterArgs p) {
     __shared__ float Rs[kRouterE][kRouterK + 1];
     __shared__ float hs[kRouterT][kRouterK];
     __shared__ int last;
     const int ks = blockIdx.x, et = blockIdx.y, tg = blockIdx.z, tid = threadIdx.x;
-    const int t0 = tg * kRouterT, e0 = et * kRouterE;
+    const int KS = gridDim.x;  // K splits = H / 128
+    const int t0 = tg * kRouterT, e0 = et * kRouterE, kb = ks * kRouterK;
     const int nt = min(kRouterT, p.T - t0), ne = min(kRouterE, p.E - e0);
-    const int KS = gridDim.x;  // K splits: at most kRouterKS, fewer when H is small
-    const int kper = p.H / KS;
     const int tw = tid >> 5, el = tid & 31;  // warp w owns tokens w, w+8, w+16, w+24; lane = expert
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int i = tid; i < kRouterE * kRouterK; i += 256) {  // router weights do not depend on the previous kernel
+        const int e = i / kRouterK, k = i % kRouterK;
+        Rs[e][k] = e < ne ? p.R[static_cast<size_t>(e0 + e) * p.H + kb + k] : 0.0f;
+    }
     pdl_wait();
     pdl_launch_dependents();
-    for (int kb = ks * kper; kb < (ks + 1) * kper; kb += kRouterK) {
-        for (int i = tid; i < kRouterE * kRouterK; i += 256) {
-            const int e = i / kRouterK, k = i % kRouterK;
-            Rs[e][k] = e < ne ? p.R[static_cast<size_t>(e0 + e) * p.H + kb + k] : 0.0f;
-        }
-        for (int i = tid; i < kRouterT * kRouterK; i += 256) {
-            const int t = i / kRouterK, k = i % kRouterK;
-            hs[t][k] = t < nt ? __ldcg(p.s1 + static_cast<size_t>(t0 + t) * p.H + kb + k) * (1.0f + __bfloat162float(p.w[kb + k])) : 0.0f;
-        }
-        __syncthreads();
+    for (int i = tid; i < kRouterT * kRouterK; i += 256) {
+        const int t = i / kRouterK, k = i % kRouterK;
+        hs[t][k] = t < nt ? __ldcg(p.s1 + static_cast<size_t>(t0 + t) * p.H + kb + k) * (1.0f + __bfloat162float(p.w[kb + k])) : 0.0f;
+    }
+    __syncthreads();
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll 4
-        for (int k = 0; k < kRouterK; ++k) {
-            const float r = Rs[el][k];
+    for (int k = 0; k < kRouterK; ++k) {
+        const float r = Rs[el][k];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) acc[j] = fmaf(hs[tw + 8 * j][k], r, acc[j]);
-        }
-        __syncthreads();
+        for (int j = 0; j < 4; ++j) acc[j] = fmaf(hs[tw + 8 * j][k], r, acc[j]);
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -111,18 +106,47 @@ __global__ void __launch_bounds__(256) router_kernel(RouterArgs p) {
     __syncthreads();
     if (!last) return;
     __threadfence();
+    // per-token 1/rms: lane q sums parts q, q + 32, ...; all four tokens' loads are in flight together
+    float* rs_s = &hs[0][0];
+    {
+        float ss[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int q = el; q < p.ssq_parts; q += 32)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (tw + 8 * j < nt) ss[j] += __ldcg(p.ssq + q * p.T + t0 + tw + 8 * j);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss[j] += __shfl_xor_sync(0xffffffffu, ss[j], o);
+            if (el == 0 && tw + 8 * j < nt) {
+                rs_s[tw + 8 * j] = rsqrtf(ss[j] / p.H + p.eps);
+                if (et == 0) p.ssq[p.ssq_parts * p.T + t0 + tw + 8 * j] = ss[j];  // total, one value for the experts' GEMM
+            }
+        }
+    }
+    float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int s0 = 0; s0 < KS; s0 += 8) {  // KS is a multiple of 8; 32 loads in flight
+        float v[4][8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                v[j][i] = (tw + 8 * j < nt && el < ne)
+                              ? __ldcg(p.part + (static_cast<size_t>(s0 + i) * p.T + t0 + tw + 8 * j) * p.E + e0 + el)
+                              : 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sum[j] += v[j][i];
+    }
+    __syncwarp();
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const int t = tw + 8 * j;
         if (t < nt && el < ne) {
-            float sum = 0.0f;
-#pragma unroll 8
-            for (int s = 0; s < KS; ++s) sum += __ldcg(p.part + (static_cast<size_t>(s) * p.T + t0 + t) * p.E + e0 + el);
-            float ss = 0.0f;
-            for (int q = 0; q < p.ssq_parts; ++q) ss += __ldcg(p.ssq + q * p.T + t0 + t);
-            sum *= rsqrtf(ss / p.H + p.eps);
-            if (p.bias != nullptr) sum += p.bias[e0 + el];
-            p.logits[static_cast<size_t>(t0 + t) * p.E + e0 + el] = sum;
+            float o = sum[j] * rs_s[t];
+            if (p.bias != nullptr) o += p.bias[e0 + el];
+            p.logits[static_cast<size_t>(t0 + t) * p.E + e0 + el] = o;
         }
     }
     if (tid == 0) p.ticket[tg * gridDim.y + et] = 0;  // ready for the next call
@@ -204,8 +228,7 @@ extern "C" int msk_layer_front(const MskLayerFront* f, int* status, void* stream
     r.s1 = f->stream1, r.w = static_cast<const __nv_bfloat16*>(f->pre_expert_norm_w), r.ssq = f->ssq1;
     r.ssq_parts = (H + 127) / 128, r.eps = f->norm_eps, r.R = f->router_w, r.bias = f->router_bias;
     r.part = f->router_part, r.ticket = f->router_ticket, r.logits = f->logits, r.T = T, r.H = H, r.E = f->E;
-    int ks = kRouterKS;
-    while (H % (ks * kRouterK) != 0) ks /= 2;
+    const int ks = H / kRouterK;  // <= 64
     return launch1(router_kernel, dim3(ks, (f->E + kRouterE - 1) / kRouterE, (T + kRouterT - 1) / kRouterT), dim3(256), 0, s, 1, r);
 }
 
@@ -216,7 +239,8 @@ extern "C" int msk_layer_decode(const MskLayerParams* p, int* status, void* stre
     MskMoeParams m = p->moe;
     const MskLayerFront& f = p->front;
     m.x = f.xn1, m.ldx = f.H;
-    m.x_ssq = f.ssq1, m.x_ssq_parts = (f.H + 127) / 128, m.x_inv_dim = 1.0f / f.H, m.x_eps = f.norm_eps;
+    m.x_ssq = f.ssq1 + static_cast<size_t>((f.H + 127) / 128) * (f.B * f.L), m.x_ssq_parts = 1,  // the router's totals
+     m.x_inv_dim = 1.0f / f.H, m.x_eps = f.norm_eps;
     m.logits = f.logits, m.n_logits = f.E;
     m.T = f.B * f.L, m.H = f.H;
     m.resid = f.stream1, m.ldr = f.H;

@@ -580,7 +580,7 @@ struct MoeCombineArgs {
 // for the second pass.
 constexpr int kCombineThreads = 512;
 
-template <int ITERS>  // ITERS * 2048 >= H
+template <int ITERS, int KS>  // ITERS * 2048 >= H; KS = K splits of gemm 2 (0: any, rolled loop)
 __global__ void __launch_bounds__(kCombineThreads) moe_combine_kernel(MoeCombineArgs p) {
     __shared__ float red[kCombineThreads / 32][8];
     __shared__ float rnorm[8];
@@ -608,12 +608,29 @@ __global__ void __launch_bounds__(kCombineThreads) moe_combine_kernel(MoeCombine
 #pragma unroll
         for (int s = 0; s < 8; ++s) z[it][s] = make_float4(0, 0, 0, 0);
         if (d >= p.H) continue;
+        // every (slot, split) load is issued before any is used; a slot of another rank reads slot 0's row
+        // (valid memory) and is discarded
+        if constexpr (KS > 0) {
+            float4 ld[8][KS];
 #pragma unroll
-        for (int s = 0; s < 8; ++s) {
-            if (!local[s]) continue;
-            for (int k = 0; k < p.S; ++k) {
-                const float4 a = __ldcg(reinterpret_cast<const float4*>(p.yp + (static_cast<size_t>(k) * p.P + t * p.top_k + s) * p.H + d));
-                z[it][s].x += a.x, z[it][s].y += a.y, z[it][s].z += a.z, z[it][s].w += a.w;
+            for (int s = 0; s < 8; ++s)
+#pragma unroll
+                for (int k = 0; k < KS; ++k)
+                    ld[s][k] = __ldcg(reinterpret_cast<const float4*>(
+                        p.yp + (static_cast<size_t>(k) * p.P + t * p.top_k + (local[s] ? s : 0)) * p.H + d));
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+#pragma unroll
+                for (int k = 0; k < KS; ++k)
+                    if (local[s]) z[it][s].x += ld[s][k].x, z[it][s].y += ld[s][k].y, z[it][s].z += ld[s][k].z, z[it][s].w += ld[s][k].w;
+        } else {
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                if (!local[s]) continue;
+                for (int k = 0; k < p.S; ++k) {
+                    const float4 a = __ldcg(reinterpret_cast<const float4*>(p.yp + (static_cast<size_t>(k) * p.P + t * p.top_k + s) * p.H + d));
+                    z[it][s].x += a.x, z[it][s].y += a.y, z[it][s].z += a.z, z[it][s].w += a.w;
+                }
             }
         }
         const uint2 pw = *reinterpret_cast<const uint2*>(p.post_w + d);
@@ -815,8 +832,10 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
     c.post_w = static_cast<const __nv_bfloat16*>(q->post_norm_w), c.eps = q->post_eps, c.resid = q->resid, c.ldr = q->ldr;
     c.out = q->out, c.out_fp32 = q->out_fp32, c.ldo = q->ldo;
     c.out_copy = static_cast<__nv_bfloat16*>(q->out_copy), c.ldc = q->ldc;
-    if (q->H <= 2 * kCombineThreads * 4) return launch_pdl(moe_combine_kernel<2>, dim3(q->T), dim3(kCombineThreads), 0, s, 1, c);
-    return launch_pdl(moe_combine_kernel<4>, dim3(q->T), dim3(kCombineThreads), 0, s, 1, c);
+    if (q->H <= 2 * kCombineThreads * 4 && s2 == 1) return launch_pdl(moe_combine_kernel<2, 1>, dim3(q->T), dim3(kCombineThreads), 0, s, 1, c);
+    if (q->H <= 2 * kCombineThreads * 4 && s2 == 2) return launch_pdl(moe_combine_kernel<2, 2>, dim3(q->T), dim3(kCombineThreads), 0, s, 1, c);
+    if (q->H <= 2 * kCombineThreads * 4) return launch_pdl(moe_combine_kernel<2, 0>, dim3(q->T), dim3(kCombineThreads), 0, s, 1, c);
+    return launch_pdl(moe_combine_kernel<4, 0>, dim3(q->T), dim3(kCombineThreads), 0, s, 1, c);
 }
 
 // ---------------------------------------------------------------- routed experts without caller scratch

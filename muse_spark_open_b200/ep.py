@@ -96,8 +96,8 @@ class CudaOps:
         buf = layer.front(data, self.state, **self.tune)
         t, h = data["stream"].shape
         rows = self.buffer("rows", (t, row_bytes(h, self.n_experts)), torch.uint8)
-        abi.check(abi.lib().msk_ep_pack(abi.ptr(buf["xn1"]), abi.ptr(buf["logits"]), abi.ptr(buf["ssq1"]),
-                                        buf["ssq1"].shape[0], abi.ptr(rows), t, h, self.n_experts, abi.stream_ptr()),
+        abi.check(abi.lib().msk_ep_pack(abi.ptr(buf["xn1"]), abi.ptr(buf["logits"]), abi.ptr(buf["ssq1"][-1]),
+                                        1, abi.ptr(rows), t, h, self.n_experts, abi.stream_ptr()),
                   "msk_ep_pack")
         del C
         return rows, buf["stream1"]
