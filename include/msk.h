@@ -141,6 +141,7 @@ typedef struct {
     float x_inv_dim, x_eps;
     int32_t* topk_ids;          /* [T, top_k] global expert ids: input, or output when logits != NULL */
     float* topk_weights;        /* [T, top_k] */
+    int ld_topk;                /* ints (floats) between token rows of topk_ids / topk_weights; 0 = top_k */
     const float* logits;        /* optional [T, n_logits]: softmax -> top-k -> renormalise inside the GEMM CTAs */
     int n_logits;
     int ld_logits;              /* floats between token rows of logits; 0 = n_logits */
@@ -193,7 +194,7 @@ int msk_moe_forward_static(const MskMoeParams* p, int* status, void* stream);
  * Stands in for muse_decode_layer/submission.py `kernel_fn` (:3978-4038) on the op list the benchmark
  * names; `prepare` (same file) corresponds to msk_moe_pack plus buffer allocation by the caller.
  *
- * msk_layer_front runs everything up to the router logits (what an expert-parallel rank does before
+ * msk_layer_front runs everything up to the router's expert choice (what an expert-parallel rank does before
  * the token exchange); msk_layer_decode adds the experts and the second residual on one GPU.
  */
 typedef struct {
@@ -226,8 +227,11 @@ typedef struct {
     void* xn1;                     /* bf16 [T, H] expert input before its row scale */
     float* ssq1;                   /* fp32 [H/128 + 1, T]: per-128-column partial sums of squares, last row their total */
     float* router_part;            /* fp32 [H/128, T, E] */
-    int32_t* router_ticket;        /* int32 [ceil(T/32) * ceil(E/32)], zero before the first call */
+    int32_t* router_ticket;        /* int32 [ceil(T/32) * (ceil(E/32) + 1)], zero before the first call */
     float* logits;                 /* fp32 [T, E] */
+    int top_k;                     /* <= 8 */
+    int32_t* topk_ids;             /* int32 [T, top_k]: softmax -> top-k -> renormalise of the logits, written by */
+    float* topk_weights;           /* fp32 [T, top_k]    the router kernel's last block per 32 tokens */
     int attn_chunks, attn_stages, qkv_splits, o_splits;
     int pdl;                       /* also chain the first kernel to whatever precedes it */
 } MskLayerFront;
@@ -236,7 +240,7 @@ int msk_layer_front(const MskLayerFront* p, int* status, void* stream);
 
 typedef struct {
     MskLayerFront front;
-    MskMoeParams moe;              /* x, x_ssq, logits, resid, T, H are filled from `front` */
+    MskMoeParams moe;              /* x, x_ssq, topk_ids, topk_weights, top_k, resid, T, H are filled from `front` */
 } MskLayerParams;
 
 int msk_layer_decode(const MskLayerParams* p, int* status, void* stream);
@@ -244,13 +248,13 @@ int msk_layer_decode(const MskLayerParams* p, int* status, void* stream);
 /* ---------------------------------------------------------------- expert-parallel exchange helpers
  * The reference runs one GPU and states its collectives as identities (muse_decode_layer/reference.py:8-10,
  * :467 "the all-reduce: identity"); these kernels sit on either side of the real exchange that replaces
- * that identity: rows packed by msk_ep_pack are gathered to every rank (dispatch), each rank runs
+ * that identity: rows packed by msk_ep_pack (expert input, expert choice, row scale) are gathered to every rank (dispatch), each rank runs
  * msk_moe_forward over all tokens with its own experts, the FP32 partials go back to the tokens' home
  * ranks (combine) and msk_ep_reduce adds them to the residual in rank order.
  */
-int msk_ep_row_bytes(int H, int E);   /* 2H (x bf16) + 4E (logits fp32) + 16 (sum of squares, padding) */
-int msk_ep_pack(const void* xn, const float* logits, const float* ssq, int ssq_parts, void* rows, int T, int H, int E,
-                void* stream);
+int msk_ep_row_bytes(int H, int top_k); /* 2H (x bf16) + 4k ids + 4k weights (padded to 16) + 16 (sum of squares, padding) */
+int msk_ep_pack(const void* xn, const int32_t* topk_ids, const float* topk_weights, const float* ssq, int ssq_parts,
+                void* rows, int T, int H, int top_k, void* stream);
 int msk_ep_reduce(const float* stream1, const float* recv /* [ranks, T, H] */, int ranks, float* out, void* out_bf16,
                   int T, int H, void* stream);
 

@@ -64,7 +64,7 @@ def lib() -> C.CDLL:
         _lib.msk_layer_front.argtypes = [vp, vp, vp]
         _lib.msk_layer_decode.argtypes = [vp, vp, vp]
         _lib.msk_ep_row_bytes.argtypes = [ci, ci]
-        _lib.msk_ep_pack.argtypes = [vp, vp, vp, ci, vp, ci, ci, ci, vp]
+        _lib.msk_ep_pack.argtypes = [vp, vp, vp, vp, ci, vp, ci, ci, ci, vp]
         _lib.msk_ep_reduce.argtypes = [vp, vp, ci, vp, vp, ci, ci, vp]
     return _lib
 
@@ -144,7 +144,8 @@ class MoeParams(C.Structure):
     _fields_ = [
         ("x", C.c_void_p), ("ldx", C.c_int),
         ("x_ssq", C.c_void_p), ("x_ssq_parts", C.c_int), ("x_inv_dim", C.c_float), ("x_eps", C.c_float),
-        ("topk_ids", C.c_void_p), ("topk_weights", C.c_void_p), ("logits", C.c_void_p), ("n_logits", C.c_int),
+        ("topk_ids", C.c_void_p), ("topk_weights", C.c_void_p), ("ld_topk", C.c_int), ("logits", C.c_void_p),
+        ("n_logits", C.c_int),
         ("ld_logits", C.c_int), ("x_ssq_tstride", C.c_int),
         ("T", C.c_int), ("top_k", C.c_int), ("local_start", C.c_int), ("local_count", C.c_int),
         ("w13_packed", C.c_void_p), ("w2_packed", C.c_void_p), ("w13_gs", C.c_void_p), ("w2_gs", C.c_void_p),
@@ -168,7 +169,7 @@ class LayerFront(C.Structure):
         ("router_w", C.c_void_p), ("router_bias", C.c_void_p), ("E", C.c_int),
         ("xn0", C.c_void_p), ("ssq0", C.c_void_p), ("qkv", C.c_void_p), ("attn", C.c_void_p), ("stream1", C.c_void_p),
         ("xn1", C.c_void_p), ("ssq1", C.c_void_p), ("router_part", C.c_void_p), ("router_ticket", C.c_void_p),
-        ("logits", C.c_void_p),
+        ("logits", C.c_void_p), ("top_k", C.c_int), ("topk_ids", C.c_void_p), ("topk_weights", C.c_void_p),
         ("attn_chunks", C.c_int), ("attn_stages", C.c_int), ("qkv_splits", C.c_int), ("o_splits", C.c_int),
         ("pdl", C.c_int),
     ]

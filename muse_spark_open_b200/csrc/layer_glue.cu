@@ -7,6 +7,7 @@
 //                the H/128 partials in a fixed order, so ids are reproducible.
 #include "msk.h"
 #include "ptx.cuh"
+#include "route.cuh"
 
 namespace msk {
 
@@ -59,7 +60,10 @@ struct RouterArgs {
     const float* R;         // [E, H]
     const float* bias;      // [E] or null
     float* part;            // [KS, T, E]
-    int* ticket;            // [token groups]
+    int* ticket;            // [token groups x expert tiles] then [token groups]
+    int top_k;
+    int* ids_out;           // [T, top_k]
+    float* wts_out;
     float* logits;          // [T, E]
     int T, H, E;
 };
@@ -69,31 +73,51 @@ constexpr int kRouterT = 32;    // tokens per block
 constexpr int kRouterE = 32;    // experts per block
 
 __global__ void __launch_bounds__(256) router_kernel(RouterArgs p) {
-    __shared__ float Rs[kRouterE][kRouterK + 1];
-    __shared__ float hs[kRouterT][kRouterK];
+    __shared__ __align__(16) float Rs[kRouterE][kRouterK + 4];  // row stride 132 floats: 16-byte rows, no bank conflicts
+    __shared__ __align__(16) float hs[kRouterT][kRouterK];
     __shared__ int last;
     const int ks = blockIdx.x, et = blockIdx.y, tg = blockIdx.z, tid = threadIdx.x;
     const int KS = gridDim.x;  // K splits = H / 128
     const int t0 = tg * kRouterT, e0 = et * kRouterE, kb = ks * kRouterK;
     const int nt = min(kRouterT, p.T - t0), ne = min(kRouterE, p.E - e0);
     const int tw = tid >> 5, el = tid & 31;  // warp w owns tokens w, w+8, w+16, w+24; lane = expert
-    for (int i = tid; i < kRouterE * kRouterK; i += 256) {  // router weights do not depend on the previous kernel
-        const int e = i / kRouterK, k = i % kRouterK;
-        Rs[e][k] = e < ne ? p.R[static_cast<size_t>(e0 + e) * p.H + kb + k] : 0.0f;
+    // both tiles are 32 rows x 32 float4; thread -> rows tw, tw+8, tw+16, tw+24, float4 column el.  All four loads
+    // are issued before the first use; rows past the end re-read the last valid row and are zeroed.
+    {
+        float4 r[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)  // router weights do not depend on the previous kernel
+            r[j] = __ldg(reinterpret_cast<const float4*>(p.R + static_cast<size_t>(e0 + min(tw + 8 * j, ne - 1)) * p.H + kb) + el);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<float4*>(&Rs[tw + 8 * j][4 * el]) = tw + 8 * j < ne ? r[j] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     }
+    const uint2 wraw = __ldg(reinterpret_cast<const uint2*>(p.w + kb) + el);
+    const float w0 = 1.0f + bf16lo(wraw.x), w1 = 1.0f + bf16hi(wraw.x), w2 = 1.0f + bf16lo(wraw.y), w3 = 1.0f + bf16hi(wraw.y);
     pdl_wait();
     pdl_launch_dependents();
-    for (int i = tid; i < kRouterT * kRouterK; i += 256) {
-        const int t = i / kRouterK, k = i % kRouterK;
-        hs[t][k] = t < nt ? __ldcg(p.s1 + static_cast<size_t>(t0 + t) * p.H + kb + k) * (1.0f + __bfloat162float(p.w[kb + k])) : 0.0f;
+    {
+        float4 h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            h[j] = __ldcg(reinterpret_cast<const float4*>(p.s1 + static_cast<size_t>(t0 + min(tw + 8 * j, nt - 1)) * p.H + kb) + el);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<float4*>(&hs[tw + 8 * j][4 * el]) =
+                tw + 8 * j < nt ? make_float4(h[j].x * w0, h[j].y * w1, h[j].z * w2, h[j].w * w3) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     }
     __syncthreads();
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll 4
-    for (int k = 0; k < kRouterK; ++k) {
-        const float r = Rs[el][k];
+#pragma unroll 8
+    for (int k4 = 0; k4 < kRouterK / 4; ++k4) {
+        const float4 r = *reinterpret_cast<const float4*>(&Rs[el][4 * k4]);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[j] = fmaf(hs[tw + 8 * j][k], r, acc[j]);
+        for (int j = 0; j < 4; ++j) {
+            if (tw + 8 * j >= nt) break;  // warp-uniform
+            const float4 h = *reinterpret_cast<const float4*>(&hs[tw + 8 * j][4 * k4]);
+            acc[j] = fmaf(h.x, r.x, acc[j]), acc[j] = fmaf(h.y, r.y, acc[j]);
+            acc[j] = fmaf(h.z, r.z, acc[j]), acc[j] = fmaf(h.w, r.w, acc[j]);
+        }
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -150,6 +174,21 @@ __global__ void __launch_bounds__(256) router_kernel(RouterArgs p) {
         }
     }
     if (tid == 0) p.ticket[tg * gridDim.y + et] = 0;  // ready for the next call
+    // the last expert tile of this token group chooses the experts: a warp per token, 4 tokens per warp
+    __threadfence();
+    __syncthreads();
+    int* ticket2 = p.ticket + gridDim.z * gridDim.y + tg;
+    if (tid == 0) last = atomicAdd(ticket2, 1) == static_cast<int>(gridDim.y) - 1;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    for (int j = 0; j < 4; ++j) {
+        const int t = tw + 8 * j;
+        if (t < nt)
+            route_token(p.logits + static_cast<size_t>(t0 + t) * p.E, p.E, p.top_k, el, p.ids_out + (t0 + t) * p.top_k,
+                        p.wts_out + (t0 + t) * p.top_k);
+    }
+    if (tid == 0) *ticket2 = 0;
 }
 
 template <typename Kern, typename Args>
@@ -190,10 +229,12 @@ extern "C" int msk_layer_front(const MskLayerFront* f, int* status, void* stream
     using namespace msk;
     if (f == nullptr || !f->stream || !f->input_norm_w || !f->w_qkv || !f->w_o || !f->pre_expert_norm_w || !f->router_w ||
         !f->xn0 || !f->ssq0 || !f->qkv || !f->attn || !f->stream1 || !f->xn1 || !f->ssq1 || !f->router_part ||
-        !f->router_ticket || !f->logits)
+        !f->router_ticket || !f->logits || !f->topk_ids || !f->topk_weights)
         return MSK_ERR_INVALID;
     const int T = f->B * f->L, H = f->H, nqkv = (2 * f->Hq + 2 * f->Hkv) * f->d, no = f->Hq * f->d;
-    if (T < 1 || T > 256 || H % 1024 != 0 || H > 8192 || f->E < 1 || f->E > 256) return MSK_ERR_UNSUPPORTED;
+    if (T < 1 || T > 256 || H % 1024 != 0 || H > 8192 || f->E < 1 || f->E > 256 || f->top_k < 1 ||
+        f->top_k > 8 || f->top_k > f->E)
+        return MSK_ERR_UNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     int rc = launch_prep(f->stream, f->input_norm_w, f->xn0, f->ssq0, T, H, f->norm_eps, s, f->pdl);
     if (rc != 0) return rc;
@@ -228,6 +269,7 @@ extern "C" int msk_layer_front(const MskLayerFront* f, int* status, void* stream
     r.s1 = f->stream1, r.w = static_cast<const __nv_bfloat16*>(f->pre_expert_norm_w), r.ssq = f->ssq1;
     r.ssq_parts = (H + 127) / 128, r.eps = f->norm_eps, r.R = f->router_w, r.bias = f->router_bias;
     r.part = f->router_part, r.ticket = f->router_ticket, r.logits = f->logits, r.T = T, r.H = H, r.E = f->E;
+    r.top_k = f->top_k, r.ids_out = f->topk_ids, r.wts_out = f->topk_weights;
     const int ks = H / kRouterK;  // <= 64
     return launch1(router_kernel, dim3(ks, (f->E + kRouterE - 1) / kRouterE, (T + kRouterT - 1) / kRouterT), dim3(256), 0, s, 1, r);
 }
@@ -241,7 +283,7 @@ extern "C" int msk_layer_decode(const MskLayerParams* p, int* status, void* stre
     m.x = f.xn1, m.ldx = f.H;
     m.x_ssq = f.ssq1 + static_cast<size_t>((f.H + 127) / 128) * (f.B * f.L), m.x_ssq_parts = 1,  // the router's totals
      m.x_inv_dim = 1.0f / f.H, m.x_eps = f.norm_eps;
-    m.logits = f.logits, m.n_logits = f.E;
+    m.logits = nullptr, m.topk_ids = f.topk_ids, m.topk_weights = f.topk_weights, m.top_k = f.top_k, m.ld_topk = 0;
     m.T = f.B * f.L, m.H = f.H;
     m.resid = f.stream1, m.ldr = f.H;
     m.pdl = 1;

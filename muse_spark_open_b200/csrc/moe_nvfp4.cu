@@ -35,6 +35,7 @@
 
 #include "msk.h"
 #include "ptx.cuh"
+#include "route.cuh"
 #include "tmap.cuh"
 
 namespace msk {
@@ -51,6 +52,7 @@ constexpr int kMaxExperts = 256;
 constexpr int kMaxGroups = 320;
 constexpr int kIssuers = 4;         // MMA-issuing warps (one lane each); a single thread issues one tcgen05.mma per ~100 clk
 constexpr int kDqGroups = 2;        // dequant warp groups (4 warps each); group g takes the chunks with index = g (mod 2)
+static_assert(kNA == kIssuers && (kIssuers & (kIssuers - 1)) == 0, "an issuing warp per A slot");
 constexpr int kMoeThreads = (1 + kIssuers + 4 + 4 * kDqGroups) * 32;
 constexpr int kRouteThreads = kMoeThreads, kRouteWarps = kRouteThreads / 32;
 
@@ -138,6 +140,7 @@ struct RouteArgs {
     int* ids_out;         // published by CTA 0 when routing from logits
     float* wts_out;
     int T, top_k, local_start, local_count;
+    int ld_ids;           // ints (floats) between token rows of ids / wts
 };
 
 struct RouteTables {
@@ -153,45 +156,6 @@ struct RouteTables {
     float r_w[kRouteWarps][8];
 };
 
-// softmax -> top-k -> renormalise for one token, one warp.  Ties go to the lower expert id.
-__device__ void route_token(const float* logits, int n, int top_k, int lane, int* ids, float* wts) {
-    float v[8];
-    float mx = -3.0e38f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int e = lane + 32 * i;
-        v[i] = e < n ? __ldcg(logits + e) : -3.0e38f;
-        mx = fmaxf(mx, v[i]);
-    }
-    mx = warp_max(mx);
-    float sum = 0.0f;
-    int my_id = 0;
-    float my_p = 0.0f;
-    for (int k = 0; k < top_k; ++k) {
-        float best = -3.0e38f;
-        int bi = 0x7fffffff;
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-            if (v[i] > best) best = v[i], bi = lane + 32 * i;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ob > best || (ob == best && oi < bi)) best = ob, bi = oi;
-        }
-        const float pk = __expf(best - mx);
-        sum += pk;
-        if (lane == k) my_id = bi, my_p = pk;
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-            if (lane + 32 * i == bi) v[i] = -3.0e38f;
-    }
-    if (lane < top_k) {
-        ids[lane] = my_id;
-        wts[lane] = my_p / sum;
-    }
-}
-
 // Builds the tables from ids (or logits).  Called by all kRouteThreads threads of a CTA; the result is
 // the same in every CTA and every kernel (pure counting, no atomics): an expert's list is cut into
 // groups that different CTAs and kernels work on, so its order must not depend on who built it.
@@ -205,15 +169,15 @@ __device__ void build_routing(RouteTables& rt, const RouteArgs& a, int* status, 
             if (lane < a.top_k) {
                 rt.ids_s[t * a.top_k + lane] = static_cast<unsigned short>(rt.r_ids[warp][lane]);
                 if (blockIdx.x == 0 && a.ids_out != nullptr) {
-                    a.ids_out[t * a.top_k + lane] = rt.r_ids[warp][lane];
-                    a.wts_out[t * a.top_k + lane] = rt.r_w[warp][lane];
+                    a.ids_out[t * a.ld_ids + lane] = rt.r_ids[warp][lane];
+                    a.wts_out[t * a.ld_ids + lane] = rt.r_w[warp][lane];
                 }
             }
             __syncwarp();
         }
     } else {
         for (int i = tid; i < P; i += kRouteThreads) {
-            const int id = __ldcg(a.ids + i);
+            const int id = __ldcg(a.ids + (i / a.top_k) * a.ld_ids + i % a.top_k);
             rt.ids_s[i] = static_cast<unsigned short>(id < 0 || id > 65534 ? 65535 : id);
         }
     }
@@ -364,6 +328,8 @@ struct MoeGemmArgs {
     int* route_pub;    // gemm 1, CTA 0: [0] local pairs, [1] groups, [2 + r] pair of sorted row r
     float* outp;       // [S][T*top_k][R]
     int S;
+    int route_early;   // the routing input is final before the previous kernel ends
+    int share_chunks;  // 1: the issuing warps split every chunk's K steps (short units); 0: a warp per A slot
     int* status;
 };
 
@@ -390,16 +356,20 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
     }
     if (tid == 32) {
         // a ring stage (weight block + B tile) is free again when the 4 dequant warps have read the block and
-        // every issuing warp's MMAs that read the B tile have completed
-        for (int i = 0; i < kNRaw; ++i) mbar_init(smem_u32(&bar.raw_full[i]), 1), mbar_init(smem_u32(&bar.raw_empty[i]), 4 + kIssuers);
-        for (int i = 0; i < kNA; ++i) mbar_init(smem_u32(&bar.a_full[i]), 4), mbar_init(smem_u32(&bar.a_empty[i]), kIssuers);
+        // the MMAs that read the B tile (one issuing warp per chunk) have completed
+        for (int i = 0; i < kNRaw; ++i) mbar_init(smem_u32(&bar.raw_full[i]), 1), mbar_init(smem_u32(&bar.raw_empty[i]), 4 + (p.share_chunks ? kIssuers : 1));
+        for (int i = 0; i < kNA; ++i) mbar_init(smem_u32(&bar.a_full[i]), 4), mbar_init(smem_u32(&bar.a_empty[i]), p.share_chunks ? kIssuers : 1);
         for (int i = 0; i < 2; ++i) mbar_init(smem_u32(&bar.d_full[i]), kIssuers), mbar_init(smem_u32(&bar.d_empty[i]), 4);
         fence_mbar_init();
     }
     if (tid == 0) prefetch_tmap(&tm_b);
-    pdl_wait();  // routing, x and the gemm-1 activations come from the previous kernels
+    // The expert ids are complete before this kernel can start whenever its predecessor in the stream is one
+    // of this file's own kernels (gather, activation): those release their dependents only after their own
+    // wait on the kernel before them.  The tables are then built while the predecessor still runs.
+    if (p.route_early) build_routing(rt, p.route, p.status, where);
+    pdl_wait();  // x and the gemm-1 activations come from the previous kernels
     pdl_launch_dependents();
-    build_routing(rt, p.route, p.status, where);
+    if (!p.route_early) build_routing(rt, p.route, p.status, where);
     if (MODE == 1 && p.x_ssq != nullptr) {
         for (int t = tid; t < p.route.T; t += kMoeThreads) {
             float s = 0.0f;
@@ -445,9 +415,14 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
         }
         __syncwarp();
     } else if (warp <= kIssuers) {
-        // ------------------------------------------------ MMA issue: every issuing warp takes 2 of the 8 K steps of
-        // every chunk (so an A slot in TMEM is free again after 2 issue times, not 8) and adds them into its own
-        // accumulator; the epilogue adds the four.
+        // ------------------------------------------------ MMA issue.  One thread issues an MMA per ~110 cycles, so
+        // four threads share the work, each into its own accumulator; the epilogue adds the accumulators.
+        //   long units:  issuing warp w owns A slot w, i.e. every chunk with (running chunk number) % 4 == w, and
+        //                issues its 8 K steps.  Owning a slot, a warp sees every phase of that slot's barrier in
+        //                order (a parity wait must never skip a phase).
+        //   short units (few tokens, many K splits): every warp issues 2 of the 8 K steps of every chunk, so a
+        //                chunk is through after 2 issue times instead of 8.
+        // a_full implies raw_full: the dequant warps waited for the stage before they wrote the A slot.
         if (lane == 0) {
             const int w = warp - 1;
             const uint32_t idesc = umma_idesc(128, kGroup, 1, 1, 0, 0);
@@ -459,16 +434,24 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d = tmem + kNA * 64 + (db * kIssuers + w) * kGroup;
+                bool first = true;
                 for (int c = 0; c < nch && ok; ++c, ++cc) {
+                    if (!p.share_chunks && cc % kNA != w) continue;
                     const int s = cc % kNRaw, as = cc % kNA;
-                    ok = mbar_wait(smem_u32(&bar.raw_full[s]), (cc / kNRaw) & 1, p.status, where | 5) &&
-                         mbar_wait(smem_u32(&bar.a_full[as]), (cc / kNA) & 1, p.status, where | 4);
+                    ok = mbar_wait(smem_u32(&bar.a_full[as]), (cc / kNA) & 1, p.status, where | 4);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t bb = base + s * kStage + kBlob + (w >> 1) * 4096;  // K steps 2w, 2w+1 sit in half w / 2
-                    const uint64_t bd = umma_smem_desc(bb, 16, 1024, kSwizzle128) + 4 * (w & 1);
-                    umma_f16_ts(d, tmem + as * 64 + 16 * w, bd, idesc, c != 0);
-                    umma_f16_ts(d, tmem + as * 64 + 16 * w + 8, bd + 2, idesc, 1);
+                    const uint64_t b0 = umma_smem_desc(base + s * kStage + kBlob, 16, 1024, kSwizzle128);
+                    if (p.share_chunks) {  // K steps 2w and 2w + 1
+                        const uint64_t bd = b0 + (w >> 1) * 256 + 4 * (w & 1);
+                        umma_f16_ts(d, tmem + as * 64 + 16 * w, bd, idesc, !first);
+                        umma_f16_ts(d, tmem + as * 64 + 16 * w + 8, bd + 2, idesc, 1);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            umma_f16_ts(d, tmem + as * 64 + 8 * j, b0 + (j < 4 ? 0 : 256) + 2 * (j & 3), idesc, !first || j != 0);
+                    }
+                    first = false;
                     umma_commit(smem_u32(&bar.a_empty[as]));
                     umma_commit(smem_u32(&bar.raw_empty[s]));
                 }
@@ -502,6 +485,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
             for (int c = 0; c < 32; ++c) v[c] = 0.0f;
 #pragma unroll
             for (int w = 0; w < kIssuers; ++w) {
+                if (!p.share_chunks && ((w - cc0) & (kIssuers - 1)) >= nch) continue;  // that warp had no chunk in this unit
                 uint32_t t[32];
                 const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + kNA * 64 + (db * kIssuers + w) * kGroup;
                 tmem_ld16(taddr, *reinterpret_cast<uint32_t(*)[16]>(&t[0]));
@@ -524,6 +508,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
         }
     } else {
         // ------------------------------------------------ dequant: codes + scales -> BF16 A operand in TMEM
+        // (all 8 warps on the same chunk was measured slower: the per-chunk handshakes then cost every warp)
         const int quarter = warp & 3, grp = (warp - (kIssuers + 5)) >> 2, row = quarter * 32 + lane;
         int cc = 0;
         bool ok = true;
@@ -563,7 +548,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
 struct MoeCombineArgs {
     const int* ids;
     const float* wts;
-    int top_k, local_start, local_count, H, S, P;
+    int top_k, local_start, local_count, H, S, P, ld_ids;
     const float* yp;            // [S][P][H]
     const __nv_bfloat16* post_w;
     float eps;
@@ -593,9 +578,9 @@ __global__ void __launch_bounds__(kCombineThreads) moe_combine_kernel(MoeCombine
     for (int s = 0; s < 8; ++s) {
         local[s] = 0, w[s] = 0.0f;
         if (s < p.top_k) {
-            const int e = __ldcg(p.ids + t * p.top_k + s) - p.local_start;
+            const int e = __ldcg(p.ids + t * p.ld_ids + s) - p.local_start;
             local[s] = e >= 0 && e < p.local_count;
-            w[s] = __ldcg(p.wts + t * p.top_k + s);
+            w[s] = __ldcg(p.wts + t * p.ld_ids + s);
         }
     }
     float4 z[ITERS][8];
@@ -783,6 +768,7 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
     ra.ids = q->topk_ids, ra.logits = q->logits, ra.n_logits = q->n_logits;
     ra.ld_logits = q->ld_logits > 0 ? q->ld_logits : q->n_logits;
     ra.ids_out = q->topk_ids, ra.wts_out = q->topk_weights;
+    ra.ld_ids = q->ld_topk > 0 ? q->ld_topk : q->top_k;
     ra.T = q->T, ra.top_k = q->top_k, ra.local_start = q->local_start, ra.local_count = q->local_count;
 
     // B operands by TMA: gemm 1 reads x itself (<= 32 tokens) or its rows gathered in expert-list order;
@@ -808,6 +794,8 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
     a.x_ssq = q->x_ssq, a.x_ssq_parts = q->x_ssq_parts, a.x_inv_dim = q->x_inv_dim, a.x_eps = q->x_eps;
     a.x_ssq_ts = q->x_ssq_tstride > 0 ? q->x_ssq_tstride : 1;
     a.route_pub = q->route_pub, a.outp = q->h1_part, a.S = s1, a.status = status;
+    a.route_early = !direct && q->logits == nullptr;  // the gather kernel precedes
+    a.share_chunks = q->T <= 4;
     rc = launch_pdl2(moe_gemm_kernel<1>, dim3(sms), dim3(kMoeThreads), smem, s, pdl, tm_b1, a);
     if (rc != 0) return rc;
 
@@ -823,11 +811,14 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
     b.route.ids_out = nullptr, b.route.wts_out = nullptr;
     b.wpacked = static_cast<const uint8_t*>(q->w2_packed), b.gs = q->w2_gs, b.R = q->H, b.K = q->I, b.direct = 0;
     b.outp = q->y_part, b.S = s2, b.status = status;
+    b.route_early = 1;  // the activation kernel precedes
+    b.share_chunks = a.share_chunks;
     rc = launch_pdl2(moe_gemm_kernel<2>, dim3(sms), dim3(kMoeThreads), smem, s, 1, tm_b2, b);
     if (rc != 0) return rc;
 
     MoeCombineArgs c{};
     c.ids = q->topk_ids, c.wts = q->topk_weights, c.top_k = q->top_k, c.local_start = q->local_start;
+    c.ld_ids = ra.ld_ids;
     c.local_count = q->local_count, c.H = q->H, c.S = s2, c.P = P, c.yp = q->y_part;
     c.post_w = static_cast<const __nv_bfloat16*>(q->post_norm_w), c.eps = q->post_eps, c.resid = q->resid, c.ldr = q->ldr;
     c.out = q->out, c.out_fp32 = q->out_fp32, c.ldo = q->ldo;

@@ -118,6 +118,10 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
         ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
         : "memory");
 }
+// Untiled bulk prefetch global -> L2 (fire and forget): address 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 // 16-byte asynchronous copy (generic proxy) and its mbarrier hook.
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");

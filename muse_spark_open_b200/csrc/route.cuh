@@ -1,0 +1,56 @@
+// Expert choice of one token by one warp: softmax -> top-k -> renormalise (the routing rule of the
+// reference's MoE layer: models/moe.py).  Shared by the router kernel and the experts' GEMM.
+#pragma once
+#include <cstdint>
+
+#include "ptx.cuh"
+
+namespace msk {
+
+// order-preserving map float -> uint32 (larger float <=> larger integer)
+__device__ __forceinline__ uint32_t float_ordered(float f) {
+    const uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float ordered_float(uint32_t o) {
+    return __uint_as_float((o & 0x80000000u) ? (o & 0x7fffffffu) : ~o);
+}
+
+// logits[0..n), n <= 256.  Lanes 0..top_k-1 write ids[lane] (global expert id) and wts[lane] (probability,
+// renormalised over the chosen).  Ties go to the lower expert id.  Two warp reductions per choice.
+__device__ __forceinline__ void route_token(const float* logits, int n, int top_k, int lane, int* ids, float* wts) {
+    uint32_t v[8];
+    uint32_t mxo = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int e = lane + 32 * i;
+        v[i] = e < n ? float_ordered(__ldcg(logits + e)) : 0u;
+        mxo = max(mxo, v[i]);
+    }
+    const float mx = ordered_float(__reduce_max_sync(0xffffffffu, mxo));
+    float sum = 0.0f, my_p = 0.0f;
+    int my_id = 0;
+    for (int k = 0; k < top_k; ++k) {
+        uint32_t best = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) best = max(best, v[i]);
+        best = __reduce_max_sync(0xffffffffu, best);
+        int cand = 0x7fffffff;  // this lane's lowest expert id holding the maximum
+#pragma unroll
+        for (int i = 7; i >= 0; --i)
+            if (v[i] == best) cand = lane + 32 * i;
+        const int bi = __reduce_min_sync(0xffffffffu, cand);
+        const float pk = __expf(ordered_float(best) - mx);
+        sum += pk;
+        if (lane == k) my_id = bi, my_p = pk;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (lane + 32 * i == bi) v[i] = 0u;
+    }
+    if (lane < top_k) {
+        ids[lane] = my_id;
+        wts[lane] = my_p / sum;
+    }
+}
+
+}  // namespace msk

@@ -5,15 +5,15 @@ Partition (the benchmark's multi-GPU config): requests are data-parallel, rank g
 [g*E/G, (g+1)*E/G); dense weights and the router are replicated.  The reference has no collective (its
 all-reduces are identities, muse_decode_layer/reference.py:8-10,467); here the exchange is real:
 
-  front      (local tokens)   norms, QKV, attention, o_proj, residual, router logits
-  dispatch   every local token's row (x bf16 | logits fp32 | sum of squares) goes to every rank, fixed
+  front      (local tokens)   norms, QKV, attention, o_proj, residual, router (logits, softmax, top-8)
+  dispatch   every local token's row (x bf16 | expert ids | weights | sum of squares) goes to every rank, fixed
              capacity T_local rows per peer: sizes are static, nothing depends on the routing, so the
              step never syncs with the host and every rank posts the same collectives in the same order.
              With dense fixed-capacity rows an all-to-all and an all-gather move the same bytes; NCCL's
              all-gather is used.
-  experts    each rank runs the grouped GEMMs over all T tokens; the routing (softmax, top-8) is
-             recomputed inside the GEMM CTAs from the gathered logits and only pairs of local experts
-             are touched; a token with no local expert yields a zero row.
+  experts    each rank runs the grouped GEMMs over all T tokens; the GEMM CTAs build their routing tables
+             from the gathered expert ids and only pairs of local experts are touched; a token with no
+             local expert yields a zero row.
   combine    all-to-all (NCCL): rank g sends rank h the FP32 partial rows of h's tokens.
   reduce     home rank adds the G partials to the residual in rank order (bitwise reproducible).
 
@@ -35,18 +35,21 @@ def shard(n: int, world: int, rank: int) -> tuple[int, int]:
     return rank * (n // world), n // world
 
 
-def row_bytes(hidden: int, n_experts: int) -> int:
-    """Bytes of one dispatched token row: x bf16 [H] | logits fp32 [E] | sum of squares fp32 + padding."""
-    return 2 * hidden + 4 * n_experts + 16
+def row_bytes(hidden: int, top_k: int = TOP_K) -> int:
+    """Bytes of one dispatched token row: x bf16 [H] | ids int32 [k] | weights fp32 [k] | pad to 16 |
+    sum of squares fp32 + padding."""
+    return 2 * hidden + ((8 * top_k + 15) & ~15) + 16
 
 
-def row_views(rows: torch.Tensor, hidden: int, n_experts: int):
-    """Strided views (x bf16 [T, H], logits fp32 [T, E], ssq fp32 [T]) into a uint8 [T, row_bytes] buffer."""
+def row_views(rows: torch.Tensor, hidden: int, top_k: int = TOP_K):
+    """Strided views (x bf16 [T, H], ids int32 [T, k], weights fp32 [T, k], ssq fp32 [T]) into a uint8
+    [T, row_bytes] buffer."""
     t = rows.shape[0]
     rb = rows.shape[1]
     x = rows.view(torch.bfloat16).view(t, rb // 2)[:, :hidden]
     f = rows.view(torch.float32).view(t, rb // 4)
-    return x, f[:, hidden // 2: hidden // 2 + n_experts], f[:, hidden // 2 + n_experts]
+    i = rows.view(torch.int32).view(t, rb // 4)
+    return x, i[:, hidden // 2: hidden // 2 + top_k], f[:, hidden // 2 + top_k: hidden // 2 + 2 * top_k], f[:, rb // 4 - 4]
 
 
 def step(data: dict, ops, group=None):
@@ -95,9 +98,9 @@ class CudaOps:
         from . import abi, layer
         buf = layer.front(data, self.state, **self.tune)
         t, h = data["stream"].shape
-        rows = self.buffer("rows", (t, row_bytes(h, self.n_experts)), torch.uint8)
-        abi.check(abi.lib().msk_ep_pack(abi.ptr(buf["xn1"]), abi.ptr(buf["logits"]), abi.ptr(buf["ssq1"][-1]),
-                                        1, abi.ptr(rows), t, h, self.n_experts, abi.stream_ptr()),
+        rows = self.buffer("rows", (t, row_bytes(h)), torch.uint8)
+        abi.check(abi.lib().msk_ep_pack(abi.ptr(buf["xn1"]), abi.ptr(buf["topk_ids"]), abi.ptr(buf["topk_weights"]),
+                                        abi.ptr(buf["ssq1"][-1]), 1, abi.ptr(rows), t, h, TOP_K, abi.stream_ptr()),
                   "msk_ep_pack")
         del C
         return rows, buf["stream1"]
@@ -107,11 +110,9 @@ class CudaOps:
         t = gathered.shape[0]
         ms = self.state["moe"]
         h = ms["H"]
-        x, logits, ssq = row_views(gathered, h, self.n_experts)
-        ids = self.buffer("ids", (t, TOP_K), torch.int32)
-        wts = self.buffer("wts", (t, TOP_K), torch.float32)
+        x, ids, wts, ssq = row_views(gathered, h)
         out = self.buffer("partial", (t, h), torch.float32)
-        moe.forward(x, ids, wts, ms, self.state["local_start"], self.state["local_count"], out=out, logits=logits,
+        moe.forward(x, ids, wts, ms, self.state["local_start"], self.state["local_count"], out=out,
                     pre_norm=(ssq, h, layer.RMS_EPS), splits=self.tune.get("moe_splits"), pdl=True)
         return out, ids
 

@@ -51,8 +51,8 @@ def buffers(state: dict, t: int, device) -> dict:
             "xn0": mk((t, h), bf), "ssq0": mk((t,), f32), "qkv": mk((t, nqkv), bf), "attn": mk((t, no), bf),
             "stream1": mk((t, h), f32), "xn1": mk((t, h), bf), "ssq1": mk((h // 128 + 1, t), f32),
             "router_part": mk((h // 128, t, e), f32),
-            "router_ticket": torch.zeros((((t + 31) // 32) * ((e + 31) // 32),), dtype=torch.int32, device=device),
-            "logits": mk((t, e), f32), "topk_w": mk((t, TOP_K), f32),
+            "router_ticket": torch.zeros((((t + 31) // 32) * ((e + 31) // 32 + 1),), dtype=torch.int32, device=device),
+            "logits": mk((t, e), f32), "topk_ids": mk((t, TOP_K), torch.int32), "topk_weights": mk((t, TOP_K), f32),
         }
     return state["bufs"][t]
 
@@ -73,14 +73,16 @@ def fill_front(f: abi.LayerFront, data: dict, state: dict, buf: dict, tune: dict
     f.pre_expert_norm_w, f.router_w = abi.ptr(state["pre_expert_norm"]), abi.ptr(state["router"])
     f.router_bias = abi.ptr(state["router_bias"]) if state["router_bias"] is not None else None
     f.E = state["E"]
-    for name in ("xn0", "ssq0", "qkv", "attn", "stream1", "xn1", "ssq1", "router_part", "router_ticket", "logits"):
+    for name in ("xn0", "ssq0", "qkv", "attn", "stream1", "xn1", "ssq1", "router_part", "router_ticket", "logits",
+                 "topk_ids", "topk_weights"):
         setattr(f, name, abi.ptr(buf[name]))
+    f.top_k = TOP_K
     f.attn_chunks, f.attn_stages = tune.get("attn_chunks", 0), tune.get("attn_stages", 0)
     f.qkv_splits, f.o_splits, f.pdl = tune.get("qkv_splits", 0), tune.get("o_splits", 0), 0
 
 
 def front(data: dict, state: dict, **tune) -> dict:
-    """Everything up to the router logits (the part an expert-parallel rank runs before the exchange)."""
+    """Everything up to the router's expert choice (the part an expert-parallel rank runs before the exchange)."""
     t = data["config"]["batch"] * data["config"]["q_len"]
     buf = buffers(state, t, data["stream"].device)
     f = abi.LayerFront()
@@ -104,8 +106,8 @@ def kernel_fn(data: dict, state: dict, **tune):
     ids = torch.empty((t, TOP_K), dtype=torch.int32, device=stream.device)
     p = abi.LayerParams()
     fill_front(p.front, data, state, buf, tune)
+    p.front.topk_ids = abi.ptr(ids)
     m = p.moe
-    m.topk_ids, m.topk_weights, m.top_k = abi.ptr(ids), abi.ptr(buf["topk_w"]), TOP_K
     m.local_start, m.local_count = state["local_start"], state["local_count"]
     m.w13_packed, m.w2_packed = abi.ptr(ms["w13"]), abi.ptr(ms["w2"])
     m.w13_gs, m.w2_gs = abi.ptr(ms["w13_gs"]), abi.ptr(ms["w2_gs"])

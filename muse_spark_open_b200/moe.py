@@ -82,7 +82,9 @@ def forward(x, ids, wts, state, local_start, local_count, out=None, logits=None,
         ssq, dim, eps = pre_norm  # [parts, T] contiguous, or one value per token with any stride
         p.x_ssq, p.x_inv_dim, p.x_eps = abi.ptr(ssq), 1.0 / dim, eps
         p.x_ssq_parts, p.x_ssq_tstride = (ssq.shape[0], 1) if ssq.dim() == 2 else (1, ssq.stride(0))
-    p.topk_ids, p.topk_weights = abi.ptr(ids), abi.ptr(wts)
+    if ids.stride(0) != wts.stride(0) or ids.stride(1) != 1 or wts.stride(1) != 1:
+        raise abi.MskError("topk_ids and topk_weights need the same row stride and unit column stride")
+    p.topk_ids, p.topk_weights, p.ld_topk = abi.ptr(ids), abi.ptr(wts), ids.stride(0)
     if logits is not None:
         p.logits, p.n_logits, p.ld_logits = abi.ptr(logits), logits.shape[1], logits.stride(0)
     p.T, p.top_k = t, top_k

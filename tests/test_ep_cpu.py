@@ -27,19 +27,22 @@ class OracleOps:
         fr = olayer.front(data, self.w)
         s1 = fr["stream1"]
         t = s1.shape[0]
-        rows = torch.zeros((t, self.ep.row_bytes(HID, NEXP)), dtype=torch.uint8)
-        x, lg, ssq = self.ep.row_views(rows, HID, NEXP)
+        from oracle import moe as omoe
+        rows = torch.zeros((t, self.ep.row_bytes(HID)), dtype=torch.uint8)
+        x, ids, wts, ssq = self.ep.row_views(rows, HID)
         # the row carries the already normalised expert input and a sum of squares that makes the
         # receiver's row scale exactly 1, so this stand-in rounds to BF16 where the oracle does
         x.copy_(fr["h"].to(torch.bfloat16))
-        lg.copy_(fr["logits"])
+        top_ids, top_w = omoe.route_softmax(fr["logits"])
+        ids.copy_(top_ids)
+        wts.copy_(top_w)
         ssq.fill_(HID * (1.0 - 1e-5))
         return rows, s1
 
     def experts(self, gathered):
         from oracle import moe as omoe
-        x, lg, ssq = self.ep.row_views(gathered, HID, NEXP)
-        ids, wts = omoe.route_softmax(lg)
+        x, ids, wts, ssq = self.ep.row_views(gathered, HID)
+        ids, wts = ids.contiguous(), wts.contiguous()
         h = (x.float() * torch.rsqrt(ssq.double() / HID + 1e-5).float()[:, None]).to(torch.bfloat16)
         md = {"hidden_states": h, "topk_ids": ids, "topk_weights": wts,
               "config": {"local_start": self.first, "local_count": self.count}}
@@ -90,10 +93,11 @@ def test_ep_step_two_cpu_ranks_matches_unsharded_oracle():
 def test_shard_and_row_layout():
     from muse_spark_open_b200 import ep
     assert ep.shard(128, 8, 3) == (48, 16)
-    assert ep.row_bytes(4096, 128) == 8192 + 512 + 16 and ep.row_bytes(4096, 128) % 16 == 0
-    rows = torch.zeros((3, ep.row_bytes(64, 8)), dtype=torch.uint8)
-    x, lg, ssq = ep.row_views(rows, 64, 8)
-    x.fill_(1.0), lg.fill_(2.0), ssq.fill_(3.0)
-    assert x.shape == (3, 64) and lg.shape == (3, 8) and ssq.shape == (3,)
+    assert ep.row_bytes(4096) == 8192 + 64 + 16 and ep.row_bytes(4096, 3) == 8192 + 32 + 16
+    rows = torch.zeros((3, ep.row_bytes(64)), dtype=torch.uint8)
+    x, ids, wts, ssq = ep.row_views(rows, 64)
+    x.fill_(1.0), ids.fill_(7), wts.fill_(2.0), ssq.fill_(3.0)
+    assert x.shape == (3, 64) and ids.shape == (3, 8) and wts.shape == (3, 8) and ssq.shape == (3,)
     raw = rows.view(torch.float32).view(3, -1)
-    assert (raw[:, 32:40] == 2.0).all() and (raw[:, 40] == 3.0).all() and (raw[:, 41:] == 0).all()
+    assert (rows.view(torch.int32).view(3, -1)[:, 32:40] == 7).all() and (raw[:, 40:48] == 2.0).all()
+    assert (raw[:, 48] == 3.0).all() and (raw[:, 49:] == 0).all()
