@@ -45,14 +45,17 @@ constexpr int kBlobScales = 8192;  // offset of the 128 x 8 block scales inside 
 constexpr int kBSlot = 8192;       // B tile of one stage: 32 rows x 256 bytes (two 128-byte-swizzled halves)
 constexpr int kStage = kBlob + kBSlot;
 constexpr int kNRaw = 11;          // ring stages (weight block + B tile)
+// nanoseconds a waiting warp of each role sleeps between polls (the dequant warps, which bound the rate, poll)
+constexpr int kSleepProducer = 200, kSleepIssuer = 40, kSleepEpilogue = 400;
 constexpr int kNA = 4;             // A slots in tensor memory, 64 columns each
 constexpr int kGroup = 32;         // pairs per expert-group (UMMA N)
 constexpr int kMaxPairs = 2048;
 constexpr int kMaxExperts = 256;
 constexpr int kMaxGroups = 320;
 constexpr int kIssuers = 4;         // MMA-issuing warps (one lane each); a single thread issues one tcgen05.mma per ~100 clk
-constexpr int kDqGroups = 2;        // dequant warp groups (4 warps each); group g takes the chunks with index = g (mod 2)
-static_assert(kNA == kIssuers && (kIssuers & (kIssuers - 1)) == 0, "an issuing warp per A slot");
+constexpr int kDqGroups = 4;        // dequant warp groups (4 warps each); group g takes the chunks with index = g (mod 4)
+static_assert(kNA == kIssuers && kNA == kDqGroups && (kIssuers & (kIssuers - 1)) == 0,
+              "A slot g is written by dequant group g and read by issuing warp g: both see every phase of its barriers");
 constexpr int kMoeThreads = (1 + kIssuers + 4 + 4 * kDqGroups) * 32;
 constexpr int kRouteThreads = kMoeThreads, kRouteWarps = kRouteThreads / 32;
 
@@ -394,22 +397,21 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
     if (warp == 0) {
         // ------------------------------------------------ producer: weight block (bulk copy) + B tile (2 TMA boxes)
         if (lane == 0) {
-            int cc = 0;
+            int cc = 0, s = 0, sph = 1;  // stage and the parity of its previous use
             bool ok = true;
             for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
                 const int g = u / per_group, rem = u % per_group, tile = rem / p.S, ks = rem % p.S;
                 const uint8_t* src = p.wpacked + ((static_cast<size_t>(rt.g_expert[g]) * tiles + tile) * KC + ks * nch) * kBlob;
                 const int row0 = p.direct ? 0 : rt.g_off[g];
-                for (int c = 0; c < nch; ++c, ++cc) {
-                    const int s = cc % kNRaw;
-                    if (cc >= kNRaw) ok = mbar_wait(smem_u32(&bar.raw_empty[s]), ((cc / kNRaw) - 1) & 1, p.status, where | 2);
+                int kg = ks * nch * 2;  // 64-column group of the B operand
+                for (int c = 0; c < nch; ++c, ++cc, src += kBlob, kg += 2) {
+                    if (cc >= kNRaw) ok = mbar_wait<kSleepProducer>(smem_u32(&bar.raw_empty[s]), sph, p.status, where | 2);
                     if (!ok) break;
                     const uint32_t full = smem_u32(&bar.raw_full[s]), dst = base + s * kStage;
-                    const int k0 = (ks * nch + c) * 128;
                     mbar_expect_tx(full, kStage);
-                    bulk_load(dst, src + static_cast<size_t>(c) * kBlob, kBlob, full);
-                    tma_load_2d(dst + kBlob, &tm_b, full, k0, row0);
-                    tma_load_2d(dst + kBlob + 4096, &tm_b, full, k0 + 64, row0);
+                    bulk_load(dst, src, kBlob, full);
+                    tma_load_3d(dst + kBlob, &tm_b, full, 0, row0, kg);
+                    if (++s == kNRaw) s = 0, sph ^= 1;
                 }
             }
         }
@@ -430,7 +432,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
             bool ok = true;
             for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++uc) {
                 const int db = uc & 1;
-                if (uc >= 2) ok = mbar_wait(smem_u32(&bar.d_empty[db]), ((uc >> 1) - 1) & 1, p.status, where | 3);
+                if (uc >= 2) ok = mbar_wait<kSleepIssuer>(smem_u32(&bar.d_empty[db]), ((uc >> 1) - 1) & 1, p.status, where | 3);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d = tmem + kNA * 64 + (db * kIssuers + w) * kGroup;
@@ -438,7 +440,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
                 for (int c = 0; c < nch && ok; ++c, ++cc) {
                     if (!p.share_chunks && cc % kNA != w) continue;
                     const int s = cc % kNRaw, as = cc % kNA;
-                    ok = mbar_wait(smem_u32(&bar.a_full[as]), (cc / kNA) & 1, p.status, where | 4);
+                    ok = mbar_wait<kSleepIssuer>(smem_u32(&bar.a_full[as]), (cc / kNA) & 1, p.status, where | 4);
                     if (!ok) break;
                     tc_fence_after();
                     const uint64_t b0 = umma_smem_desc(base + s * kStage + kBlob, 16, 1024, kSwizzle128);
@@ -477,47 +479,53 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
                 mypair = rt.list[off + lane];
             }
             const float myscale = (MODE == 1 && p.x_ssq != nullptr && mypair >= 0) ? rs_s[mypair / p.route.top_k] : 1.0f;
-            ok = mbar_wait(smem_u32(&bar.d_full[db]), (uc >> 1) & 1, p.status, where | 6);
+            ok = mbar_wait<kSleepEpilogue>(smem_u32(&bar.d_full[db]), (uc >> 1) & 1, p.status, where | 6);
             if (!ok) break;
             tc_fence_after();
-            float v[32];
-#pragma unroll
-            for (int c = 0; c < 32; ++c) v[c] = 0.0f;
-#pragma unroll
-            for (int w = 0; w < kIssuers; ++w) {
-                if (!p.share_chunks && ((w - cc0) & (kIssuers - 1)) >= nch) continue;  // that warp had no chunk in this unit
-                uint32_t t[32];
-                const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + kNA * 64 + (db * kIssuers + w) * kGroup;
-                tmem_ld16(taddr, *reinterpret_cast<uint32_t(*)[16]>(&t[0]));
-                tmem_ld16(taddr + 16, *reinterpret_cast<uint32_t(*)[16]>(&t[16]));
-                tmem_wait_ld();
-#pragma unroll
-                for (int c = 0; c < 32; ++c) v[c] += __uint_as_float(t[c]);
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar.d_empty[db]));
             const float scale = __ldg(p.gs + e) * 67108864.0f;  // global scale * 2^26
             float* dst = p.outp + (static_cast<size_t>(ks) * P) * p.R + tile * 128 + row;
 #pragma unroll
-            for (int c = 0; c < kGroup; ++c) {
-                const int pr = __shfl_sync(0xffffffffu, mypair, c);
-                const float sc = __shfl_sync(0xffffffffu, myscale, c);
-                if (pr >= 0) dst[static_cast<size_t>(pr) * p.R] = v[c] * scale * sc;
+            for (int h = 0; h < kGroup / 16; ++h) {  // 16 accumulator columns at a time (register budget)
+                float v[16];
+#pragma unroll
+                for (int c = 0; c < 16; ++c) v[c] = 0.0f;
+#pragma unroll
+                for (int w = 0; w < kIssuers; ++w) {
+                    if (!p.share_chunks && ((w - cc0) & (kIssuers - 1)) >= nch) continue;  // that warp had no chunk in this unit
+                    uint32_t t[16];
+                    tmem_ld16(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + kNA * 64 + (db * kIssuers + w) * kGroup + h * 16, t);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) v[c] += __uint_as_float(t[c]);
+                }
+                if (h == kGroup / 16 - 1) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bar.d_empty[db]));
+                }
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    const int pr = __shfl_sync(0xffffffffu, mypair, h * 16 + c);
+                    const float sc = __shfl_sync(0xffffffffu, myscale, h * 16 + c);
+                    if (pr >= 0) dst[static_cast<size_t>(pr) * p.R] = v[c] * scale * sc;
+                }
             }
         }
     } else {
         // ------------------------------------------------ dequant: codes + scales -> BF16 A operand in TMEM
         // (all 8 warps on the same chunk was measured slower: the per-chunk handshakes then cost every warp)
         const int quarter = warp & 3, grp = (warp - (kIssuers + 5)) >> 2, row = quarter * 32 + lane;
-        int cc = 0;
+        // the dequant warps do not care about unit boundaries: group g takes chunks g, g + 2, ... of this CTA's
+        // stream; stage, slot and their phases are stepped, not divided
+        const int my_units = blockIdx.x < n_units ? (n_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        const int total = my_units * nch;
         bool ok = true;
-        for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-            for (int c = 0; c < nch; ++c, ++cc) {
-                if (cc % kDqGroups != grp) continue;
-                const int s = cc % kNRaw, as = cc % kNA;
-                ok = mbar_wait(smem_u32(&bar.raw_full[s]), (cc / kNRaw) & 1, p.status, where | 7);
-                if (ok && cc >= kNA) ok = mbar_wait(smem_u32(&bar.a_empty[as]), ((cc / kNA) - 1) & 1, p.status, where | 8);
+        int s = grp % kNRaw, sph = 0, aph = 0;
+        const int as = grp;  // this group's A slot
+        for (int cc = grp; cc < total && ok; cc += kDqGroups) {
+            {
+                ok = mbar_wait(smem_u32(&bar.raw_full[s]), sph, p.status, where | 7);
+                if (ok && cc >= kNA) ok = mbar_wait(smem_u32(&bar.a_empty[as]), aph ^ 1, p.status, where | 8);
                 if (!ok) break;
                 tc_fence_after();
                 const uint8_t* raw = gbase + s * kStage;
@@ -536,6 +544,9 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bar.a_full[as]));
+                s += kDqGroups;
+                if (s >= kNRaw) s -= kNRaw, sph ^= 1;
+                aph ^= 1;
             }
         }
     }
@@ -774,9 +785,9 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
     // B operands by TMA: gemm 1 reads x itself (<= 32 tokens) or its rows gathered in expert-list order;
     // gemm 2 reads the activations the act kernel writes in that same order.  Box = 32 rows x 64 k.
     CUtensorMap tm_b1, tm_b2;
-    int rc = direct ? make_tmap_bf16_2d(&tm_b1, q->x, q->T, q->H, q->ldx, kGroup)
-                    : make_tmap_bf16_2d(&tm_b1, q->x_sorted, P, q->H, q->H, kGroup);
-    if (rc == 0) rc = make_tmap_bf16_2d(&tm_b2, q->inter_sorted, P, q->I, q->I, kGroup);
+    int rc = direct ? make_tmap_bf16_k128(&tm_b1, q->x, q->T, q->H, q->ldx, kGroup)
+                    : make_tmap_bf16_k128(&tm_b1, q->x_sorted, P, q->H, q->H, kGroup);
+    if (rc == 0) rc = make_tmap_bf16_k128(&tm_b2, q->inter_sorted, P, q->I, q->I, kGroup);
     if (rc != 0) return rc;
 
     int pdl = q->pdl;

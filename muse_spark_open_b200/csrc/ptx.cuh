@@ -75,11 +75,16 @@ constexpr long long kWaitSlowPathCycles = 1ll << 20;
 // Bounded wait on an mbarrier phase.  The fast path only polls the barrier.  After about half a
 // millisecond it also looks at `status` (so that one lost signal does not cost a full budget per
 // waiter) and, once the budget is spent, records MSK_ERR_TIMEOUT and returns false.
+// SLEEP_NS > 0: the warp sleeps between polls.  A polling warp issues instructions all the time and takes
+// issue slots from the warps of its scheduler that do the arithmetic; roles that wait long (an epilogue
+// waiting for a whole tile, a producer far ahead of its consumers) should sleep.
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int where) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     uint32_t spins = 0;
     for (;;) {
+        if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 1023u) == 0) {
             const long long dt = clock64() - t0;
@@ -102,6 +107,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
         : "memory");
 }
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z,

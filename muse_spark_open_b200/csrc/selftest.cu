@@ -5,6 +5,7 @@
 //   mode 1  e4m3, A K-major from a paged cache by 4-D TMA, B K-major written by threads (scores)
 //   mode 2  e4m3, A MN-major from a paged cache by 4-D TMA, B K-major written by threads (values)
 //   mode 3  bf16, A written to tensor memory by tcgen05.st, B K-major by cp.async       (experts)
+// (kind::f16 wants both operands in the same format: FP16 x BF16 in one MMA ends in a CUDA error.)
 #include "msk.h"
 #include "ptx.cuh"
 #include "tmap.cuh"
