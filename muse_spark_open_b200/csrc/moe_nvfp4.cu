@@ -43,8 +43,12 @@ namespace msk {
 constexpr int kBlob = 9216;        // one packed 128-row x 128-k weight block
 constexpr int kBlobScales = 8192;  // offset of the 128 x 8 block scales inside a blob
 constexpr int kBSlot = 8192;       // B tile of one stage: 32 rows x 256 bytes (two 128-byte-swizzled halves)
-constexpr int kStage = kBlob + kBSlot;
-constexpr int kNRaw = 11;          // ring stages (weight block + B tile)
+// A ring stage holds a PAIR of consecutive chunks of a unit: [weights 0][weights 1][B tile 0][B tile 1].  The
+// two weight blocks are adjacent in memory and the two B tiles are one TMA box, so the single producer thread
+// issues one wait, one bulk copy and one tensor copy per 2 chunks (its issue rate was the limit with one chunk
+// per stage).  Units with an odd number of chunks use stages of one chunk (second halves unused).
+constexpr int kStage = 2 * (kBlob + kBSlot);
+constexpr int kNRaw = 5;           // ring stages
 // nanoseconds a waiting warp of each role sleeps between polls (the dequant warps, which bound the rate, poll)
 constexpr int kSleepProducer = 200, kSleepIssuer = 40, kSleepEpilogue = 400;
 constexpr int kNA = 4;             // A slots in tensor memory, 64 columns each
@@ -357,10 +361,11 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
         tmem_alloc(smem_u32(&bar.tmem_slot), 512);
         tmem_relinquish();
     }
+    const int psh = ((p.K / 128 / p.S) & 1) ? 0 : 1;  // log2(chunks per ring stage)
     if (tid == 32) {
         // a ring stage (weight block + B tile) is free again when the 4 dequant warps have read the block and
         // the MMAs that read the B tile (one issuing warp per chunk) have completed
-        for (int i = 0; i < kNRaw; ++i) mbar_init(smem_u32(&bar.raw_full[i]), 1), mbar_init(smem_u32(&bar.raw_empty[i]), 4 + (p.share_chunks ? kIssuers : 1));
+        for (int i = 0; i < kNRaw; ++i) mbar_init(smem_u32(&bar.raw_full[i]), 1), mbar_init(smem_u32(&bar.raw_empty[i]), (4 + (p.share_chunks ? kIssuers : 1)) << psh);
         for (int i = 0; i < kNA; ++i) mbar_init(smem_u32(&bar.a_full[i]), 4), mbar_init(smem_u32(&bar.a_empty[i]), p.share_chunks ? kIssuers : 1);
         for (int i = 0; i < 2; ++i) mbar_init(smem_u32(&bar.d_full[i]), kIssuers), mbar_init(smem_u32(&bar.d_empty[i]), 4);
         fence_mbar_init();
@@ -397,20 +402,21 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
     if (warp == 0) {
         // ------------------------------------------------ producer: weight block (bulk copy) + B tile (2 TMA boxes)
         if (lane == 0) {
-            int cc = 0, s = 0, sph = 1;  // stage and the parity of its previous use
+            int pc = 0, s = 0, sph = 1;  // stages filled so far, stage, parity of the stage's previous use
+            const int per = 1 << psh;
             bool ok = true;
             for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
                 const int g = u / per_group, rem = u % per_group, tile = rem / p.S, ks = rem % p.S;
                 const uint8_t* src = p.wpacked + ((static_cast<size_t>(rt.g_expert[g]) * tiles + tile) * KC + ks * nch) * kBlob;
                 const int row0 = p.direct ? 0 : rt.g_off[g];
                 int kg = ks * nch * 2;  // 64-column group of the B operand
-                for (int c = 0; c < nch; ++c, ++cc, src += kBlob, kg += 2) {
-                    if (cc >= kNRaw) ok = mbar_wait<kSleepProducer>(smem_u32(&bar.raw_empty[s]), sph, p.status, where | 2);
+                for (int c = 0; c < nch; c += per, ++pc, src += per * kBlob, kg += 2 * per) {
+                    if (pc >= kNRaw) ok = mbar_wait<kSleepProducer>(smem_u32(&bar.raw_empty[s]), sph, p.status, where | 2);
                     if (!ok) break;
                     const uint32_t full = smem_u32(&bar.raw_full[s]), dst = base + s * kStage;
-                    mbar_expect_tx(full, kStage);
-                    bulk_load(dst, src, kBlob, full);
-                    tma_load_3d(dst + kBlob, &tm_b, full, 0, row0, kg);
+                    mbar_expect_tx(full, per * kBlob + 2 * kBSlot);  // the B box always spans 2 chunks
+                    bulk_load(dst, src, per * kBlob, full);
+                    tma_load_3d(dst + 2 * kBlob, &tm_b, full, 0, row0, kg);
                     if (++s == kNRaw) s = 0, sph ^= 1;
                 }
             }
@@ -439,11 +445,11 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
                 bool first = true;
                 for (int c = 0; c < nch && ok; ++c, ++cc) {
                     if (!p.share_chunks && cc % kNA != w) continue;
-                    const int s = cc % kNRaw, as = cc % kNA;
+                    const int s = (cc >> psh) % kNRaw, as = cc % kNA, sub = cc & ((1 << psh) - 1);
                     ok = mbar_wait<kSleepIssuer>(smem_u32(&bar.a_full[as]), (cc / kNA) & 1, p.status, where | 4);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint64_t b0 = umma_smem_desc(base + s * kStage + kBlob, 16, 1024, kSwizzle128);
+                    const uint64_t b0 = umma_smem_desc(base + s * kStage + 2 * kBlob + sub * kBSlot, 16, 1024, kSwizzle128);
                     if (p.share_chunks) {  // K steps 2w and 2w + 1
                         const uint64_t bd = b0 + (w >> 1) * 256 + 4 * (w & 1);
                         umma_f16_ts(d, tmem + as * 64 + 16 * w, bd, idesc, !first);
@@ -520,15 +526,16 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
         const int my_units = blockIdx.x < n_units ? (n_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
         const int total = my_units * nch;
         bool ok = true;
-        int s = grp % kNRaw, sph = 0, aph = 0;
+        int s = (grp >> psh) % kNRaw, sph = 0, aph = 0;
         const int as = grp;  // this group's A slot
+        const int sub = grp & ((1 << psh) - 1), sstep = kDqGroups >> psh;  // place in the stage; stages per step
         for (int cc = grp; cc < total && ok; cc += kDqGroups) {
             {
                 ok = mbar_wait(smem_u32(&bar.raw_full[s]), sph, p.status, where | 7);
                 if (ok && cc >= kNA) ok = mbar_wait(smem_u32(&bar.a_empty[as]), aph ^ 1, p.status, where | 8);
                 if (!ok) break;
                 tc_fence_after();
-                const uint8_t* raw = gbase + s * kStage;
+                const uint8_t* raw = gbase + s * kStage + sub * kBlob;
                 const uint2 sc = *reinterpret_cast<const uint2*>(raw + kBlobScales + row * 8);
                 const uint32_t pairs[4] = {scale_pair(sc.x), scale_pair(sc.x >> 16), scale_pair(sc.y), scale_pair(sc.y >> 16)};
                 const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + as * 64;
@@ -544,7 +551,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bar.a_full[as]));
-                s += kDqGroups;
+                s += sstep;
                 if (s >= kNRaw) s -= kNRaw, sph ^= 1;
                 aph ^= 1;
             }
@@ -785,9 +792,9 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
     // B operands by TMA: gemm 1 reads x itself (<= 32 tokens) or its rows gathered in expert-list order;
     // gemm 2 reads the activations the act kernel writes in that same order.  Box = 32 rows x 64 k.
     CUtensorMap tm_b1, tm_b2;
-    int rc = direct ? make_tmap_bf16_k128(&tm_b1, q->x, q->T, q->H, q->ldx, kGroup)
-                    : make_tmap_bf16_k128(&tm_b1, q->x_sorted, P, q->H, q->H, kGroup);
-    if (rc == 0) rc = make_tmap_bf16_k128(&tm_b2, q->inter_sorted, P, q->I, q->I, kGroup);
+    int rc = direct ? make_tmap_bf16_kgroups(&tm_b1, q->x, q->T, q->H, q->ldx, kGroup, 4)
+                    : make_tmap_bf16_kgroups(&tm_b1, q->x_sorted, P, q->H, q->H, kGroup, 4);
+    if (rc == 0) rc = make_tmap_bf16_kgroups(&tm_b2, q->inter_sorted, P, q->I, q->I, kGroup, 4);
     if (rc != 0) return rc;
 
     int pdl = q->pdl;

@@ -58,11 +58,11 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_
     return make_tmap(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-int make_tmap_bf16_k128(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems,
-                        uint32_t box_rows) {
+int make_tmap_bf16_kgroups(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems,
+                           uint32_t box_rows, uint32_t box_groups) {
     const uint64_t dims[3] = {64, rows, cols / 64};
     const uint64_t strides[2] = {ld_elems * 2, 128};
-    const uint32_t box[3] = {64, box_rows, 2};
+    const uint32_t box[3] = {64, box_rows, box_groups};
     return make_tmap(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 

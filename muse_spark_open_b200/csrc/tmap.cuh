@@ -17,10 +17,10 @@ int make_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const void*
 int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems,
                       uint32_t box_rows);
 
-// The same matrix as a 3-D tensor (64 columns, rows, column groups of 64) with a box of 2 column groups:
-// one copy brings a [box_rows x 128] K-major tile as two swizzled [box_rows x 64] halves, 64 * box_rows * 2
-// bytes apart (what a UMMA descriptor with the 128-byte swizzle wants).  Coordinates: (0, row, column / 64).
-int make_tmap_bf16_k128(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems,
-                        uint32_t box_rows);
+// The same matrix as a 3-D tensor (64 columns, rows, column groups of 64) with a box of `box_groups` column
+// groups: one copy brings a [box_rows x 64 * box_groups] K-major tile as swizzled [box_rows x 64] parts, 64 *
+// box_rows * 2 bytes apart (what a UMMA descriptor with the 128-byte swizzle wants).  Coordinates: (0, row, column / 64).
+int make_tmap_bf16_kgroups(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems,
+                           uint32_t box_rows, uint32_t box_groups);
 
 }  // namespace msk
