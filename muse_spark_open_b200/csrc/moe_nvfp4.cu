@@ -490,30 +490,42 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
             tc_fence_after();
             const float scale = __ldg(p.gs + e) * 67108864.0f;  // global scale * 2^26
             float* dst = p.outp + (static_cast<size_t>(ks) * P) * p.R + tile * 128 + row;
+            // 16 accumulator columns at a time (register budget), only the columns in use; two accumulators are
+            // read per wait: a read of tensor memory that is busy with MMAs and the dequant warps' stores takes
+            // hundreds of cycles, and with short units (gemm 2) the epilogue is what bounds the rate
+            const int used = p.direct ? p.route.T : n;
 #pragma unroll
-            for (int h = 0; h < kGroup / 16; ++h) {  // 16 accumulator columns at a time (register budget)
+            for (int h = 0; h < kGroup / 16; ++h) {
                 float v[16];
 #pragma unroll
                 for (int c = 0; c < 16; ++c) v[c] = 0.0f;
+                if (h * 16 < used) {
+                    const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + kNA * 64 + db * kIssuers * kGroup + h * 16;
 #pragma unroll
-                for (int w = 0; w < kIssuers; ++w) {
-                    if (!p.share_chunks && ((w - cc0) & (kIssuers - 1)) >= nch) continue;  // that warp had no chunk in this unit
-                    uint32_t t[16];
-                    tmem_ld16(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + kNA * 64 + (db * kIssuers + w) * kGroup + h * 16, t);
-                    tmem_wait_ld();
+                    for (int w = 0; w < kIssuers; w += 2) {
+                        // accumulators of warps that had no chunk in this unit hold stale values: skipped
+                        const bool has0 = p.share_chunks || ((w - cc0) & (kIssuers - 1)) < nch;
+                        const bool has1 = p.share_chunks || ((w + 1 - cc0) & (kIssuers - 1)) < nch;
+                        uint32_t t0[16], t1[16];
+                        if (has0) tmem_ld16(taddr + w * kGroup, t0);
+                        if (has1) tmem_ld16(taddr + (w + 1) * kGroup, t1);
+                        tmem_wait_ld();
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) v[c] += __uint_as_float(t[c]);
+                        for (int c = 0; c < 16; ++c) v[c] += (has0 ? __uint_as_float(t0[c]) : 0.0f) + (has1 ? __uint_as_float(t1[c]) : 0.0f);
+                    }
                 }
                 if (h == kGroup / 16 - 1) {
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&bar.d_empty[db]));
                 }
+                if (h * 16 < used) {
 #pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                    const int pr = __shfl_sync(0xffffffffu, mypair, h * 16 + c);
-                    const float sc = __shfl_sync(0xffffffffu, myscale, h * 16 + c);
-                    if (pr >= 0) dst[static_cast<size_t>(pr) * p.R] = v[c] * scale * sc;
+                    for (int c = 0; c < 16; ++c) {
+                        const int pr = __shfl_sync(0xffffffffu, mypair, h * 16 + c);
+                        const float sc = __shfl_sync(0xffffffffu, myscale, h * 16 + c);
+                        if (pr >= 0) dst[static_cast<size_t>(pr) * p.R] = v[c] * scale * sc;
+                    }
                 }
             }
         }
