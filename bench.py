@@ -173,11 +173,15 @@ def run_ours(args):
     if world == 1:
         state = layer.prepare(weights)
         step = lambda: layer.kernel_fn(data, state)  # noqa: E731
-        launches = 8
+        # prep_norm, qkv projection, attention, o projection, router, [gather when > 32 tokens], gemm 1, activation,
+        # gemm 2, combine
+        launches = 9 + (r_count > 32)
     else:
         ops = ep.CudaOps(weights, rank, world, NEXP)
         step = lambda: ep.step(data, ops)  # noqa: E731
-        launches = 10
+        # the five kernels up to the router, the row pack, the experts over all ranks' tokens (4 or 5), the reduce;
+        # NCCL's own kernels (all-gather, all-to-all) are not counted
+        launches = 5 + 1 + 4 + (REQUESTS > 32) + 1
     for _ in range(max(args.warmup, 3)):
         out = step()
     torch.cuda.synchronize()
@@ -246,15 +250,14 @@ def run_ours(args):
         ms_state = state["moe"]
         cfg = data["config"]
         from muse_spark_open_b200 import attention, moe, proj
-        wts = torch.empty((r_count, 8), dtype=torch.float32, device=dev)
-        ids2 = torch.empty_like(ids)
         mo = torch.empty((r_count, HIDDEN), dtype=torch.float32, device=dev)
         kv_bytes = sum(seqs) * HKV * HEAD * 2
         per_exp = sum(weights[k][0].numel() * weights[k][0].element_size() for k in ("w13", "w13_sf", "w2", "w2_sf"))
         kern = {
             "attn_decode": (lambda: attention.launch(buf["qkv"], buf["attn"], data, cfg), kv_bytes + r_count * 9216 * 2 + r_count * 4096 * 2),
-            "moe (gemm1 + gemm2 + combine)": (lambda: moe.forward(buf["xn1"], ids2, wts, ms_state, 0, NEXP, out=mo, logits=buf["logits"],
-                                                                   pre_norm=(buf["ssq1"], HIDDEN, 1e-5)), touched * per_exp + 2 * r_count * HIDDEN * 2),
+            "moe (gather + gemm1 + act + gemm2 + combine)": (lambda: moe.forward(buf["xn1"], ids, buf["topk_weights"], ms_state, 0, NEXP, out=mo,
+                                                                                 pre_norm=(buf["ssq1"][-1], HIDDEN, 1e-5)),
+                                                             touched * per_exp + 2 * r_count * HIDDEN * 2),
             "proj_skinny qkv": (lambda: proj.skinny(buf["xn0"], state["qkv_gate"], out=buf["qkv"]), 9216 * 4096 * 2 + r_count * (4096 + 9216) * 2),
             "proj_skinny o": (lambda: proj.skinny(buf["attn"], state["o"], out=buf["stream1"], resid=data["stream"]), 4096 * 4096 * 2 + r_count * 4096 * 10),
         }

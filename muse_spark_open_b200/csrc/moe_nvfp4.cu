@@ -431,10 +431,15 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
         //   short units (few tokens, many K splits): every warp issues 2 of the 8 K steps of every chunk, so a
         //                chunk is through after 2 issue times instead of 8.
         // a_full implies raw_full: the dequant warps waited for the stage before they wrote the A slot.
+        // This thread shares its scheduler with five busy warps, so every instruction of its sequential loop costs
+        // tens of cycles: it visits only its own chunks and steps stage, slot and phases instead of dividing.
         if (lane == 0) {
             const int w = warp - 1;
             const uint32_t idesc = umma_idesc(128, kGroup, 1, 1, 0, 0);
-            int cc = 0, uc = 0;
+            const int step = p.share_chunks ? 1 : kIssuers;         // chunks between two of this warp's chunks
+            const int sstep = p.share_chunks ? 0 : (kIssuers >> psh);  // ring stages between them (share: see below)
+            int c = p.share_chunks ? 0 : w, cc = c;                  // place in the unit, running chunk number
+            int s = (cc >> psh) % kNRaw, as = cc % kNA, aph = 0, uc = 0;
             bool ok = true;
             for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++uc) {
                 const int db = uc & 1;
@@ -443,26 +448,34 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
                 tc_fence_after();
                 const uint32_t d = tmem + kNA * 64 + (db * kIssuers + w) * kGroup;
                 bool first = true;
-                for (int c = 0; c < nch && ok; ++c, ++cc) {
-                    if (!p.share_chunks && cc % kNA != w) continue;
-                    const int s = (cc >> psh) % kNRaw, as = cc % kNA, sub = cc & ((1 << psh) - 1);
-                    ok = mbar_wait<kSleepIssuer>(smem_u32(&bar.a_full[as]), (cc / kNA) & 1, p.status, where | 4);
+                for (; c < nch; c += step, cc += step) {
+                    ok = mbar_wait<kSleepIssuer>(smem_u32(&bar.a_full[as]), aph, p.status, where | 4);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint64_t b0 = umma_smem_desc(base + s * kStage + 2 * kBlob + sub * kBSlot, 16, 1024, kSwizzle128);
+                    const uint32_t a0 = tmem + as * 64;
+                    const uint64_t b0 = umma_smem_desc(base + s * kStage + 2 * kBlob + (cc & ((1 << psh) - 1)) * kBSlot, 16, 1024, kSwizzle128);
                     if (p.share_chunks) {  // K steps 2w and 2w + 1
                         const uint64_t bd = b0 + (w >> 1) * 256 + 4 * (w & 1);
-                        umma_f16_ts(d, tmem + as * 64 + 16 * w, bd, idesc, !first);
-                        umma_f16_ts(d, tmem + as * 64 + 16 * w + 8, bd + 2, idesc, 1);
+                        umma_f16_ts(d, a0 + 16 * w, bd, idesc, !first);
+                        umma_f16_ts(d, a0 + 16 * w + 8, bd + 2, idesc, 1);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            umma_f16_ts(d, tmem + as * 64 + 8 * j, b0 + (j < 4 ? 0 : 256) + 2 * (j & 3), idesc, !first || j != 0);
+                        for (int j = 0; j < 8; ++j)  // K step j: 8 columns of A, 32 bytes of a B row, second half 4096 B on
+                            umma_f16_ts(d, a0 + 8 * j, b0 + (j < 4 ? 0 : 256) + 2 * (j & 3), idesc, !first || j != 0);
                     }
                     first = false;
                     umma_commit(smem_u32(&bar.a_empty[as]));
                     umma_commit(smem_u32(&bar.raw_empty[s]));
+                    if (p.share_chunks) {  // every chunk: next slot, next stage every 2^psh chunks
+                        if (++as == kNA) as = 0, aph ^= 1;
+                        if (((cc + 1) & ((1 << psh) - 1)) == 0 && ++s == kNRaw) s = 0;
+                    } else {               // own slot; its barrier flips every visit
+                        aph ^= 1;
+                        s += sstep;
+                        if (s >= kNRaw) s -= kNRaw;
+                    }
                 }
+                c -= nch;
                 if (ok) umma_commit(smem_u32(&bar.d_full[db]));
             }
         }
@@ -490,43 +503,44 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
             tc_fence_after();
             const float scale = __ldg(p.gs + e) * 67108864.0f;  // global scale * 2^26
             float* dst = p.outp + (static_cast<size_t>(ks) * P) * p.R + tile * 128 + row;
-            // 16 accumulator columns at a time (register budget), only the columns in use; two accumulators are
-            // read per wait: a read of tensor memory that is busy with MMAs and the dequant warps' stores takes
-            // hundreds of cycles, and with short units (gemm 2) the epilogue is what bounds the rate
-            const int used = p.direct ? p.route.T : n;
+            // Eight accumulator columns per step, only the columns in use, in a rolled loop: this code runs once per
+            // unit and unrolled it was mostly instruction fetch (with short units, gemm 2, the epilogue bounded the
+            // rate).  The accumulators of issuing warps that had no chunk in this unit hold stale values: skipped.
+            const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + kNA * 64 + db * kIssuers * kGroup;
+            unsigned has = 0;
 #pragma unroll
-            for (int h = 0; h < kGroup / 16; ++h) {
-                float v[16];
+            for (int w = 0; w < kIssuers; ++w)
+                if (p.share_chunks || ((w - cc0) & (kIssuers - 1)) < nch) has |= 1u << w;
+            // columns that hold a pair of this expert (in direct mode most tokens have none)
+            const unsigned cols = __ballot_sync(0xffffffffu, mypair >= 0);
+            const int last8 = cols ? (31 - __clz(cols)) & ~7 : 0;  // the last group of 8 columns with work
+#pragma unroll 1
+            for (int c0 = 0; c0 <= last8; c0 += 8) {
+                if (((cols >> c0) & 0xFFu) == 0) continue;
+                uint32_t t[kIssuers][8];
 #pragma unroll
-                for (int c = 0; c < 16; ++c) v[c] = 0.0f;
-                if (h * 16 < used) {
-                    const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + kNA * 64 + db * kIssuers * kGroup + h * 16;
-#pragma unroll
-                    for (int w = 0; w < kIssuers; w += 2) {
-                        // accumulators of warps that had no chunk in this unit hold stale values: skipped
-                        const bool has0 = p.share_chunks || ((w - cc0) & (kIssuers - 1)) < nch;
-                        const bool has1 = p.share_chunks || ((w + 1 - cc0) & (kIssuers - 1)) < nch;
-                        uint32_t t0[16], t1[16];
-                        if (has0) tmem_ld16(taddr + w * kGroup, t0);
-                        if (has1) tmem_ld16(taddr + (w + 1) * kGroup, t1);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int c = 0; c < 16; ++c) v[c] += (has0 ? __uint_as_float(t0[c]) : 0.0f) + (has1 ? __uint_as_float(t1[c]) : 0.0f);
-                    }
-                }
-                if (h == kGroup / 16 - 1) {
+                for (int w = 0; w < kIssuers; ++w)
+                    if (has & (1u << w)) tmem_ld8(taddr + w * kGroup + c0, t[w]);
+                tmem_wait_ld();
+                if (c0 == last8) {  // last read of this accumulator buffer
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&bar.d_empty[db]));
                 }
-                if (h * 16 < used) {
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) {
-                        const int pr = __shfl_sync(0xffffffffu, mypair, h * 16 + c);
-                        const float sc = __shfl_sync(0xffffffffu, myscale, h * 16 + c);
-                        if (pr >= 0) dst[static_cast<size_t>(pr) * p.R] = v[c] * scale * sc;
-                    }
+                for (int c = 0; c < 8; ++c) {
+                    float v = 0.0f;
+#pragma unroll
+                    for (int w = 0; w < kIssuers; ++w)
+                        if (has & (1u << w)) v += __uint_as_float(t[w][c]);
+                    const int pr = __shfl_sync(0xffffffffu, mypair, c0 + c);
+                    const float sc = __shfl_sync(0xffffffffu, myscale, c0 + c);
+                    if (pr >= 0) dst[static_cast<size_t>(pr) * p.R] = v * scale * sc;
                 }
+            }
+            if (cols == 0) {  // never the case for a unit that exists; keeps the barrier protocol whole
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bar.d_empty[db]));
             }
         }
     } else {
