@@ -140,19 +140,27 @@ __global__ void __launch_bounds__(128) proj_skinny_kernel(const __grid_constant_
     const uint32_t trow = tmem + (static_cast<uint32_t>(warp * 32) << 16);
     const int row = tid, n = n0 + row;
 
-    // The code below runs once per CTA, straight from a cold instruction cache: keep it small
-    // (rolled loops, one TMEM column per step) rather than fast per iteration.
+    // The code below runs once per CTA, straight from a cold instruction cache: rolled loops over groups of 8
+    // tokens (one tensor-memory round trip per group, not per token: with 256 tokens the round trips were a
+    // third of the kernel).  Tokens are owned in contiguous blocks of red_rows: CTA r finishes tokens
+    // [r * red_rows, (r + 1) * red_rows).
+    const int t_lo = rank * p.red_rows, t_hi = min(p.M, t_lo + p.red_rows);
     if (S > 1) {
         if (ok) {
 #pragma unroll 1
-            for (int t = 0; t < p.M; ++t) {
-                const int owner = t % S;
-                if (owner == rank) continue;
-                const uint32_t v = tmem_ld1(trow + t);
+            for (int t0 = 0; t0 < p.M; t0 += 8) {
+                if (t0 >= t_lo && t0 + 8 <= t_lo + p.red_rows) continue;  // all mine
+                uint32_t v[8];
+                tmem_ld8(trow + t0, v);
                 tmem_wait_ld();
-                const int slot = (rank - owner - 1 + S) % S;
-                const uint32_t local = red_base + ((slot * p.red_rows + t / S) * 128 + row) * 4;
-                dsmem_st_f32(dsmem_addr(local, owner), __uint_as_float(v));
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int t = t0 + i, owner = t / p.red_rows;
+                    if (t >= p.M || owner == rank) continue;
+                    const int slot = (rank - owner - 1 + S) % S;
+                    const uint32_t local = red_base + ((slot * p.red_rows + (t - owner * p.red_rows)) * 128 + row) * 4;
+                    dsmem_st_f32(dsmem_addr(local, owner), __uint_as_float(v[i]));
+                }
             }
         }
         cluster_sync_all();  // every thread of every CTA, also after a failed wait
@@ -161,33 +169,39 @@ __global__ void __launch_bounds__(128) proj_skinny_kernel(const __grid_constant_
     if (ok) {
         const float nw = (p.next_norm_w != nullptr && n < p.N) ? 1.0f + __bfloat162float(p.next_norm_w[n]) : 1.0f;
 #pragma unroll 1
-        for (int t = rank; t < p.M; t += S) {
-            float acc = __uint_as_float(tmem_ld1(trow + t));
+        for (int t0 = t_lo & ~7; t0 < t_hi; t0 += 8) {
+            uint32_t v[8];
+            tmem_ld8(trow + t0, v);
             tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int t = t0 + i;
+                if (t < t_lo || t >= t_hi) continue;  // uniform over the CTA
+                float acc = __uint_as_float(v[i]);
 #pragma unroll 1
-            for (int src = 0; src < S - 1; ++src) acc += red[(src * p.red_rows + t / S) * 128 + row];
-            acc *= rs[t];
-            if (n < p.N) {
-                if (p.resid != nullptr) acc += __ldcg(p.resid + static_cast<size_t>(t) * p.ldr + n);
-                if (p.out != nullptr) {
-                    if (p.out_fp32) static_cast<float*>(p.out)[static_cast<size_t>(t) * p.ldo + n] = acc;
-                    else static_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(t) * p.ldo + n] = __float2bfloat16(acc);
+                for (int src = 0; src < S - 1; ++src) acc += red[(src * p.red_rows + (t - t_lo)) * 128 + row];
+                acc *= rs[t];
+                if (n < p.N) {
+                    if (p.resid != nullptr) acc += __ldcg(p.resid + static_cast<size_t>(t) * p.ldr + n);
+                    if (p.out != nullptr) {
+                        if (p.out_fp32) static_cast<float*>(p.out)[static_cast<size_t>(t) * p.ldo + n] = acc;
+                        else static_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(t) * p.ldo + n] = __float2bfloat16(acc);
+                    }
+                    if (p.out_normed != nullptr)
+                        p.out_normed[static_cast<size_t>(t) * p.ldn + n] = __float2bfloat16(acc * nw);
+                } else {
+                    acc = 0.0f;
                 }
-                if (p.out_normed != nullptr)
-                    p.out_normed[static_cast<size_t>(t) * p.ldn + n] = __float2bfloat16(acc * nw);
-            } else {
-                acc = 0.0f;
-            }
-            if (p.out_ssq != nullptr) {
-                const float q = warp_sum(acc * acc);
-                if (lane == 0) wsum[warp][t] = q;
+                if (p.out_ssq != nullptr) {
+                    const float q = warp_sum(acc * acc);
+                    if (lane == 0) wsum[warp][t] = q;
+                }
             }
         }
         if (p.out_ssq != nullptr) {
             __syncthreads();
-            for (int t = tid; t < p.M; t += 128)
-                if (t % S == rank)
-                    p.out_ssq[blockIdx.y * p.M + t] = (wsum[0][t] + wsum[1][t]) + (wsum[2][t] + wsum[3][t]);
+            for (int t = t_lo + tid; t < t_hi; t += 128)
+                p.out_ssq[blockIdx.y * p.M + t] = (wsum[0][t] + wsum[1][t]) + (wsum[2][t] + wsum[3][t]);
         }
     }
     tc_fence_before();
