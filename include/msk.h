@@ -101,7 +101,8 @@ typedef struct {
     int B, L, Hq, Hkv, d, page_size, num_pages, window;
     float qk_scale_factor, sm_scale;
     int chunks;               /* split-KV ways = cluster size (1, 2, 4 or 8); 0 = pick */
-    int stages;               /* K/V tile ring depth (2..4); 0 = pick */
+    int stages;               /* K/V tile ring depth (3 or 4); 0 = pick */
+    int issuers;              /* decode: MMA-issuing warps, 2 (128 tensor-memory columns, more CTAs per SM) or 4; 0 = pick */
     int pdl;
 } MskAttnParams;
 
@@ -232,7 +233,7 @@ typedef struct {
     int top_k;                     /* <= 8 */
     int32_t* topk_ids;             /* int32 [T, top_k]: softmax -> top-k -> renormalise of the logits, written by */
     float* topk_weights;           /* fp32 [T, top_k]    the router kernel's last block per 32 tokens */
-    int attn_chunks, attn_stages, qkv_splits, o_splits;
+    int attn_chunks, attn_stages, attn_issuers, qkv_splits, o_splits;
     int pdl;                       /* also chain the first kernel to whatever precedes it */
 } MskLayerFront;
 

@@ -27,7 +27,7 @@ def inv_freq(theta: float, d: int, device) -> torch.Tensor | None:
     return _inv_freq[key]
 
 
-def launch(qkv2d: torch.Tensor, out2d: torch.Tensor, data: dict, cfg: dict, chunks: int = 0, stages: int = 0,
+def launch(qkv2d: torch.Tensor, out2d: torch.Tensor, data: dict, cfg: dict, chunks: int = 0, stages: int = 0, issuers: int = 0,
            pdl: bool = False) -> None:
     """qkv2d bf16 [B*L, >= (2Hq+2Hkv)*d] (row stride free), out2d bf16 [B*L, Hq*d]."""
     p = abi.AttnParams()
@@ -43,7 +43,7 @@ def launch(qkv2d: torch.Tensor, out2d: torch.Tensor, data: dict, cfg: dict, chun
     p.B, p.L, p.Hq, p.Hkv, p.d = cfg["batch"], cfg["q_len"], cfg["num_q_heads"], cfg["num_kv_heads"], cfg["head_dim"]
     p.page_size, p.num_pages, p.window = cfg["page_size"], kc.shape[0], cfg["window"]
     p.qk_scale_factor, p.sm_scale = cfg["qk_scale_factor"], cfg["sm_scale"]
-    p.chunks, p.stages, p.pdl = chunks, stages, int(pdl)
+    p.chunks, p.stages, p.issuers, p.pdl = chunks, stages, issuers, int(pdl)
     st = abi.status_for(qkv2d.device)
     abi.check(abi.lib().msk_attn_decode(C.byref(p), st.p, abi.stream_ptr()), "msk_attn_decode")
 

@@ -104,14 +104,14 @@ __device__ __forceinline__ void norm_rope_row(float (&x)[4], float post_scale, c
     }
 }
 
-template <int L>
+template <int L, int ISS>  // ISS: MMA-issuing warps (one thread issues only ~1 MMA per 100 clocks)
 __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUtensorMap tm_k,
                                                    const __grid_constant__ CUtensorMap tm_v, AttnArgs p) {
     constexpr int NR = 8 * L;                 // query rows per KV head
     constexpr int NP = 2 * NR;                // UMMA N: rows [0, NR) hold the first split term, [NR, 2 NR) the second
-    constexpr int ISS = L == 1 ? 4 : 2;       // MMA-issuing warps (one thread issues only ~1 MMA per 100 clocks)
     constexpr int SBUF = L == 1 ? 2 : 1;      // score buffers in TMEM (2: the next tile's scores are computed ahead)
-    constexpr uint32_t kCols = L == 1 ? 256 : 512;  // SBUF * ISS * NP score columns, then ISS * NP output columns
+    // SBUF * ISS * NP score columns, then ISS * NP output columns, as a power of two
+    constexpr uint32_t kCols = (SBUF + 1) * ISS * NP <= 128 ? 128 : (SBUF + 1) * ISS * NP <= 256 ? 256 : 512;
     constexpr uint32_t kOCol = SBUF * ISS * NP;
     constexpr int QP_BYTES = NP * 128;
     constexpr float kLoScale = 16.0f;         // the second split term is stored times 16 (keeps small residuals in range)
@@ -545,25 +545,32 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
     if (warp == 0) tmem_dealloc(tmem, kCols);
 }
 
-template <int L>
+template <int L, int ISS>
 int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
     constexpr int NR = 8 * L, NP = 2 * NR;
+    constexpr int kColsHost = ((L == 1 ? 3 : 2) * ISS * NP <= 128) ? 128 : ((L == 1 ? 3 : 2) * ISS * NP <= 256) ? 256 : 512;
     const int tile_cap = (q->max_pages * q->page_size + kTileKeys - 1) / kTileKeys;
     int tiles_max = tile_cap;
     if (q->window > 0) tiles_max = min(tiles_max, q->window / kTileKeys + 2);
     if (tiles_max < 1) tiles_max = 1;
+    // the ring needs 3 slots: a tile's slot is refilled one iteration after its tile (finish_tile runs late),
+    // and the next tile's scores are issued one iteration early
+    if (q->stages != 0 && (q->stages < 3 || q->stages > kAttnMaxStages)) return MSK_ERR_INVALID;
+    const int nst = q->stages > 0 ? q->stages : 3;
+    const int smem = 1024 + nst * kStageBytes + 2 * NP * 128 + NR * 128 * 4;
+    int resident = min(232448 / (smem + 2048), 512 / kColsHost);  // CTAs per SM: shared memory, tensor memory
+    if (resident < 1) resident = 1;
     int C = q->chunks;
     if (C <= 0) {
-        int want = (2 * 148) / (q->B * q->Hkv);  // two resident CTAs per SM
+        int want = (resident * 148) / (q->B * q->Hkv);
         if (want > tiles_max) want = tiles_max;
         C = 1;
         while (2 * C <= want && C < 8) C *= 2;
+        // plenty of (request, head) pairs but long, uneven contexts: halves balance the last wave better
+        if (C == 1 && tiles_max >= 32) C = 2;
     }
     if (C != 1 && C != 2 && C != 4 && C != 8) return MSK_ERR_INVALID;
     if ((tiles_max + C - 1) / C > kMaxTilesPerCta) return MSK_ERR_UNSUPPORTED;
-    int nst = q->stages > 0 ? q->stages : 3;
-    if (nst > kAttnMaxStages) nst = kAttnMaxStages;
-    const int smem = 1024 + nst * kStageBytes + 2 * NP * 128 + NR * 128 * 4;
 
     CUtensorMap tm_k, tm_v;
     const uint64_t dims[4] = {128, static_cast<uint64_t>(q->Hkv), static_cast<uint64_t>(q->page_size),
@@ -593,7 +600,7 @@ int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
 
     static int configured = 0;
     if (smem > configured) {
-        if (cudaFuncSetAttribute(attn_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(attn_kernel<L, ISS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return MSK_ERR_CUDA;
         configured = smem;
     }
@@ -616,7 +623,7 @@ int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
     }
     cfg.attrs = attrs;
     cfg.numAttrs = na;
-    return cudaLaunchKernelEx(&cfg, attn_kernel<L>, tm_k, tm_v, a) == cudaSuccess ? 0 : MSK_ERR_CUDA;
+    return cudaLaunchKernelEx(&cfg, attn_kernel<L, ISS>, tm_k, tm_v, a) == cudaSuccess ? 0 : MSK_ERR_CUDA;
 }
 
 }  // namespace msk
@@ -628,7 +635,10 @@ extern "C" int msk_attn_decode(const MskAttnParams* q, int* status, void* stream
         return MSK_ERR_INVALID;
     if (q->d != 128 || q->Hkv < 1 || q->Hq != 8 * q->Hkv || q->B < 1) return MSK_ERR_UNSUPPORTED;
     if (q->page_size < 8 || q->page_size > 128 || (q->page_size & (q->page_size - 1)) != 0) return MSK_ERR_UNSUPPORTED;
-    if (q->L == 1) return launch_attn<1>(q, status, static_cast<cudaStream_t>(stream));
-    if (q->L == 8) return launch_attn<8>(q, status, static_cast<cudaStream_t>(stream));
+    if (q->issuers != 0 && q->issuers != 2 && q->issuers != 4) return MSK_ERR_INVALID;
+    // decode: two issuing warps (128 tensor-memory columns) measured a little faster than four
+    if (q->L == 1 && q->issuers == 4) return launch_attn<1, 4>(q, status, static_cast<cudaStream_t>(stream));
+    if (q->L == 1) return launch_attn<1, 2>(q, status, static_cast<cudaStream_t>(stream));
+    if (q->L == 8) return launch_attn<8, 2>(q, status, static_cast<cudaStream_t>(stream));
     return MSK_ERR_UNSUPPORTED;
 }

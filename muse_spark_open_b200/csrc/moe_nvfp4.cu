@@ -409,14 +409,19 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
                 const int g = u / per_group, rem = u % per_group, tile = rem / p.S, ks = rem % p.S;
                 const uint8_t* src = p.wpacked + ((static_cast<size_t>(rt.g_expert[g]) * tiles + tile) * KC + ks * nch) * kBlob;
                 const int row0 = p.direct ? 0 : rt.g_off[g];
-                int kg = ks * nch * 2;  // 64-column group of the B operand
-                for (int c = 0; c < nch; c += per, ++pc, src += per * kBlob, kg += 2 * per) {
+                const int kg0 = ks * nch * 2;  // 64-column group of the B operand
+                // every CTA reads the same B tiles (direct mode) for the same k: unit u starts its K range at a
+                // different stage, so that the CTAs do not pull the same lines from the same L2 slices together
+                const int nstg = nch >> psh;
+                int ii = u % nstg;
+                for (int c = 0; c < nch; c += per, ++pc) {
                     if (pc >= kNRaw) ok = mbar_wait<kSleepProducer>(smem_u32(&bar.raw_empty[s]), sph, p.status, where | 2);
                     if (!ok) break;
                     const uint32_t full = smem_u32(&bar.raw_full[s]), dst = base + s * kStage;
                     mbar_expect_tx(full, per * kBlob + 2 * kBSlot);  // the B box always spans 2 chunks
-                    bulk_load(dst, src, per * kBlob, full);
-                    tma_load_3d(dst + 2 * kBlob, &tm_b, full, 0, row0, kg);
+                    bulk_load(dst, src + static_cast<size_t>(ii) * (per * kBlob), per * kBlob, full);
+                    tma_load_3d(dst + 2 * kBlob, &tm_b, full, 0, row0, kg0 + ii * 2 * per);
+                    if (++ii == nstg) ii = 0;
                     if (++s == kNRaw) s = 0, sph ^= 1;
                 }
             }

@@ -59,6 +59,10 @@ __global__ void __launch_bounds__(128) proj_skinny_kernel(const __grid_constant_
     const int kt0 = static_cast<int>(static_cast<long long>(rank) * KT / S);
     const int kt1 = static_cast<int>(static_cast<long long>(rank + 1) * KT / S);
     const int nk = kt1 - kt0;
+    // Every tile of a K split reads the same x tiles; started together they would all pull the same lines out of
+    // the same L2 slices at the same time.  Tile y therefore walks its K range from a different starting point.
+    const int rot = nk > 0 ? static_cast<int>((blockIdx.y * 5u) % static_cast<unsigned>(nk)) : 0;
+    auto kt_of = [&](int i) { const int j = i + rot; return kt0 + (j >= nk ? j - nk : j); };
     auto full = [&](int s) { return smem_u32(&bars[s]); };
     auto empty = [&](int s) { return smem_u32(&bars[kProjMaxStages + s]); };
     const uint32_t bar_done = smem_u32(&bars[2 * kProjMaxStages]);
@@ -88,17 +92,17 @@ __global__ void __launch_bounds__(128) proj_skinny_kernel(const __grid_constant_
             const int pre = nk < nst ? nk : nst;
             for (int i = 0; i < pre; ++i) {
                 mbar_expect_tx(full(i), stage_bytes);
-                tma_load_2d(base + i * stage_bytes, &tm_w, full(i), (kt0 + i) * 64, n0);
+                tma_load_2d(base + i * stage_bytes, &tm_w, full(i), kt_of(i) * 64, n0);
             }
             pdl_wait();  // x is the previous kernel's output
             for (int i = 0; i < pre; ++i)
-                tma_load_2d(base + i * stage_bytes + kProjWBytes, &tm_x, full(i), (kt0 + i) * 64, 0);
+                tma_load_2d(base + i * stage_bytes + kProjWBytes, &tm_x, full(i), kt_of(i) * 64, 0);
             for (int i = pre; i < nk; ++i) {
                 const int s = i % nst;
                 if (!mbar_wait(empty(s), ((i / nst) - 1) & 1, p.status, where | 1)) break;
                 mbar_expect_tx(full(s), stage_bytes);
-                tma_load_2d(base + s * stage_bytes, &tm_w, full(s), (kt0 + i) * 64, n0);
-                tma_load_2d(base + s * stage_bytes + kProjWBytes, &tm_x, full(s), (kt0 + i) * 64, 0);
+                tma_load_2d(base + s * stage_bytes, &tm_w, full(s), kt_of(i) * 64, n0);
+                tma_load_2d(base + s * stage_bytes + kProjWBytes, &tm_x, full(s), kt_of(i) * 64, 0);
             }
         }
         __syncwarp();

@@ -78,6 +78,7 @@ def fill_front(f: abi.LayerFront, data: dict, state: dict, buf: dict, tune: dict
         setattr(f, name, abi.ptr(buf[name]))
     f.top_k = TOP_K
     f.attn_chunks, f.attn_stages = tune.get("attn_chunks", 0), tune.get("attn_stages", 0)
+    f.attn_issuers = tune.get("attn_issuers", 0)
     f.qkv_splits, f.o_splits, f.pdl = tune.get("qkv_splits", 0), tune.get("o_splits", 0), 0
 
 

@@ -62,10 +62,10 @@ def run_attn(a):
     g = torch.Generator(device=DEV).manual_seed(2)
     qkv = torch.randn((t, 9216), generator=g, device=DEV).to(torch.bfloat16)
     out = torch.empty((t, 4096), dtype=torch.bfloat16, device=DEV)
-    us = _time(lambda: attention.launch(qkv, out, data, cfg, chunks=a.chunks, stages=a.stages), a)
+    us = _time(lambda: attention.launch(qkv, out, data, cfg, chunks=a.chunks, stages=a.stages, issuers=a.issuers), a)
     keys = sum(min(s, a.window - 1) if a.window else s for s in seqs)
     _emit("attn_decode", us, keys * 4 * 128 * 2 + t * (9216 + 4096) * 2, batch=a.batch, q_len=a.q_len, window=a.window,
-          ctx=a.ctx, chunks=a.chunks, stages=a.stages)
+          ctx=a.ctx, chunks=a.chunks, stages=a.stages, issuers=a.issuers)
 
 
 def run_moe(a):
@@ -74,17 +74,19 @@ def run_moe(a):
     g = torch.Generator(device=DEV).manual_seed(3)
     x = torch.randn((a.tokens, 4096), generator=g, device=DEV).to(torch.bfloat16)
     logits = torch.randn((a.tokens, 128), generator=g, device=DEV)
-    ids = torch.empty((a.tokens, 8), dtype=torch.int32, device=DEV)
-    wts = torch.empty((a.tokens, 8), dtype=torch.float32, device=DEV)
+    # the expert choice as the router kernel leaves it (the experts take ids and weights as inputs, like the
+    # reference's op); --logits moves softmax / top-8 into the GEMM CTAs instead
+    pk, ids = torch.softmax(logits, -1).topk(8, -1)
+    ids, wts = ids.to(torch.int32).contiguous(), (pk / pk.sum(-1, keepdim=True)).contiguous()
     out = torch.empty((a.tokens, 4096), dtype=torch.bfloat16, device=DEV)
     sp = (a.s1, a.s2) if a.s1 else None
-    fn = lambda: moe.forward(x, ids, wts, state, 0, 128, out=out, logits=logits, splits=sp)  # noqa: E731
+    fn = lambda: moe.forward(x, ids, wts, state, 0, 128, out=out, logits=logits if a.logits else None, splits=sp)  # noqa: E731
     fn()
     torch.cuda.synchronize()
     touched = int(torch.unique(ids).numel())
     per = sum(w[k][0].numel() * w[k][0].element_size() for k in ("w13", "w13_sf", "w2", "w2_sf"))
     us = _time(fn, a)
-    _emit("moe_forward (gemm1 + gemm2 + combine)", us, touched * per + 2 * a.tokens * 4096 * 2, tokens=a.tokens, touched=touched,
+    _emit("moe_forward (gather + gemm1 + act + gemm2 + combine)", us, touched * per + 2 * a.tokens * 4096 * 2, tokens=a.tokens, touched=touched,
           splits=sp)
 
 
@@ -112,7 +114,9 @@ def main():
     ap.add_argument("--q-len", type=int, default=1)
     ap.add_argument("--chunks", type=int, default=0)
     ap.add_argument("--stages", type=int, default=0)
+    ap.add_argument("--issuers", type=int, default=0)
     ap.add_argument("--tokens", type=int, default=32)
+    ap.add_argument("--logits", action="store_true")
     ap.add_argument("--s1", type=int, default=0)
     ap.add_argument("--s2", type=int, default=0)
     ap.add_argument("--reps", type=int, default=10)
