@@ -16,13 +16,14 @@ __device__ __forceinline__ float ordered_float(uint32_t o) {
     return __uint_as_float((o & 0x80000000u) ? (o & 0x7fffffffu) : ~o);
 }
 
-// logits[0..n), n <= 256.  Lanes 0..top_k-1 write ids[lane] (global expert id) and wts[lane] (probability,
+// logits[0..n), n <= 32 * NV.  Lanes 0..top_k-1 write ids[lane] (global expert id) and wts[lane] (probability,
 // renormalised over the chosen).  Ties go to the lower expert id.  Two warp reductions per choice.
-__device__ __forceinline__ void route_token(const float* logits, int n, int top_k, int lane, int* ids, float* wts) {
-    uint32_t v[8];
+template <int NV>
+__device__ __forceinline__ void route_token_nv(const float* logits, int n, int top_k, int lane, int* ids, float* wts) {
+    uint32_t v[NV];
     uint32_t mxo = 0;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < NV; ++i) {
         const int e = lane + 32 * i;
         v[i] = e < n ? float_ordered(__ldcg(logits + e)) : 0u;
         mxo = max(mxo, v[i]);
@@ -33,24 +34,28 @@ __device__ __forceinline__ void route_token(const float* logits, int n, int top_
     for (int k = 0; k < top_k; ++k) {
         uint32_t best = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) best = max(best, v[i]);
+        for (int i = 0; i < NV; ++i) best = max(best, v[i]);
         best = __reduce_max_sync(0xffffffffu, best);
         int cand = 0x7fffffff;  // this lane's lowest expert id holding the maximum
 #pragma unroll
-        for (int i = 7; i >= 0; --i)
+        for (int i = NV - 1; i >= 0; --i)
             if (v[i] == best) cand = lane + 32 * i;
         const int bi = __reduce_min_sync(0xffffffffu, cand);
         const float pk = __expf(ordered_float(best) - mx);
         sum += pk;
         if (lane == k) my_id = bi, my_p = pk;
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+        for (int i = 0; i < NV; ++i)
             if (lane + 32 * i == bi) v[i] = 0u;
     }
     if (lane < top_k) {
         ids[lane] = my_id;
         wts[lane] = my_p / sum;
     }
+}
+__device__ __forceinline__ void route_token(const float* logits, int n, int top_k, int lane, int* ids, float* wts) {
+    if (n <= 128) route_token_nv<4>(logits, n, top_k, lane, ids, wts);
+    else route_token_nv<8>(logits, n, top_k, lane, ids, wts);
 }
 
 }  // namespace msk
