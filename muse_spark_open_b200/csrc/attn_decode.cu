@@ -55,7 +55,7 @@ struct AttnArgs {
     int max_pages;
     const long long* cache_loc;
     const float* inv_freq;
-    int B, Hq, Hkv, page_size, num_pages, window, nstages;
+    int B, Hq, Hkv, page_size, num_pages, window, nstages, longest_first;
     float qk_scale_factor, sm_scale, q_split_scale;
     int* status;
 };
@@ -125,7 +125,28 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
     __shared__ float sc_tail[NR][L];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int C = gridDim.x, rank = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int C = gridDim.x, rank = blockIdx.x, h = blockIdx.y;
+    int b = blockIdx.z;
+    if (p.longest_first) {
+        // More CTAs than the GPU holds at once, contexts of very different lengths: the CTAs are handed out in
+        // grid order, so slice z takes the request with the z-th longest context and the last wave is made of
+        // short requests (list scheduling, longest first).  Every CTA ranks the <= 256 lengths itself.
+        __shared__ int lens_s[256];
+        __shared__ int b_s;
+        for (int i = threadIdx.x; i < p.B; i += 128) lens_s[i] = p.seq_lens[i];
+        __syncthreads();
+        for (int j = threadIdx.x; j < p.B; j += 128) {
+            const int lj = lens_s[j];
+            int r = 0;
+            for (int i = 0; i < p.B; ++i) {
+                const int li = lens_s[i];
+                r += (li > lj || (li == lj && i < j)) ? 1 : 0;
+            }
+            if (r == static_cast<int>(blockIdx.z)) b_s = j;
+        }
+        __syncthreads();
+        b = b_s;
+    }
     const int where = MSK_K_ATTN << 8;
     const int nst = p.nstages;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -590,6 +611,7 @@ int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
     a.k_scale = q->k_scale, a.v_scale = q->v_scale, a.seq_lens = q->seq_lens, a.page_table = q->page_table;
     a.max_pages = q->max_pages, a.cache_loc = reinterpret_cast<const long long*>(q->cache_loc), a.inv_freq = q->inv_freq;
     a.B = q->B, a.Hq = q->Hq, a.Hkv = q->Hkv, a.page_size = q->page_size, a.num_pages = q->num_pages;
+    a.longest_first = (q->B <= 256 && q->B * q->Hkv * C > resident * 148) ? 1 : 0;
     a.window = q->window, a.nstages = nst, a.qk_scale_factor = q->qk_scale_factor, a.sm_scale = q->sm_scale;
     // largest power of two that keeps |q| * scale <= 448 (|q| <= qk_scale_factor * sqrt(128) after RMSNorm)
     float qs = 1.0f;

@@ -76,10 +76,10 @@ __global__ void __launch_bounds__(256) router_kernel(RouterArgs p) {
     __shared__ __align__(16) float Rs[kRouterE][kRouterK + 4];  // row stride 132 floats: 16-byte rows, no bank conflicts
     __shared__ __align__(16) float hs[kRouterT][kRouterK];
     __shared__ int last;
-    const int ks = blockIdx.x, et = blockIdx.y, tg = blockIdx.z, tid = threadIdx.x;
+    const int ks = blockIdx.x, et = blockIdx.y, tid = threadIdx.x;
     const int KS = gridDim.x;  // K splits = H / 128
-    const int t0 = tg * kRouterT, e0 = et * kRouterE, kb = ks * kRouterK;
-    const int nt = min(kRouterT, p.T - t0), ne = min(kRouterE, p.E - e0);
+    const int e0 = et * kRouterE, kb = ks * kRouterK;
+    const int ne = min(kRouterE, p.E - e0), n_tg = (p.T + kRouterT - 1) / kRouterT;
     const int tw = tid >> 5, el = tid & 31;  // warp w owns tokens w, w+8, w+16, w+24; lane = expert
     // both tiles are 32 rows x 32 float4; thread -> rows tw, tw+8, tw+16, tw+24, float4 column el.  All four loads
     // are issued before the first use; rows past the end re-read the last valid row and are zeroed.
@@ -96,6 +96,10 @@ __global__ void __launch_bounds__(256) router_kernel(RouterArgs p) {
     const float w0 = 1.0f + bf16lo(wraw.x), w1 = 1.0f + bf16hi(wraw.x), w2 = 1.0f + bf16lo(wraw.y), w3 = 1.0f + bf16hi(wraw.y);
     pdl_wait();
     pdl_launch_dependents();
+    // a block keeps its tile of router weights for several token groups (the grid stays within one wave of CTAs)
+    for (int tg = blockIdx.z; tg < n_tg; tg += gridDim.z) {
+    const int t0 = tg * kRouterT, nt = min(kRouterT, p.T - t0);
+    __syncthreads();  // the previous group's use of hs and `last` is over
     {
         float4 h[4];
 #pragma unroll
@@ -128,7 +132,7 @@ __global__ void __launch_bounds__(256) router_kernel(RouterArgs p) {
     __syncthreads();
     if (tid == 0) last = atomicAdd(p.ticket + tg * gridDim.y + et, 1) == KS - 1;
     __syncthreads();
-    if (!last) return;
+    if (!last) continue;
     __threadfence();
     // per-token 1/rms: lane q sums parts q, q + 32, ...; all four tokens' loads are in flight together
     float* rs_s = &hs[0][0];
@@ -177,10 +181,10 @@ __global__ void __launch_bounds__(256) router_kernel(RouterArgs p) {
     // the last expert tile of this token group chooses the experts: a warp per token, 4 tokens per warp
     __threadfence();
     __syncthreads();
-    int* ticket2 = p.ticket + gridDim.z * gridDim.y + tg;
+    int* ticket2 = p.ticket + n_tg * gridDim.y + tg;
     if (tid == 0) last = atomicAdd(ticket2, 1) == static_cast<int>(gridDim.y) - 1;
     __syncthreads();
-    if (!last) return;
+    if (!last) continue;
     __threadfence();
     for (int j = 0; j < 4; ++j) {
         const int t = tw + 8 * j;
@@ -189,6 +193,7 @@ __global__ void __launch_bounds__(256) router_kernel(RouterArgs p) {
                         p.wts_out + (t0 + t) * p.top_k);
     }
     if (tid == 0) *ticket2 = 0;
+    }
 }
 
 template <typename Kern, typename Args>
@@ -271,7 +276,10 @@ extern "C" int msk_layer_front(const MskLayerFront* f, int* status, void* stream
     r.part = f->router_part, r.ticket = f->router_ticket, r.logits = f->logits, r.T = T, r.H = H, r.E = f->E;
     r.top_k = f->top_k, r.ids_out = f->topk_ids, r.wts_out = f->topk_weights;
     const int ks = H / kRouterK;  // <= 64
-    return launch1(router_kernel, dim3(ks, (f->E + kRouterE - 1) / kRouterE, (T + kRouterT - 1) / kRouterT), dim3(256), 0, s, 1, r);
+    const int et = (f->E + kRouterE - 1) / kRouterE, n_tg = (T + kRouterT - 1) / kRouterT;
+    int gz = n_tg;  // 6 blocks of 33 KB fit an SM: more than one wave of them would double the kernel's time
+    while (gz > 1 && ks * et * gz > 6 * 148) gz = (gz + 1) / 2;
+    return launch1(router_kernel, dim3(ks, et, gz), dim3(256), 0, s, 1, r);
 }
 
 extern "C" int msk_layer_decode(const MskLayerParams* p, int* status, void* stream) {
