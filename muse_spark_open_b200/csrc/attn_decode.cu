@@ -547,6 +547,16 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
         const float ss = warp_sum(vv * vv);
         if (lane == 0) wred[warp][nl] = ss;
     }
+    // decode: the gates of this CTA's rows are requested together (a load between two stores is not moved up by
+    // the compiler, and one global round trip per row is most of this epilogue)
+    float gate_r[L == 1 ? NR : 1];
+    if constexpr (L == 1) {
+#pragma unroll
+        for (int nl = 0; nl < NR; ++nl) {
+            const int n = rank * rows_per + nl;
+            gate_r[nl] = nl < rows_per ? __bfloat162float(p.qkv[static_cast<size_t>(b) * p.ld_qkv + (p.Hq + 2 * p.Hkv + h * 8 + (n & 7)) * 128 + tid]) : 0.0f;
+        }
+    }
     __syncthreads();
     if (ok) {
 #pragma unroll
@@ -556,7 +566,7 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
             const size_t tok = static_cast<size_t>(b) * L + j;
             const float ss = (wred[0][nl] + wred[1][nl]) + (wred[2][nl] + wred[3][nl]);
             const float r = 1.0f / sqrtf(ss * (1.0f / 128.0f) + 1e-5f);
-            const float gate = __bfloat162float(p.qkv[tok * p.ld_qkv + (p.Hq + 2 * p.Hkv + h * 8 + g) * 128 + tid]);
+            const float gate = L == 1 ? gate_r[nl] : __bfloat162float(p.qkv[tok * p.ld_qkv + (p.Hq + 2 * p.Hkv + h * 8 + g) * 128 + tid]);
             const float sg = 1.0f / (1.0f + __expf(-gate));
             p.out[tok * p.ld_out + (h * 8 + g) * 128 + tid] = __float2bfloat16(val[nl] * r * sg);
         }

@@ -174,6 +174,13 @@ __global__ void __launch_bounds__(128) proj_skinny_kernel(const __grid_constant_
         const float nw = (p.next_norm_w != nullptr && n < p.N) ? 1.0f + __bfloat162float(p.next_norm_w[n]) : 1.0f;
 #pragma unroll 1
         for (int t0 = t_lo & ~7; t0 < t_hi; t0 += 8) {
+            // the group's residual values are requested together, before anything waits for one of them
+            float rv[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int t = t0 + i;
+                rv[i] = (p.resid != nullptr && n < p.N && t >= t_lo && t < t_hi) ? __ldcg(p.resid + static_cast<size_t>(t) * p.ldr + n) : 0.0f;
+            }
             uint32_t v[8];
             tmem_ld8(trow + t0, v);
             tmem_wait_ld();
@@ -186,7 +193,7 @@ __global__ void __launch_bounds__(128) proj_skinny_kernel(const __grid_constant_
                 for (int src = 0; src < S - 1; ++src) acc += red[(src * p.red_rows + (t - t_lo)) * 128 + row];
                 acc *= rs[t];
                 if (n < p.N) {
-                    if (p.resid != nullptr) acc += __ldcg(p.resid + static_cast<size_t>(t) * p.ldr + n);
+                    acc += rv[i];
                     if (p.out != nullptr) {
                         if (p.out_fp32) static_cast<float*>(p.out)[static_cast<size_t>(t) * p.ldo + n] = acc;
                         else static_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(t) * p.ldo + n] = __float2bfloat16(acc);

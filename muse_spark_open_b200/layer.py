@@ -100,7 +100,7 @@ def kernel_fn(data: dict, state: dict, **tune):
     t, h = stream.shape
     buf = buffers(state, t, stream.device)
     ms = state["moe"]
-    s1, s2 = tune.get("moe_splits") or moe.splits_for(t, ms["H"], ms["I"])
+    s1, s2 = tune.get("moe_splits") or moe.splits_for(t, ms["H"], ms["I"], state["local_count"], TOP_K)
     h1, y, inter, xs, pub = moe.scratch(ms, t, TOP_K, s1, s2, stream.device)
     hidden = torch.empty((t, h), dtype=torch.bfloat16, device=stream.device)
     out = torch.empty((t, h), dtype=torch.float32, device=stream.device)

@@ -20,13 +20,25 @@ POST_NORM_EPS = 1e-8
 MAX_TOKENS = 256
 
 
-def splits_for(tokens: int, h: int, inner: int) -> tuple[int, int]:
-    """K splits of the two GEMMs: more when few experts are touched, so every SM has work."""
+def splits_for(tokens: int, h: int, inner: int, local_count: int = 128, top_k: int = 8, sms: int = 148) -> tuple[int, int]:
+    """K splits of the two GEMMs: more when few expert-groups are touched (few tokens, or few local experts
+    under expert parallelism), so that every SM gets a few work units.  The small-batch entries are measured."""
     s1 = 4 if tokens <= 2 else 2 if tokens <= 8 else 1
-    s2 = 2 if tokens <= 4 and (inner // 128) % 2 == 0 else 1
+    s2 = 2 if tokens <= 4 else 1
+    groups = max(1, min(local_count, tokens * top_k))  # expert-groups (<= 32 pairs each) touched, roughly
+
+    def widen(s, units, chunks, cap):
+        while s < cap and units * s < 3 * sms and chunks % (2 * s) == 0 and chunks // (2 * s) >= 2:
+            s *= 2
+        return s
+
+    s1 = widen(s1, groups * (2 * inner // 128), h // 128, 4)
+    s2 = widen(s2, groups * (h // 128), inner // 128, 2)
     while (h // 128) % s1:
         s1 //= 2
-    return max(s1, 1), s2
+    while (inner // 128) % s2:
+        s2 //= 2
+    return max(s1, 1), max(s2, 1)
 
 
 def prepare(weights: dict, weights_start: int = 0) -> dict:
@@ -72,7 +84,7 @@ def forward(x, ids, wts, state, local_start, local_count, out=None, logits=None,
     top_k = ids.shape[1]
     if t > MAX_TOKENS:
         raise abi.MskError(f"experts built for decode/verify steps of up to {MAX_TOKENS} tokens, got {t}")
-    s1, s2 = splits or splits_for(t, state["H"], state["I"])
+    s1, s2 = splits or splits_for(t, state["H"], state["I"], local_count, top_k)
     h1, y, inter, xs, pub = scratch(state, t, top_k, s1, s2, x.device)
     if out is None:
         out = torch.empty((t, h), dtype=torch.bfloat16, device=x.device)
@@ -133,7 +145,7 @@ def forward_no_alloc(x, ids, wts, state, local_start, local_count, out, splits=N
     them in stream order.  Make the first call on a device outside any stream capture."""
     t, h = x.shape
     top_k = ids.shape[1]
-    s1, s2 = splits or splits_for(t, state["H"], state["I"])
+    s1, s2 = splits or splits_for(t, state["H"], state["I"], local_count, top_k)
     if 4 * (s1 * t * top_k * 2 * state["I"] + s2 * t * top_k * state["H"]) + 2 * t * top_k * state["I"] + 4096 > 4 * STATIC_SCRATCH_FLOATS:
         raise abi.MskError("this step needs more scratch than the library's built-in 4 MiB: use forward()")
     p = abi.MoeParams()
