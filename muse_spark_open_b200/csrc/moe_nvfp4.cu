@@ -50,7 +50,7 @@ constexpr int kBSlot = 8192;       // B tile of one stage: 32 rows x 256 bytes (
 constexpr int kStage = 2 * (kBlob + kBSlot);
 constexpr int kNRaw = 5;           // ring stages
 // nanoseconds a waiting warp of each role sleeps between polls (the dequant warps, which bound the rate, poll)
-constexpr int kSleepProducer = 200, kSleepIssuer = 40, kSleepEpilogue = 400;
+constexpr int kSleepProducer = 200, kSleepIssuer = 40, kSleepEpilogue = 60;
 constexpr int kNA = 4;             // A slots in tensor memory, 64 columns each
 constexpr int kGroup = 32;         // pairs per expert-group (UMMA N)
 constexpr int kMaxPairs = 2048;
@@ -503,10 +503,10 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
                 mypair = rt.list[off + lane];
             }
             const float myscale = (MODE == 1 && p.x_ssq != nullptr && mypair >= 0) ? rs_s[mypair / p.route.top_k] : 1.0f;
+            const float scale = __ldg(p.gs + e) * 67108864.0f;  // global scale * 2^26 (requested before the wait)
             ok = mbar_wait<kSleepEpilogue>(smem_u32(&bar.d_full[db]), (uc >> 1) & 1, p.status, where | 6);
             if (!ok) break;
             tc_fence_after();
-            const float scale = __ldg(p.gs + e) * 67108864.0f;  // global scale * 2^26
             float* dst = p.outp + (static_cast<size_t>(ks) * P) * p.R + tile * 128 + row;
             // Eight accumulator columns per step, only the columns in use, in a rolled loop: this code runs once per
             // unit and unrolled it was mostly instruction fetch (with short units, gemm 2, the epilogue bounded the

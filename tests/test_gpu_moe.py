@@ -92,6 +92,18 @@ def test_moe_routing_from_logits_in_kernel():
     torch.testing.assert_close(out.float().cpu(), omoe.ref_kernel(data, weights).float(), rtol=2e-2, atol=1e-2)
 
 
+def test_moe_expert_parallel_rank_shape():
+    """What one of 8 expert-parallel ranks runs: all 256 tokens of the step, 16 local experts of the benchmark's
+    shape (few expert-groups, so gemm 1 runs with 4 K splits and the gathered input rows)."""
+    weights = omoe.make_weights(3, n_experts=128, hidden=4096, inner=768)
+    data = omoe.make_input(256, 4, local_start=32, local_count=16)
+    out, _, _ = _run(data, weights)
+    ref = omoe.ref_kernel(data, weights)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=1e-2)
+    untouched = ~((data["topk_ids"] >= 32) & (data["topk_ids"] < 48)).any(-1)
+    assert (out[untouched] == 0).all()
+
+
 def test_moe_benchmark_shape():
     """32 tokens, hidden 4096, 128 experts of gate_up [1536, 4096] / down [4096, 768], softmax top-8."""
     weights = omoe.make_weights(0, n_experts=128, hidden=4096, inner=768)
