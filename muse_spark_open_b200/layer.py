@@ -84,10 +84,20 @@ def fill_front(f: abi.LayerFront, data: dict, state: dict, buf: dict, tune: dict
 
 def front(data: dict, state: dict, **tune) -> dict:
     """Everything up to the router's expert choice (the part an expert-parallel rank runs before the exchange)."""
-    t = data["config"]["batch"] * data["config"]["q_len"]
+    cfg = data["config"]
+    t = cfg["batch"] * cfg["q_len"]
     buf = buffers(state, t, data["stream"].device)
-    f = abi.LayerFront()
-    fill_front(f, data, state, buf, tune)
+    # the argument block depends only on addresses, shapes and a few config scalars: it is rebuilt when one of
+    # them changes, not on every step (filling it costs as much host time as a small kernel takes on the GPU)
+    key = (tuple(data[k].data_ptr() for k in ("stream", "k_cache", "v_cache", "k_scale", "v_scale", "seq_lens", "page_table",
+                                              "cache_loc")),
+           data["k_cache"].shape[0], data["page_table"].shape[1], tuple(sorted(cfg.items())), tuple(sorted(tune.items())))
+    cached = state.get("front_args")
+    if cached is None or cached[0] != key:
+        f = abi.LayerFront()
+        fill_front(f, data, state, buf, tune)
+        state["front_args"] = cached = (key, f)
+    f = cached[1]
     st = abi.status_for(data["stream"].device)
     abi.check(abi.lib().msk_layer_front(C.byref(f), st.p, abi.stream_ptr()), "msk_layer_front")
     return buf

@@ -84,10 +84,21 @@ def forward(x, ids, wts, state, local_start, local_count, out=None, logits=None,
     top_k = ids.shape[1]
     if t > MAX_TOKENS:
         raise abi.MskError(f"experts built for decode/verify steps of up to {MAX_TOKENS} tokens, got {t}")
-    s1, s2 = splits or splits_for(t, state["H"], state["I"], local_count, top_k)
-    h1, y, inter, xs, pub = scratch(state, t, top_k, s1, s2, x.device)
     if out is None:
         out = torch.empty((t, h), dtype=torch.bfloat16, device=x.device)
+    # the argument block depends only on addresses, strides and scalars: rebuilt when one changes, not per call
+    key = (x.data_ptr(), x.stride(0), ids.data_ptr(), wts.data_ptr(), ids.stride(0), out.data_ptr(), out.stride(0), out.dtype,
+           t, top_k, local_start, local_count, splits, pdl,
+           None if logits is None else (logits.data_ptr(), logits.stride(0)),
+           None if pre_norm is None else (pre_norm[0].data_ptr(), tuple(pre_norm[0].shape), pre_norm[0].stride(0), pre_norm[1], pre_norm[2]),
+           None if resid is None else (resid.data_ptr(), resid.stride(0)))
+    cached = state.get("forward_args")
+    if cached is not None and cached[0] == key:
+        st = abi.status_for(x.device)
+        abi.check(abi.lib().msk_moe_forward(C.byref(cached[1]), st.p, abi.stream_ptr()), "msk_moe_forward")
+        return out
+    s1, s2 = splits or splits_for(t, state["H"], state["I"], local_count, top_k)
+    h1, y, inter, xs, pub = scratch(state, t, top_k, s1, s2, x.device)
     p = abi.MoeParams()
     p.x, p.ldx = abi.ptr(x), x.stride(0)
     if pre_norm is not None:
@@ -114,6 +125,7 @@ def forward(x, ids, wts, state, local_start, local_count, out=None, logits=None,
     if resid is not None:
         p.resid, p.ldr = abi.ptr(resid), resid.stride(0)
     p.out, p.out_fp32, p.ldo, p.pdl = abi.ptr(out), int(out.dtype == torch.float32), out.stride(0), int(pdl)
+    state["forward_args"] = (key, p)
     st = abi.status_for(x.device)
     abi.check(abi.lib().msk_moe_forward(C.byref(p), st.p, abi.stream_ptr()), "msk_moe_forward")
     return out

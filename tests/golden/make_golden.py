@@ -108,7 +108,9 @@ def proj_cases(ref):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <checkout of Kushagrabainsla/muse-spark-open>")
+    ref_root = sys.argv[1]
     out = {}
     att, _ = load(ref_root, "muse_attention_decode")
     out["attention"] = dict(attention_cases(att))
