@@ -110,7 +110,10 @@ class CudaOps:
         t = gathered.shape[0]
         ms = self.state["moe"]
         h = ms["H"]
-        x, ids, wts, ssq = row_views(gathered, h)
+        key = ("views", gathered.data_ptr(), t)
+        if key not in self.bufs:  # the gathered buffer is persistent: its strided views are built once
+            self.bufs[key] = row_views(gathered, h)
+        x, ids, wts, ssq = self.bufs[key]
         out = self.buffer("partial", (t, h), torch.float32)
         moe.forward(x, ids, wts, ms, self.state["local_start"], self.state["local_count"], out=out,
                     pre_norm=(ssq, h, layer.RMS_EPS), splits=self.tune.get("moe_splits"), pdl=True)
