@@ -71,6 +71,23 @@ def test_attention_benchmark_shapes():
         _check(data, out, k_new, v_new, f"benchmark q_len={q_len}")
 
 
+def test_attention_grid_beyond_one_wave():
+    """80 requests x 4 KV heads with very uneven contexts, full attention: more CTAs than the GPU holds at once, so
+    every CTA ranks the context lengths and takes the requests longest first, and the one long context makes the
+    launch split every request's keys over two CTAs.  This is the branch the 256-request step runs in."""
+    g = torch.Generator().manual_seed(17)
+    seqs = torch.randint(64, 1501, (80,), generator=g).tolist()
+    seqs[37] = 4500   # 36 tiles of 128 keys: the "long contexts" rule picks two chunks
+    seqs[5] = seqs[6]  # a tie in the ranking
+    data = oattn.make_input(80, seqs, seed=23, q_len=1, window=0, rope_theta=0.0)
+    out, k_new, v_new, _ = _run(data)
+    _check(data, out, k_new, v_new, "beyond one wave")
+    # the same requests through one chunk per request and through four: the order of the slices must not matter
+    for chunks in (1, 4):
+        out_c = _run(data, chunks=chunks)[0]
+        torch.testing.assert_close(out_c.float(), out.float(), rtol=2e-2, atol=1e-2)
+
+
 def test_attention_outlier_cache_and_small_scale():
     data = oattn.make_input(3, [900, 1500, 64], seed=5, q_len=8, hq=8, hkv=1, cache_dist="outliers", kv_scale=1 / 64)
     out, k_new, v_new, _ = _run(data)

@@ -95,11 +95,18 @@ def test_layer_small():
         _run_and_check(weights, data, f"small q_len={q_len}")
 
 
-@pytest.mark.parametrize("batch,q_len", [(1, 1), (16, 1), (32, 1), (4, 8)])
-def test_layer_benchmark_shapes(batch, q_len):
-    """hidden 4096, 32/4 heads of 128, 128 experts [1536,4096]/[4096,768], full attention, context 2048."""
-    weights = olayer.make_weights(0)
-    data = olayer.make_input(batch, [2048] * batch, 1, q_len=q_len, rope_theta=0.0)
+@pytest.fixture(scope="module")
+def bench_weights():
+    return olayer.make_weights(0)
+
+
+@pytest.mark.parametrize("batch,q_len", [(1, 1), (16, 1), (32, 1), (1, 8), (16, 8), (32, 8)])
+def test_layer_benchmark_shapes(batch, q_len, bench_weights):
+    """The benchmark's single-GPU layer at its stated size: hidden 4096, 32/4 heads of 128, 128 experts
+    [1536,4096]/[4096,768], full attention, context 8192 per request, batch 1 / 16 / 32, decode and 8-token verify
+    blocks.  Every request is checked."""
+    weights = bench_weights
+    data = olayer.make_input(batch, [8192] * batch, 1, q_len=q_len, window=0, rope_theta=0.0)
     state, dd = _run_and_check(weights, data, f"benchmark b={batch} L={q_len}")
     if batch == 16:
         from muse_spark_open_b200 import layer
@@ -107,3 +114,21 @@ def test_layer_benchmark_shapes(batch, q_len):
         b = layer.kernel_fn(dd, state)
         torch.cuda.synchronize()
         assert torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])  # replays are bitwise identical
+
+
+def test_layer_256_requests(bench_weights):
+    """The token count of the 256-request benchmark step (contexts kept short so that the CPU oracle stays cheap):
+    attention takes the requests longest first over several waves of CTAs (once with one CTA per request and KV
+    head, once with the keys split over two, as the benchmark's long contexts make the launch choose), the router
+    runs eight token groups with both ticket stages, the experts read gathered input rows with all 128 experts
+    touched, and both projections run at M = 256 with the fused epilogue."""
+    g = torch.Generator().manual_seed(5)
+    seqs = torch.randint(1, 700, (256,), generator=g).tolist()
+    data = olayer.make_input(256, seqs, 9, q_len=1, window=0, rope_theta=0.0)
+    _run_and_check(bench_weights, data, "256 requests")
+    state, dd = _run_and_check(bench_weights, data, "256 requests, two chunks", attn_chunks=2)
+    from muse_spark_open_b200 import layer
+    a = layer.kernel_fn(dd, state)
+    b = layer.kernel_fn(dd, state)
+    torch.cuda.synchronize()
+    assert torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])
