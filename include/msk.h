@@ -1,8 +1,8 @@
 /* C ABI of libmsk_b200.so: one decoder layer's decode step on B200 (sm_100a).
  *
  * Every entry point takes plain device pointers and sizes, launches on the given CUDA stream
- * (a cudaStream_t passed as void*), never synchronises and never allocates (except msk_selftest_*
- * and the *_create/*_workspace_bytes helpers, which say so).  Return value: 0 on success, a
+ * (a cudaStream_t passed as void*), never synchronises and never allocates: every buffer, scratch
+ * included, is the caller's (the *_bytes functions give the sizes).  Return value: 0 on success, a
  * negative code for a rejected call (-1 invalid argument, -2 CUDA error, -3 unsupported shape).
  * Device-side problems (a bounded wait that expired, an index out of range) do not trap: the
  * kernel records them in `status`, a device int32[4] owned by the caller:
@@ -42,7 +42,7 @@ int msk_selftest_umma(int mode, const void* a, const void* b, float* d, int n, i
  *   acc *= rsqrt(sum_p in_ssq[p*M + t] * in_inv_dim + in_eps)   (RMSNorm of the input rows, folded)
  *   acc += resid[t*ldr + n]                                       (FP32 residual)
  *   out (bf16 or fp32) = acc
- *   out_normed[t*ldn + n] = bf16(acc * (1 + next_norm_w[n]))     (input of the next op, un-normalised)
+ *   out_normed[t*ldn + n] = bf16 or fp16(acc * (1 + next_norm_w[n]))   (input of the next op, un-normalised)
  *   out_ssq[tile*M + t] = sum over the tile's 128 columns of acc^2 (tile = n / 128)
  */
 typedef struct {
@@ -60,11 +60,12 @@ typedef struct {
     const float* resid;     /* fp32 [M, ldr] or NULL */
     int ldr;
     const void* next_norm_w;/* bf16 [N] or NULL */
-    void* out_normed;       /* bf16 [M, ldn] or NULL */
+    void* out_normed;       /* bf16 (fp16 when normed_fp16 != 0) [M, ldn] or NULL */
     int ldn;
     float* out_ssq;         /* fp32 [ceil(N/128), M] or NULL */
     int pdl;                /* launch with programmatic stream serialization (the kernel waits for its
                                predecessor only after it has started streaming W) */
+    int normed_fp16;        /* out_normed is written as FP16 (saturating), what the experts' GEMM consumes */
 } MskProjParams;
 
 int msk_proj_skinny(const MskProjParams* p, int* status, void* stream);
@@ -109,12 +110,14 @@ typedef struct {
 int msk_attn_decode(const MskAttnParams* p, int* status, void* stream);
 
 /* ---------------------------------------------------------------- NVFP4 (w4a16) routed experts
- * Per local (token, slot) pair: h = x . W13[e]^T, inter = bf16(silu(h[:I]) * h[I:]), y = inter . W2[e]^T,
+ * Per local (token, slot) pair: h = x . W13[e]^T, inter = fp16(silu(h[:I]) * h[I:]), y = inter . W2[e]^T,
  * out[token] += topk_weight * rmsnorm(y * (1 + post_norm_w), eps); tokens without a local pair give zeros.
  * Weights are NVFP4: E2M1 codes (two per byte, low nibble first), one E4M3 scale per 16 values, one FP32
  * scale per expert.  Stands in for muse_moe_w4a16/submission.py: `prepare` + `_pack_expert` (:793-871),
  * `moe_forward` (pybind, :730-768) behind `kernel_fn` (:874-897) = `moe_gemm` x2 + `norm_kernel`
  * (:307-666), with the layer hooks `pre_norm` (x_ssq) and `local_start_dev` of :888-896.
+ * The tensor cores run FP16 x FP16 -> FP32: the dequantised weights (E2M1 x E4M3) are exact in FP16, a BF16
+ * activation converts exactly for 2^-14 <= |x| <= 65504 (smaller magnitudes round to multiples of 2^-24).
  */
 typedef struct {
     const void* w13;     /* uint8 [E, 2I, H/2]: gate rows [0, I) then up rows [I, 2I) */
@@ -124,18 +127,20 @@ typedef struct {
     int E, H, I;         /* H and I multiples of 128 */
 } MskMoeWeights;
 
-/* Bytes of the two repacked weight buffers (lossless: same codes and scales, 9216-byte blocks of
- * 128 rows x 128 k with the codes' bits permuted for the in-kernel decoder). */
+/* Bytes of the two repacked weight buffers (lossless: same codes and scales, re-ordered into 9216-byte
+ * blocks of 128 rows x 128 k; in W13 every 32 rows of a block are 16 gate rows and the 16 up rows of the same
+ * channels). */
 int msk_moe_packed_bytes(int E, int H, int I, size_t* w13_bytes, size_t* w2_bytes);
 int msk_moe_pack(const MskMoeWeights* w, void* w13_packed, void* w2_packed, void* stream);
-/* Test hook: expand a packed buffer to BF16 [E, R, K] = e2m1 * e4m3 scale (no per-expert scale). */
-int msk_moe_dequant(const void* packed, void* out_bf16, int E, int R, int K, void* stream);
-/* Bytes of the scratch buffers msk_moe_forward needs for T tokens (x_sorted is 0 up to 32 tokens). */
+/* Test hook: expand a packed buffer to BF16 [E, R, K] = e2m1 * e4m3 scale (no per-expert scale), rows in the
+ * original order; gate_up != 0 for a packed W13 (R = 2I). */
+int msk_moe_dequant(const void* packed, void* out_bf16, int E, int R, int K, int gate_up, void* stream);
+/* Bytes of the scratch buffers msk_moe_forward needs for T tokens (h1 and route only with s1 > 1). */
 int msk_moe_scratch_bytes(int T, int top_k, int H, int I, int s1, int s2, size_t* h1_bytes, size_t* y_bytes,
                           size_t* inter_bytes, size_t* x_sorted_bytes, size_t* route_bytes);
 
 typedef struct {
-    const void* x;              /* bf16 [T, ldx] */
+    const void* x;              /* [T, ldx] bf16, or fp16 when x_fp16 != 0 */
     int ldx;
     const float* x_ssq;         /* optional: [x_ssq_parts, T] partial sums of squares of the un-normalised */
     int x_ssq_parts;            /*   rows; gemm 1 then scales row t by rsqrt(sum * x_inv_dim + x_eps)      */
@@ -156,12 +161,14 @@ typedef struct {
     const void* post_norm_w;    /* bf16 [H] */
     float post_eps;
     int H, I;
-    float* h1_part;             /* scratch fp32 [s1, T*top_k, 2I] */
+    float* h1_part;             /* scratch fp32 [s1, T*top_k, 2I]; only needed for s1 > 1 */
     float* y_part;              /* scratch fp32 [s2, T*top_k, H] */
-    void* inter_sorted;         /* scratch bf16 [T*top_k, I]: activations between the GEMMs, expert-list order */
-    void* x_sorted;             /* scratch bf16 [T*top_k, H]: gathered inputs; only needed for T > 32 */
-    int32_t* route_pub;         /* scratch int32 [2 + T*top_k]: the routing list gemm 1 publishes */
-    int s1, s2;                 /* K splits of the two GEMMs (divide H/128 and I/128) */
+    void* inter_sorted;         /* scratch fp16 [T*top_k, I]: activations between the GEMMs, expert-list order */
+    void* x_sorted;             /* scratch fp16: [T, H] up to 32 tokens, else [T*top_k, H] (inputs gathered in
+                                   expert-list order); not needed for T <= 32 with x_fp16 */
+    int32_t* route_pub;         /* scratch int32 [2 + T*top_k]: the routing list gemm 1 publishes; only for s1 > 1 */
+    int s1, s2;                 /* K splits of the two GEMMs (divide H/128 and I/128); 0 = 1.  With s1 = 1 the
+                                   activation is applied in gemm 1's epilogue (one launch fewer) */
     const float* resid;         /* optional fp32 [T, ldr] added to the result */
     int ldr;
     void* out;                  /* [T, ldo] bf16, or fp32 when out_fp32 != 0 */
@@ -169,6 +176,7 @@ typedef struct {
     void* out_copy;             /* optional bf16 [T, ldc] copy of the result */
     int ldc;
     int pdl;
+    int x_fp16;                 /* x is FP16 already (the layer's o_proj epilogue writes it so) */
 } MskMoeParams;
 
 int msk_moe_forward(const MskMoeParams* p, int* status, void* stream);
@@ -225,7 +233,7 @@ typedef struct {
     void* qkv;                     /* bf16 [T, (2Hq+2Hkv)*d] */
     void* attn;                    /* bf16 [T, Hq*d] */
     float* stream1;                /* fp32 [T, H] stream after attention */
-    void* xn1;                     /* bf16 [T, H] expert input before its row scale */
+    void* xn1;                     /* fp16 [T, H] expert input before its row scale */
     float* ssq1;                   /* fp32 [H/128 + 1, T]: per-128-column partial sums of squares, last row their total */
     float* router_part;            /* fp32 [H/128, T, E] */
     int32_t* router_ticket;        /* int32 [ceil(T/32) * (ceil(E/32) + 1)], zero before the first call */
@@ -253,7 +261,7 @@ int msk_layer_decode(const MskLayerParams* p, int* status, void* stream);
  * msk_moe_forward over all tokens with its own experts, the FP32 partials go back to the tokens' home
  * ranks (combine) and msk_ep_reduce adds them to the residual in rank order.
  */
-int msk_ep_row_bytes(int H, int top_k); /* 2H (x bf16) + 4k ids + 4k weights (padded to 16) + 16 (sum of squares, padding) */
+int msk_ep_row_bytes(int H, int top_k); /* 2H (x, 2-byte elements) + 4k ids + 4k weights (padded to 16) + 16 (sum of squares, padding) */
 int msk_ep_pack(const void* xn, const int32_t* topk_ids, const float* topk_weights, const float* ssq, int ssq_parts,
                 void* rows, int T, int H, int top_k, void* stream);
 int msk_ep_reduce(const float* stream1, const float* recv /* [ranks, T, H] */, int ranks, float* out, void* out_bf16,

@@ -34,7 +34,7 @@ class ProjParams(C.Structure):
         ("in_ssq", C.c_void_p), ("in_ssq_parts", C.c_int), ("in_inv_dim", C.c_float), ("in_eps", C.c_float),
         ("resid", C.c_void_p), ("ldr", C.c_int),
         ("next_norm_w", C.c_void_p), ("out_normed", C.c_void_p), ("ldn", C.c_int),
-        ("out_ssq", C.c_void_p), ("pdl", C.c_int),
+        ("out_ssq", C.c_void_p), ("pdl", C.c_int), ("normed_fp16", C.c_int),
     ]
 
 
@@ -57,7 +57,7 @@ def lib() -> C.CDLL:
         _lib.msk_attn_decode.argtypes = [vp, vp, vp]
         _lib.msk_moe_packed_bytes.argtypes = [ci, ci, ci, vp, vp]
         _lib.msk_moe_pack.argtypes = [vp, vp, vp, vp]
-        _lib.msk_moe_dequant.argtypes = [vp, vp, ci, ci, ci, vp]
+        _lib.msk_moe_dequant.argtypes = [vp, vp, ci, ci, ci, ci, vp]
         _lib.msk_moe_scratch_bytes.argtypes = [ci, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp]
         _lib.msk_moe_forward.argtypes = [vp, vp, vp]
         _lib.msk_moe_forward_static.argtypes = [vp, vp, vp]
@@ -153,7 +153,7 @@ class MoeParams(C.Structure):
         ("h1_part", C.c_void_p), ("y_part", C.c_void_p), ("inter_sorted", C.c_void_p), ("x_sorted", C.c_void_p),
         ("route_pub", C.c_void_p), ("s1", C.c_int), ("s2", C.c_int),
         ("resid", C.c_void_p), ("ldr", C.c_int), ("out", C.c_void_p), ("out_fp32", C.c_int), ("ldo", C.c_int),
-        ("out_copy", C.c_void_p), ("ldc", C.c_int), ("pdl", C.c_int),
+        ("out_copy", C.c_void_p), ("ldc", C.c_int), ("pdl", C.c_int), ("x_fp16", C.c_int),
     ]
 
 

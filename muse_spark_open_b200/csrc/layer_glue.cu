@@ -266,7 +266,7 @@ extern "C" int msk_layer_front(const MskLayerFront* f, int* status, void* stream
     o.x = f->attn, o.w = f->w_o, o.M = T, o.N = H, o.K = no, o.splits = f->o_splits;
     o.out = f->stream1, o.out_fp32 = 1, o.ldo = H;
     o.resid = f->stream, o.ldr = H;
-    o.next_norm_w = f->pre_expert_norm_w, o.out_normed = f->xn1, o.ldn = H, o.out_ssq = f->ssq1, o.pdl = 1;
+    o.next_norm_w = f->pre_expert_norm_w, o.out_normed = f->xn1, o.ldn = H, o.normed_fp16 = 1, o.out_ssq = f->ssq1, o.pdl = 1;
     rc = msk_proj_skinny(&o, status, stream);
     if (rc != 0) return rc;
 
@@ -289,7 +289,7 @@ extern "C" int msk_layer_decode(const MskLayerParams* p, int* status, void* stre
     if (rc != 0) return rc;
     MskMoeParams m = p->moe;
     const MskLayerFront& f = p->front;
-    m.x = f.xn1, m.ldx = f.H;
+    m.x = f.xn1, m.ldx = f.H, m.x_fp16 = 1;
     m.x_ssq = f.ssq1 + static_cast<size_t>((f.H + 127) / 128) * (f.B * f.L), m.x_ssq_parts = 1,  // the router's totals
      m.x_inv_dim = 1.0f / f.H, m.x_eps = f.norm_eps;
     m.logits = nullptr, m.topk_ids = f.topk_ids, m.topk_weights = f.topk_weights, m.top_k = f.top_k, m.ld_topk = 0;

@@ -1,7 +1,9 @@
 // NVFP4 (w4a16) routed experts: grouped GEMMs with the routing done inside the GEMM CTAs.
 //
-//   gemm 1   h[pair, 2I] = x[token(pair)] . W13[expert(pair)]^T      (gate rows, then up rows)
-//   act      inter[pair, I] = bf16(silu(h_gate) * h_up), rows in expert-list order
+//   stage    x16[row] = fp16(x[token(row)])   (only when x arrives as BF16, or for more than 32 tokens, where
+//            the rows are also gathered into expert-list order)
+//   gemm 1   h[pair, 2I] = x[token(pair)] . W13[expert(pair)]^T, and in its epilogue
+//            inter[row, I] = fp16(silu(h_gate) * h_up), rows in expert-list order
 //   gemm 2   y[pair, H]  = inter . W2[expert]^T
 //   combine  out[t] = sum over the token's local (expert) slots of w[t, slot] * rmsnorm(y * (1 + w_post))
 //
@@ -10,27 +12,33 @@
 // pair lists and walks the work units (expert-group of <= 32 pairs, 128-row tile, K split) that fall
 // to it, so every touched expert's weights stream through the SMs once.
 //
-// One persistent CTA per SM, 17 warps:
-//   warp 0        producer: per 128x128 weight block one untiled bulk copy (TMA) of 8 KB of bit-permuted
-//                 E2M1 codes + 1 KB of E4M3 block scales (repacked at prepare time: one contiguous
-//                 9216-byte read, each thread's 16 bytes at a conflict-free slot), and two TMA boxes of the
-//                 B operand (32 rows x 64 k, 128-byte swizzle) into the same ring stage: x itself when the
-//                 step has at most 32 tokens (column = token), else x gathered in expert-list order by a
-//                 small kernel; for gemm 2 the activations the act kernel wrote in that order.
-//   warps 9..16   dequant (two groups of four warps, one chunk per group at a time): thread = weight row.  8 codes per word become 4 BF16x2 registers with 3
-//                 shift+mask steps (the permutation puts every code's bits where BF16 wants them,
-//                 magnitudes as BF16 subnormals * 2^-126), times the block scale (E4M3 * 2^100 as BF16)
-//                 with one HMUL2 each: exact E2M1 x E4M3 products * 2^-26, written straight into tensor
-//                 memory (tcgen05.st) as the A operand.  No BF16 round trip through shared memory.
+// Arithmetic: FP16 x FP16 -> FP32 on the tensor cores.  Every E2M1 x E4M3 product (|v| in [2^-10, 2688], at
+// most 5 significant bits) is exact in FP16, so the weights enter exactly; a BF16 activation converts to FP16
+// exactly whenever 2^-14 <= |x| <= 65504 (8 significant bits into 11), smaller ones round to the 2^-24 grid
+// (absolute error <= 2^-25 per element), larger ones saturate.  sm_100a converts two E2M1 codes to FP16x2 in
+// one instruction (cvt.rn.f16x2.e2m1x2), which is why FP16 and not BF16 is the operand type.
+//
+// One persistent CTA per SM, 25 warps:
+//   warp 0        producer: per 128x128 weight block one untiled bulk copy (TMA) of 8 KB of E2M1 codes
+//                 + 1 KB of E4M3 block scales (repacked at prepare time: one contiguous 9216-byte read,
+//                 each thread's 16 bytes at a conflict-free slot), and one TMA box of the FP16 B operand
+//                 (32 rows x 64 k parts, 128-byte swizzle) into the same ring stage.
+//   warps 9..24   dequant, four groups of four warps, group g <-> A slot g in tensor memory: thread = weight
+//                 row; per 8 codes 4 cvt.rn.f16x2.e2m1x2 and 4 mul.f16x2 by the block scale (itself one
+//                 cvt.rn.f16x2.e4m3x2 per two scales), written straight into tensor memory (tcgen05.st)
+//                 as the A operand.  No round trip through shared memory.
 //   warps 1..4    one lane each issues tcgen05.mma kind::f16, A from TMEM, B from shared memory.  One thread
-//                 can issue only about one MMA per 100 clocks whatever N is, so four warps issue in parallel
-//                 (2 of a chunk's 8 K steps each), each into its own FP32 accumulator in TMEM
-//                 (double-buffered per unit).
-//   warps 5..8    epilogue: adds the four accumulators, tcgen05.ld, times global scale * 2^26 (and the folded pre-expert RMSNorm row
-//                 scale), plain stores into this K split's FP32 partial buffer.  K splits are summed in a
+//                 can issue only about one MMA per 100 clocks whatever N is, so four warps issue in parallel,
+//                 each into its own FP32 accumulator in TMEM (double-buffered per unit).
+//   warps 5..8    epilogue: adds the four accumulators (tcgen05.ld), times the expert's global scale (and the
+//                 folded pre-expert RMSNorm row scale).  gemm 1 with one K split: gate and up rows of the same
+//                 16 channels sit in the two halves of each warp (repacked so at prepare time), one shuffle
+//                 brings them together and fp16(silu(gate) * up) goes straight to the B operand of gemm 2.
+//                 Otherwise plain stores into this K split's FP32 partial buffer; K splits are summed in a
 //                 fixed order by the consumer, so results are bitwise reproducible and no buffer has to
 //                 be zeroed between calls.
 // Roofline: HBM (0.5625 bytes per weight of every touched expert).
+#include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
 #include "msk.h"
@@ -56,6 +64,7 @@ constexpr int kGroup = 32;         // pairs per expert-group (UMMA N)
 constexpr int kMaxPairs = 2048;
 constexpr int kMaxExperts = 256;
 constexpr int kMaxGroups = 320;
+constexpr int kMaxDevices = 64;     // per-device host state (function attributes, the built-in scratch's address)
 constexpr int kIssuers = 4;         // MMA-issuing warps (one lane each); a single thread issues one tcgen05.mma per ~100 clk
 constexpr int kDqGroups = 4;        // dequant warp groups (4 warps each); group g takes the chunks with index = g (mod 4)
 static_assert(kNA == kIssuers && kNA == kDqGroups && (kIssuers & (kIssuers - 1)) == 0,
@@ -64,54 +73,69 @@ constexpr int kMoeThreads = (1 + kIssuers + 4 + 4 * kDqGroups) * 32;
 constexpr int kRouteThreads = kMoeThreads, kRouteWarps = kRouteThreads / 32;
 
 // ---------------------------------------------------------------- weight repacking (prepare time)
-// destination bit of (code i, field f) with fields m, e0, e1, s = code bits 0..3
-__constant__ uint8_t kBitPos[8][4] = {{6, 7, 8, 15},   {22, 23, 24, 31}, {3, 4, 5, 12},    {19, 20, 21, 28},
-                                      {0, 1, 2, 9},    {16, 17, 18, 25}, {10, 11, 13, 14}, {26, 27, 29, 30}};
+// Row of the [R, K] matrix that packed row r of 128-row tile rt holds.  Plain matrices: rt * 128 + r.
+// gate_up matrices (inner = I > 0, rows [0, I) gate, [I, 2I) up): every 32 packed rows hold 16 gate rows followed
+// by the 16 up rows of the same channels, so that one warp of the GEMM epilogue (32 accumulator lanes) owns
+// both arguments of silu(gate) * up: channel = rt * 64 + (r / 32) * 16 + r % 16, up if (r / 16) is odd.
+__host__ __device__ __forceinline__ int packed_src_row(int rt, int r, int inner) {
+    if (inner == 0) return rt * 128 + r;
+    const int ch = rt * 64 + (r >> 5) * 16 + (r & 15);
+    return ((r >> 4) & 1) ? inner + ch : ch;
+}
 
+// One block = 4 quarters (32 k each) x 128 rows x 16 bytes of codes as stored (two per byte, even k in the low
+// nibble), then 128 rows x 8 block scales.
 __global__ void moe_pack_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ sf,
-                                uint8_t* __restrict__ packed, int R, int K) {
+                                uint8_t* __restrict__ packed, int R, int K, int inner) {
     const int kc = blockIdx.x, rt = blockIdx.y, e = blockIdx.z, r = threadIdx.x;
     const int KC = K / 128, tiles = R / 128;
-    const size_t row = static_cast<size_t>(e) * R + rt * 128 + r;
+    const size_t row = static_cast<size_t>(e) * R + packed_src_row(rt, r, inner);
     uint8_t* blob = packed + ((static_cast<size_t>(e) * tiles + rt) * KC + kc) * kBlob;
-    for (int q = 0; q < 4; ++q) {
-        uint32_t w[4];
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t src = *reinterpret_cast<const uint32_t*>(codes + row * (K / 2) + (kc * 128 + q * 32 + j * 8) / 2);
-            uint32_t o = 0;
-            for (int i = 0; i < 8; ++i) {
-                const uint32_t c = (src >> (4 * i)) & 0xF;
-                for (int f = 0; f < 4; ++f) o |= ((c >> f) & 1u) << kBitPos[i][f];
-            }
-            w[j] = o;
-        }
-        *reinterpret_cast<uint4*>(blob + q * 2048 + r * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-    }
+    for (int q = 0; q < 4; ++q)
+        *reinterpret_cast<uint4*>(blob + q * 2048 + r * 16) =
+            *reinterpret_cast<const uint4*>(codes + row * (K / 2) + (kc * 128 + q * 32) / 2);
     *reinterpret_cast<uint2*>(blob + kBlobScales + r * 8) =
         *reinterpret_cast<const uint2*>(sf + row * (K / 16) + kc * 8);
 }
 
 // ---------------------------------------------------------------- dequantisation
-__device__ __forceinline__ uint32_t hmul2_bf16(uint32_t a, uint32_t b) {
+__device__ __forceinline__ uint32_t hmul2_f16(uint32_t a, uint32_t b) {
     uint32_t d;
-    asm("mul.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    asm("mul.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
     return d;
 }
-// two E4M3 scale bytes (bits 0..7 and 8..15 of `two`) -> BF16x2 (s0 * 2^100, s1 * 2^100), exact.
-// byte << 4 read as BF16 is s * 2^-120 (subnormals included); two multiplications by 2^110.
+// two E4M3 block scales (bits 0..15 of `two`) -> FP16x2 (s0, s1), exact (E4M3 subnormals are FP16 normals)
 __device__ __forceinline__ uint32_t scale_pair(uint32_t two) {
-    const uint32_t raw = ((two & 0xFFu) << 4) | ((two & 0xFF00u) << 12);
-    return hmul2_bf16(hmul2_bf16(raw, 0x76807680u), 0x76807680u);
+    uint32_t d;
+    asm("{\n"
+        ".reg .b16 t;\n"
+        "cvt.u16.u32 t, %1;\n"
+        "cvt.rn.f16x2.e4m3x2 %0, t;\n"
+        "}\n"
+        : "=r"(d)
+        : "r"(two));
+    return d;
 }
-// 8 permuted codes -> 4 BF16x2 registers holding value * scale * 2^-26 (k ascending, low half first)
-__device__ __forceinline__ void dequant_word(uint32_t P, uint32_t s2, uint32_t* r) {
-    constexpr uint32_t M = 0x81C081C0u;
-    r[0] = hmul2_bf16(P & M, s2);
-    r[1] = hmul2_bf16((P << 3) & M, s2);
-    r[2] = hmul2_bf16((P << 6) & M, s2);
-    r[3] = hmul2_bf16(((P >> 4) & 0x00C000C0u) | ((P >> 5) & 0x01000100u) | ((P << 1) & 0x80008000u), s2);
+// 8 codes (one word: byte i holds k = 2i in its low and k = 2i + 1 in its high nibble) -> 4 FP16x2 registers
+// holding value * block scale, k ascending, low half first.  s2 = the scale in both halves.
+__device__ __forceinline__ void dequant_word(uint32_t w, uint32_t s2, uint32_t* r) {
+    uint32_t v0, v1, v2, v3;
+    asm("{\n"
+        ".reg .b8 b0, b1, b2, b3;\n"
+        "mov.b32 {b0, b1, b2, b3}, %4;\n"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n"
+        "cvt.rn.f16x2.e2m1x2 %3, b3;\n"
+        "}\n"
+        : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3)
+        : "r"(w));
+    r[0] = hmul2_f16(v0, s2);
+    r[1] = hmul2_f16(v1, s2);
+    r[2] = hmul2_f16(v2, s2);
+    r[3] = hmul2_f16(v3, s2);
 }
-// one thread's 32 codes (16 bytes) and their 2 block scales -> 16 registers
+// one thread's 32 codes (16 bytes) and their 2 block scales (FP16x2) -> 16 registers
 __device__ __forceinline__ void dequant_quarter(const uint4 w, uint32_t pair, uint32_t (&r)[16]) {
     const uint32_t s0 = __byte_perm(pair, 0, 0x1010), s1 = __byte_perm(pair, 0, 0x3232);
     dequant_word(w.x, s0, r + 0);
@@ -120,21 +144,23 @@ __device__ __forceinline__ void dequant_quarter(const uint4 w, uint32_t pair, ui
     dequant_word(w.w, s1, r + 12);
 }
 
-// Dequantise packed blocks into plain BF16 [rows, K] (value * scale, no global scale): test hook for
-// the bit-exactness of the in-kernel dequantisation.
-__global__ void moe_dequant_kernel(const uint8_t* __restrict__ packed, __nv_bfloat16* __restrict__ out, int R, int K) {
+// Dequantise packed blocks into plain BF16 [rows, K] in the matrix's own row order (value * block scale, no
+// global scale; exact in BF16 too): test hook for the bit-exactness of the in-kernel dequantisation.
+__global__ void moe_dequant_kernel(const uint8_t* __restrict__ packed, __nv_bfloat16* __restrict__ out, int R, int K,
+                                   int inner) {
     const int kc = blockIdx.x, rt = blockIdx.y, e = blockIdx.z, r = threadIdx.x;
     const int KC = K / 128, tiles = R / 128;
     const uint8_t* blob = packed + ((static_cast<size_t>(e) * tiles + rt) * KC + kc) * kBlob;
     const uint2 sc = *reinterpret_cast<const uint2*>(blob + kBlobScales + r * 8);
     const uint32_t pairs[4] = {scale_pair(sc.x), scale_pair(sc.x >> 16), scale_pair(sc.y), scale_pair(sc.y >> 16)};
-    __nv_bfloat16* dst = out + (static_cast<size_t>(e) * R + rt * 128 + r) * K + kc * 128;
+    __nv_bfloat16* dst = out + (static_cast<size_t>(e) * R + packed_src_row(rt, r, inner)) * K + kc * 128;
     for (int q = 0; q < 4; ++q) {
         uint32_t v[16];
         dequant_quarter(*reinterpret_cast<const uint4*>(blob + q * 2048 + r * 16), pairs[q], v);
         for (int i = 0; i < 16; ++i) {
-            dst[q * 32 + 2 * i] = __float2bfloat16(bf16lo(v[i]) * 67108864.0f);
-            dst[q * 32 + 2 * i + 1] = __float2bfloat16(bf16hi(v[i]) * 67108864.0f);
+            const __half2 h = *reinterpret_cast<const __half2*>(&v[i]);
+            dst[q * 32 + 2 * i] = __float2bfloat16(__low2float(h));
+            dst[q * 32 + 2 * i + 1] = __float2bfloat16(__high2float(h));
         }
     }
 }
@@ -155,7 +181,7 @@ struct RouteTables {
     int counts[kMaxExperts];
     int offs[kMaxExperts + 1];
     unsigned short ids_s[kMaxPairs];   // expert id of every pair (65535 = none)
-    unsigned short pos_s[kMaxPairs];
+    unsigned short pos_s[kMaxPairs];   // in the end: row of every pair in `list` (65535 = not a local pair)
     unsigned short list[kMaxPairs];    // pairs sorted by (local expert, pair index)
     unsigned short g_expert[kMaxGroups], g_off[kMaxGroups], g_n[kMaxGroups];
     unsigned short seg_cnt[kRouteWarps][kMaxExperts];  // pairs per (warp segment, expert)
@@ -261,43 +287,70 @@ __device__ void build_routing(RouteTables& rt, const RouteArgs& a, int* status, 
     __syncthreads();
     for (int i = tid; i < P; i += kRouteThreads) {
         const int e = static_cast<int>(rt.ids_s[i]) - a.local_start;
-        if (e >= 0 && e < a.local_count) rt.list[rt.offs[e] + rt.seg_cnt[i / seg][e] + rt.pos_s[i]] = static_cast<unsigned short>(i);
+        if (e >= 0 && e < a.local_count) {
+            const int dst = rt.offs[e] + rt.seg_cnt[i / seg][e] + rt.pos_s[i];
+            rt.list[dst] = static_cast<unsigned short>(i);
+            rt.pos_s[i] = static_cast<unsigned short>(dst);
+        } else {
+            rt.pos_s[i] = 65535;
+        }
     }
     __syncthreads();
 }
 
 // ---------------------------------------------------------------- B-operand helpers
-// gather (more than 32 tokens): x rows in expert-list order, so that an expert-group's B tile is one TMA box
-struct MoeGatherArgs {
+// FP16 copy of the expert input.  Up to 32 tokens: row = token (the GEMM's B tile is the tokens themselves).
+// More: rows in expert-list order, so that an expert-group's B tile is one TMA box.
+struct MoeStageArgs {
     RouteArgs route;
-    const __nv_bfloat16* x;
-    int ldx, H;
-    __nv_bfloat16* x_sorted;  // [T*top_k, H]
+    const void* x;     // [T, ldx] BF16, or FP16 when x_fp16
+    int ldx, H, x_fp16, direct;
+    __half* x16;       // [T, H] (direct) or [T*top_k, H]
     int* status;
 };
 
-__global__ void __launch_bounds__(kRouteThreads) moe_gather_kernel(MoeGatherArgs p) {
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
+    const float lo = fminf(fmaxf(bf16lo(v), -65504.0f), 65504.0f), hi = fminf(fmaxf(bf16hi(v), -65504.0f), 65504.0f);
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+__global__ void __launch_bounds__(kRouteThreads) moe_stage_kernel(MoeStageArgs p) {
     __shared__ RouteTables rt;
     pdl_wait();
     pdl_launch_dependents();
-    RouteArgs ra = p.route;
-    ra.ids_out = nullptr;
-    build_routing(rt, ra, p.status, MSK_K_MOE1 << 8);
+    int n_rows = p.route.T;
+    if (!p.direct) {
+        RouteArgs ra = p.route;
+        ra.ids_out = nullptr;
+        build_routing(rt, ra, p.status, MSK_K_MOE1 << 8);
+        n_rows = rt.n_local;
+    }
     const int tid = threadIdx.x;
-    for (int r = blockIdx.x; r < rt.n_local; r += gridDim.x) {
-        const int tok = rt.list[r] / p.route.top_k;
-        const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(tok) * p.ldx);
-        uint4* dst = reinterpret_cast<uint4*>(p.x_sorted + static_cast<size_t>(r) * p.H);
-        for (int i = tid; i < p.H / 8; i += kRouteThreads) dst[i] = __ldcg(src + i);
+    for (int r = blockIdx.x; r < n_rows; r += gridDim.x) {
+        const int tok = p.direct ? r : rt.list[r] / p.route.top_k;
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.x) + static_cast<size_t>(tok) * p.ldx);
+        uint4* dst = reinterpret_cast<uint4*>(p.x16 + static_cast<size_t>(r) * p.H);
+        for (int i = tid; i < p.H / 8; i += kRouteThreads) {
+            uint4 v = __ldcg(src + i);
+            if (!p.x_fp16) v = make_uint4(bf16x2_to_f16x2(v.x), bf16x2_to_f16x2(v.y), bf16x2_to_f16x2(v.z), bf16x2_to_f16x2(v.w));
+            dst[i] = v;
+        }
     }
 }
 
-// activation between the two GEMMs: inter[r] = bf16(silu(gate) * up) of the r-th pair in expert-list order
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+__device__ __forceinline__ float clamp_f16(float v) { return fminf(fmaxf(v, -65504.0f), 65504.0f); }
+
+// Activation between the two GEMMs when gemm 1 ran with K splits (its epilogue then cannot apply it):
+// inter[r] = fp16(silu(gate) * up) of the r-th pair in expert-list order.  The partial rows are in packed row
+// order (see packed_src_row): channel j sits at column (j / 64) * 128 + (j % 64 / 16) * 32 + j % 16, its up
+// value 16 columns further.
 struct MoeActArgs {
     const int* route_pub;  // [0] = local pairs, [2 + r] = pair of sorted row r (published by gemm 1)
     const float* h1;       // [s1][P][2I]
     int s1, P, inner;
-    __nv_bfloat16* inter;  // [P, I]
+    __half* inter;         // [P, I]
 };
 
 __global__ void __launch_bounds__(256) moe_act_kernel(MoeActArgs p) {
@@ -307,17 +360,19 @@ __global__ void __launch_bounds__(256) moe_act_kernel(MoeActArgs p) {
     for (int r = blockIdx.x; r < n_local; r += gridDim.x) {
         const int pair = __ldcg(p.route_pub + 2 + r);
         for (int k = threadIdx.x * 4; k < p.inner; k += 1024) {
+            const int col = (k >> 6) * 128 + ((k >> 4) & 3) * 32 + (k & 15);
             float4 g = make_float4(0, 0, 0, 0), u = make_float4(0, 0, 0, 0);
             for (int s = 0; s < p.s1; ++s) {
-                const float* row = p.h1 + (static_cast<size_t>(s) * p.P + pair) * (2 * p.inner) + k;
+                const float* row = p.h1 + (static_cast<size_t>(s) * p.P + pair) * (2 * p.inner) + col;
                 const float4 a = __ldcg(reinterpret_cast<const float4*>(row));
-                const float4 c = __ldcg(reinterpret_cast<const float4*>(row + p.inner));
+                const float4 c = __ldcg(reinterpret_cast<const float4*>(row + 16));
                 g.x += a.x, g.y += a.y, g.z += a.z, g.w += a.w;
                 u.x += c.x, u.y += c.y, u.z += c.z, u.w += c.w;
             }
-            const float o0 = g.x / (1.0f + __expf(-g.x)) * u.x, o1 = g.y / (1.0f + __expf(-g.y)) * u.y;
-            const float o2 = g.z / (1.0f + __expf(-g.z)) * u.z, o3 = g.w / (1.0f + __expf(-g.w)) * u.w;
-            *reinterpret_cast<uint2*>(p.inter + static_cast<size_t>(r) * p.inner + k) = make_uint2(pack_bf16(o0, o1), pack_bf16(o2, o3));
+            const __half2 o01 = __floats2half2_rn(clamp_f16(silu_mul(g.x, u.x)), clamp_f16(silu_mul(g.y, u.y)));
+            const __half2 o23 = __floats2half2_rn(clamp_f16(silu_mul(g.z, u.z)), clamp_f16(silu_mul(g.w, u.w)));
+            *reinterpret_cast<uint2*>(p.inter + static_cast<size_t>(r) * p.inner + k) =
+                make_uint2(*reinterpret_cast<const uint32_t*>(&o01), *reinterpret_cast<const uint32_t*>(&o23));
         }
     }
 }
@@ -333,7 +388,9 @@ struct MoeGemmArgs {
     int x_ssq_parts, x_ssq_ts;
     float x_inv_dim, x_eps;
     int* route_pub;    // gemm 1, CTA 0: [0] local pairs, [1] groups, [2 + r] pair of sorted row r
-    float* outp;       // [S][T*top_k][R]
+    float* outp;       // [S][T*top_k][R] FP32 partials (not written when fuse_act)
+    __half* inter;     // gemm 1, fuse_act: [T*top_k, inner] activations, rows in expert-list order
+    int inner, fuse_act;
     int S;
     int route_early;   // the routing input is final before the previous kernel ends
     int share_chunks;  // 1: the issuing warps split every chunk's K steps (short units); 0: a warp per A slot
@@ -440,7 +497,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
         // tens of cycles: it visits only its own chunks and steps stage, slot and phases instead of dividing.
         if (lane == 0) {
             const int w = warp - 1;
-            const uint32_t idesc = umma_idesc(128, kGroup, 1, 1, 0, 0);
+            const uint32_t idesc = umma_idesc(128, kGroup, 0, 0, 0, 0);  // FP16 x FP16 -> FP32
             const int step = p.share_chunks ? 1 : kIssuers;         // chunks between two of this warp's chunks
             const int sstep = p.share_chunks ? 0 : (kIssuers >> psh);  // ring stages between them (share: see below)
             int c = p.share_chunks ? 0 : w, cc = c;                  // place in the unit, running chunk number
@@ -503,11 +560,15 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
                 mypair = rt.list[off + lane];
             }
             const float myscale = (MODE == 1 && p.x_ssq != nullptr && mypair >= 0) ? rs_s[mypair / p.route.top_k] : 1.0f;
-            const float scale = __ldg(p.gs + e) * 67108864.0f;  // global scale * 2^26 (requested before the wait)
+            // fused activation: the row of `inter` that belongs to that pair (its place in the expert-ordered list)
+            const int myrow = (MODE == 1 && mypair >= 0) ? static_cast<int>(rt.pos_s[mypair]) : -1;
+            const float scale = __ldg(p.gs + e);  // the expert's global scale (requested before the wait)
             ok = mbar_wait<kSleepEpilogue>(smem_u32(&bar.d_full[db]), (uc >> 1) & 1, p.status, where | 6);
             if (!ok) break;
             tc_fence_after();
             float* dst = p.outp + (static_cast<size_t>(ks) * P) * p.R + tile * 128 + row;
+            // channel of this lane's gate row (lanes 0..15 of a warp hold gate rows, 16..31 the up rows of the same channels)
+            __half* dst_act = p.inter + tile * 64 + quarter * 16 + (lane & 15);
             // Eight accumulator columns per step, only the columns in use, in a rolled loop: this code runs once per
             // unit and unrolled it was mostly instruction fetch (with short units, gemm 2, the epilogue bounded the
             // rate).  The accumulators of issuing warps that had no chunk in this unit hold stale values: skipped.
@@ -538,9 +599,16 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
 #pragma unroll
                     for (int w = 0; w < kIssuers; ++w)
                         if (has & (1u << w)) v += __uint_as_float(t[w][c]);
-                    const int pr = __shfl_sync(0xffffffffu, mypair, c0 + c);
                     const float sc = __shfl_sync(0xffffffffu, myscale, c0 + c);
-                    if (pr >= 0) dst[static_cast<size_t>(pr) * p.R] = v * scale * sc;
+                    v *= scale * sc;
+                    if (MODE == 1 && p.fuse_act) {
+                        const int sr = __shfl_sync(0xffffffffu, myrow, c0 + c);
+                        const float up = __shfl_xor_sync(0xffffffffu, v, 16);
+                        if (sr >= 0 && lane < 16) dst_act[static_cast<size_t>(sr) * p.inner] = __float2half_rn(clamp_f16(silu_mul(v, up)));
+                    } else {
+                        const int pr = __shfl_sync(0xffffffffu, mypair, c0 + c);
+                        if (pr >= 0) dst[static_cast<size_t>(pr) * p.R] = v;
+                    }
                 }
             }
             if (cols == 0) {  // never the case for a unit that exists; keeps the barrier protocol whole
@@ -759,18 +827,18 @@ extern "C" int msk_moe_pack(const MskMoeWeights* w, void* w13_packed, void* w2_p
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     moe_pack_kernel<<<dim3(w->H / 128, 2 * w->I / 128, w->E), 128, 0, s>>>(
         static_cast<const uint8_t*>(w->w13), static_cast<const uint8_t*>(w->w13_sf), static_cast<uint8_t*>(w13_packed),
-        2 * w->I, w->H);
+        2 * w->I, w->H, w->I);
     moe_pack_kernel<<<dim3(w->I / 128, w->H / 128, w->E), 128, 0, s>>>(
         static_cast<const uint8_t*>(w->w2), static_cast<const uint8_t*>(w->w2_sf), static_cast<uint8_t*>(w2_packed), w->H,
-        w->I);
+        w->I, 0);
     return cudaGetLastError() == cudaSuccess ? 0 : MSK_ERR_CUDA;
 }
 
-extern "C" int msk_moe_dequant(const void* packed, void* out_bf16, int E, int R, int K, void* stream) {
+extern "C" int msk_moe_dequant(const void* packed, void* out_bf16, int E, int R, int K, int gate_up, void* stream) {
     using namespace msk;
     if (!packed || !out_bf16 || R % 128 != 0 || K % 128 != 0) return MSK_ERR_INVALID;
     moe_dequant_kernel<<<dim3(K / 128, R / 128, E), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint8_t*>(packed), static_cast<__nv_bfloat16*>(out_bf16), R, K);
+        static_cast<const uint8_t*>(packed), static_cast<__nv_bfloat16*>(out_bf16), R, K, gate_up ? R / 2 : 0);
     return cudaGetLastError() == cudaSuccess ? 0 : MSK_ERR_CUDA;
 }
 
@@ -781,7 +849,7 @@ extern "C" int msk_moe_scratch_bytes(int T, int top_k, int H, int I, int s1, int
     if (h1_bytes) *h1_bytes = s1 * P * 2 * I * sizeof(float);
     if (y_bytes) *y_bytes = s2 * P * H * sizeof(float);
     if (inter_bytes) *inter_bytes = P * I * 2;
-    if (x_sorted_bytes) *x_sorted_bytes = T > msk::kGroup ? P * H * 2 : 0;
+    if (x_sorted_bytes) *x_sorted_bytes = (T > msk::kGroup ? P : static_cast<size_t>(T)) * H * 2;
     if (route_bytes) *route_bytes = (2 + P) * sizeof(int);
     return 0;
 }
@@ -789,8 +857,9 @@ extern "C" int msk_moe_scratch_bytes(int T, int top_k, int H, int I, int s1, int
 extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream) {
     using namespace msk;
     if (q == nullptr || !q->x || !q->w13_packed || !q->w2_packed || !q->w13_gs || !q->w2_gs || !q->post_norm_w ||
-        !q->h1_part || !q->y_part || !q->inter_sorted || !q->route_pub || !q->out || !q->topk_ids || !q->topk_weights)
+        !q->y_part || !q->inter_sorted || !q->out || !q->topk_ids || !q->topk_weights)
         return MSK_ERR_INVALID;
+    if (q->s1 > 1 && (!q->h1_part || !q->route_pub)) return MSK_ERR_INVALID;  // only the K-split gemm 1 leaves FP32 partials
     const int P = q->T * q->top_k;
     if (q->T < 1 || q->top_k < 1 || q->top_k > 8 || P > kMaxPairs || q->local_count < 1 || q->local_count > kMaxExperts ||
         q->T > kMaxPairs / 8)
@@ -798,20 +867,21 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
     if (q->H % 128 != 0 || q->I % 128 != 0 || q->ldx % 8 != 0 || q->H > 16 * kCombineThreads) return MSK_ERR_UNSUPPORTED;
     if (q->logits != nullptr && (q->n_logits > 256 || q->n_logits < q->top_k)) return MSK_ERR_UNSUPPORTED;
     const int direct = q->T <= kGroup;
-    if (!direct && q->x_sorted == nullptr) return MSK_ERR_INVALID;
+    const int stage = !(direct && q->x_fp16);  // the GEMM reads x itself only when it is FP16 and needs no gathering
+    if (stage && q->x_sorted == nullptr) return MSK_ERR_INVALID;
     const int s1 = q->s1 > 0 ? q->s1 : 1, s2 = q->s2 > 0 ? q->s2 : 1;
     if ((q->H / 128) % s1 != 0 || (q->I / 128) % s2 != 0) return MSK_ERR_INVALID;
     int dev = 0, sms = 148;
-    if (cudaGetDevice(&dev) != cudaSuccess) return MSK_ERR_CUDA;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return MSK_ERR_CUDA;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int smem = 1024 + kNRaw * kStage;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[kMaxDevices] = {};  // the attribute is per device
+    if (!configured[dev]) {
         if (cudaFuncSetAttribute(moe_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
             cudaFuncSetAttribute(moe_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return MSK_ERR_CUDA;
-        configured = true;
+        configured[dev] = true;
     }
     RouteArgs ra{};
     ra.ids = q->topk_ids, ra.logits = q->logits, ra.n_logits = q->n_logits;
@@ -820,20 +890,22 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
     ra.ld_ids = q->ld_topk > 0 ? q->ld_topk : q->top_k;
     ra.T = q->T, ra.top_k = q->top_k, ra.local_start = q->local_start, ra.local_count = q->local_count;
 
-    // B operands by TMA: gemm 1 reads x itself (<= 32 tokens) or its rows gathered in expert-list order;
-    // gemm 2 reads the activations the act kernel writes in that same order.  Box = 32 rows x 64 k.
+    // B operands by TMA (FP16, box = 32 rows x 64 k): gemm 1 reads the staged copy of x (tokens as rows up to 32
+    // tokens, else rows gathered in expert-list order) or x itself; gemm 2 reads the activations in that order.
     CUtensorMap tm_b1, tm_b2;
-    int rc = direct ? make_tmap_bf16_kgroups(&tm_b1, q->x, q->T, q->H, q->ldx, kGroup, 4)
-                    : make_tmap_bf16_kgroups(&tm_b1, q->x_sorted, P, q->H, q->H, kGroup, 4);
+    int rc = !stage    ? make_tmap_bf16_kgroups(&tm_b1, q->x, q->T, q->H, q->ldx, kGroup, 4)
+             : direct ? make_tmap_bf16_kgroups(&tm_b1, q->x_sorted, q->T, q->H, q->H, kGroup, 4)
+                      : make_tmap_bf16_kgroups(&tm_b1, q->x_sorted, P, q->H, q->H, kGroup, 4);
     if (rc == 0) rc = make_tmap_bf16_kgroups(&tm_b2, q->inter_sorted, P, q->I, q->I, kGroup, 4);
     if (rc != 0) return rc;
 
     int pdl = q->pdl;
-    if (!direct) {
-        MoeGatherArgs g{};
-        g.route = ra, g.x = static_cast<const __nv_bfloat16*>(q->x), g.ldx = q->ldx, g.H = q->H;
-        g.x_sorted = static_cast<__nv_bfloat16*>(q->x_sorted), g.status = status;
-        rc = launch_pdl(moe_gather_kernel, dim3(sms), dim3(kRouteThreads), 0, s, pdl, g);
+    if (stage) {
+        MoeStageArgs g{};
+        g.route = ra, g.x = q->x, g.ldx = q->ldx, g.H = q->H, g.x_fp16 = q->x_fp16, g.direct = direct;
+        g.x16 = static_cast<__half*>(q->x_sorted), g.status = status;
+        const int rows = direct ? q->T : P;
+        rc = launch_pdl(moe_stage_kernel, dim3(rows < sms ? rows : sms), dim3(kRouteThreads), 0, s, pdl, g);
         if (rc != 0) return rc;
         pdl = 1;
     }
@@ -843,16 +915,19 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
     a.x_ssq = q->x_ssq, a.x_ssq_parts = q->x_ssq_parts, a.x_inv_dim = q->x_inv_dim, a.x_eps = q->x_eps;
     a.x_ssq_ts = q->x_ssq_tstride > 0 ? q->x_ssq_tstride : 1;
     a.route_pub = q->route_pub, a.outp = q->h1_part, a.S = s1, a.status = status;
-    a.route_early = !direct && q->logits == nullptr;  // the gather kernel precedes
+    a.inter = static_cast<__half*>(q->inter_sorted), a.inner = q->I, a.fuse_act = s1 == 1;
+    a.route_early = stage && q->logits == nullptr;  // the staging kernel precedes
     a.share_chunks = q->T <= 4;
     rc = launch_pdl2(moe_gemm_kernel<1>, dim3(sms), dim3(kMoeThreads), smem, s, pdl, tm_b1, a);
     if (rc != 0) return rc;
 
-    MoeActArgs act{};
-    act.route_pub = q->route_pub, act.h1 = q->h1_part, act.s1 = s1, act.P = P, act.inner = q->I;
-    act.inter = static_cast<__nv_bfloat16*>(q->inter_sorted);
-    rc = launch_pdl(moe_act_kernel, dim3(P < 2 * sms ? P : 2 * sms), dim3(256), 0, s, 1, act);
-    if (rc != 0) return rc;
+    if (!a.fuse_act) {
+        MoeActArgs act{};
+        act.route_pub = q->route_pub, act.h1 = q->h1_part, act.s1 = s1, act.P = P, act.inner = q->I;
+        act.inter = static_cast<__half*>(q->inter_sorted);
+        rc = launch_pdl(moe_act_kernel, dim3(P < 2 * sms ? P : 2 * sms), dim3(256), 0, s, 1, act);
+        if (rc != 0) return rc;
+    }
 
     MoeGemmArgs b{};
     b.route = ra;
@@ -860,7 +935,8 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
     b.route.ids_out = nullptr, b.route.wts_out = nullptr;
     b.wpacked = static_cast<const uint8_t*>(q->w2_packed), b.gs = q->w2_gs, b.R = q->H, b.K = q->I, b.direct = 0;
     b.outp = q->y_part, b.S = s2, b.status = status;
-    b.route_early = 1;  // the activation kernel precedes
+    // the ids are final before gemm 2 can start, unless gemm 1 itself chose them from logits and ran just before
+    b.route_early = !a.fuse_act || q->logits == nullptr;
     b.share_chunks = a.share_chunks;
     rc = launch_pdl2(moe_gemm_kernel<2>, dim3(sms), dim3(kMoeThreads), smem, s, 1, tm_b2, b);
     if (rc != 0) return rc;
@@ -891,8 +967,7 @@ constexpr size_t kStaticScratchFloats = 1u << 20;
 static __device__ __align__(256) float g_moe_static_scratch[kStaticScratchFloats];
 
 namespace {
-constexpr int kMaxDevices = 64;
-float* g_static_scratch_ptr[kMaxDevices] = {};  // device address of the array, per device
+float* g_static_scratch_ptr[msk::kMaxDevices] = {};  // device address of the array, per device
 }  // namespace
 
 extern "C" int msk_moe_forward_static(const MskMoeParams* q, int* status, void* stream) {
@@ -910,7 +985,7 @@ extern "C" int msk_moe_forward_static(const MskMoeParams* q, int* status, void* 
     }
     if (total > kStaticScratchFloats * sizeof(float)) return MSK_ERR_UNSUPPORTED;  // beyond the built-in scratch
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return MSK_ERR_CUDA;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= msk::kMaxDevices) return MSK_ERR_CUDA;
     if (g_static_scratch_ptr[dev] == nullptr) {
         // Set-up, once per device and with that device current.  In host code the array's name is only a
         // stand-in; kernels need the address the runtime reports for the symbol on this device.

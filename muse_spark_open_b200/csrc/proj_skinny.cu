@@ -12,6 +12,8 @@
 //                       straight into that CTA's shared memory (DSMEM), one cluster barrier, then each owner
 //                       adds in a fixed order (bitwise reproducible), applies the fused epilogue and stores.
 // HBM traffic: W once (N*K*2 bytes); x is re-read per tile from L2.  Roofline: HBM.
+#include <cuda_fp16.h>
+
 #include "msk.h"
 #include "ptx.cuh"
 #include "tmap.cuh"
@@ -33,7 +35,7 @@ struct ProjArgs {
     int ldr;
     const __nv_bfloat16* next_norm_w;
     __nv_bfloat16* out_normed;
-    int ldn;
+    int ldn, normed_fp16;
     float* out_ssq;
     int* status;
 };
@@ -198,8 +200,13 @@ __global__ void __launch_bounds__(128) proj_skinny_kernel(const __grid_constant_
                         if (p.out_fp32) static_cast<float*>(p.out)[static_cast<size_t>(t) * p.ldo + n] = acc;
                         else static_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(t) * p.ldo + n] = __float2bfloat16(acc);
                     }
-                    if (p.out_normed != nullptr)
-                        p.out_normed[static_cast<size_t>(t) * p.ldn + n] = __float2bfloat16(acc * nw);
+                    if (p.out_normed != nullptr) {
+                        if (p.normed_fp16)
+                            reinterpret_cast<__half*>(p.out_normed)[static_cast<size_t>(t) * p.ldn + n] =
+                                __float2half_rn(fminf(fmaxf(acc * nw, -65504.0f), 65504.0f));
+                        else
+                            p.out_normed[static_cast<size_t>(t) * p.ldn + n] = __float2bfloat16(acc * nw);
+                    }
                 } else {
                     acc = 0.0f;
                 }
@@ -264,7 +271,7 @@ extern "C" int msk_proj_skinny(const MskProjParams* q, int* status, void* stream
     a.in_ssq = q->in_ssq, a.in_ssq_parts = q->in_ssq_parts, a.in_inv_dim = q->in_inv_dim, a.in_eps = q->in_eps;
     a.resid = q->resid, a.ldr = q->ldr;
     a.next_norm_w = static_cast<const __nv_bfloat16*>(q->next_norm_w);
-    a.out_normed = static_cast<__nv_bfloat16*>(q->out_normed), a.ldn = q->ldn;
+    a.out_normed = static_cast<__nv_bfloat16*>(q->out_normed), a.ldn = q->ldn, a.normed_fp16 = q->normed_fp16;
     a.out_ssq = q->out_ssq, a.status = status;
 
     static int configured_smem = 0;

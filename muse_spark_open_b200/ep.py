@@ -6,7 +6,7 @@ Partition (the benchmark's multi-GPU config): requests are data-parallel, rank g
 all-reduces are identities, muse_decode_layer/reference.py:8-10,467); here the exchange is real:
 
   front      (local tokens)   norms, QKV, attention, o_proj, residual, router (logits, softmax, top-8)
-  dispatch   every local token's row (x bf16 | expert ids | weights | sum of squares) goes to every rank, fixed
+  dispatch   every local token's row (x fp16 | expert ids | weights | sum of squares) goes to every rank, fixed
              capacity T_local rows per peer: sizes are static, nothing depends on the routing, so the
              step never syncs with the host and every rank posts the same collectives in the same order.
              With dense fixed-capacity rows an all-to-all and an all-gather move the same bytes; NCCL's
@@ -36,17 +36,17 @@ def shard(n: int, world: int, rank: int) -> tuple[int, int]:
 
 
 def row_bytes(hidden: int, top_k: int = TOP_K) -> int:
-    """Bytes of one dispatched token row: x bf16 [H] | ids int32 [k] | weights fp32 [k] | pad to 16 |
+    """Bytes of one dispatched token row: x fp16 [H] | ids int32 [k] | weights fp32 [k] | pad to 16 |
     sum of squares fp32 + padding."""
     return 2 * hidden + ((8 * top_k + 15) & ~15) + 16
 
 
 def row_views(rows: torch.Tensor, hidden: int, top_k: int = TOP_K):
-    """Strided views (x bf16 [T, H], ids int32 [T, k], weights fp32 [T, k], ssq fp32 [T]) into a uint8
+    """Strided views (x fp16 [T, H], ids int32 [T, k], weights fp32 [T, k], ssq fp32 [T]) into a uint8
     [T, row_bytes] buffer."""
     t = rows.shape[0]
     rb = rows.shape[1]
-    x = rows.view(torch.bfloat16).view(t, rb // 2)[:, :hidden]
+    x = rows.view(torch.float16).view(t, rb // 2)[:, :hidden]
     f = rows.view(torch.float32).view(t, rb // 4)
     i = rows.view(torch.int32).view(t, rb // 4)
     return x, i[:, hidden // 2: hidden // 2 + top_k], f[:, hidden // 2 + top_k: hidden // 2 + 2 * top_k], f[:, rb // 4 - 4]

@@ -49,7 +49,7 @@ def buffers(state: dict, t: int, device) -> dict:
         mk = lambda shape, dt: torch.empty(shape, dtype=dt, device=device)
         state["bufs"][t] = {
             "xn0": mk((t, h), bf), "ssq0": mk((t,), f32), "qkv": mk((t, nqkv), bf), "attn": mk((t, no), bf),
-            "stream1": mk((t, h), f32), "xn1": mk((t, h), bf), "ssq1": mk((h // 128 + 1, t), f32),
+            "stream1": mk((t, h), f32), "xn1": mk((t, h), torch.float16), "ssq1": mk((h // 128 + 1, t), f32),
             "router_part": mk((h // 128, t, e), f32),
             "router_ticket": torch.zeros((((t + 31) // 32) * ((e + 31) // 32 + 1),), dtype=torch.int32, device=device),
             "logits": mk((t, e), f32), "topk_ids": mk((t, TOP_K), torch.int32), "topk_weights": mk((t, TOP_K), f32),

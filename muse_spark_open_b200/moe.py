@@ -1,7 +1,7 @@
 """NVFP4 routed experts: the reference's per-op entry points over the C ABI.
 
 `prepare(weights) -> state` repacks the experts once (lossless: same E2M1 codes and E4M3 scales,
-re-ordered into 9216-byte blocks for the kernel's decoder); `kernel_fn(data, state) -> bf16 [T, H]`
+re-ordered into 9216-byte blocks, gate and up rows of W13 interleaved); `kernel_fn(data, state) -> bf16 [T, H]`
 with the `Weights` / `Config` / `Inputs` fields of muse_moe_w4a16/submission.py:32-57 (ids and
 weights are inputs, experts outside [local_start, local_start + local_count) are skipped).
 Layer hooks like the reference's (submission.py:888-896): `data["pre_norm"] = (ssq [parts, T], dim,
@@ -21,24 +21,18 @@ MAX_TOKENS = 256
 
 
 def splits_for(tokens: int, h: int, inner: int, local_count: int = 128, top_k: int = 8, sms: int = 148) -> tuple[int, int]:
-    """K splits of the two GEMMs: more when few expert-groups are touched (few tokens, or few local experts
-    under expert parallelism), so that every SM gets a few work units.  The small-batch entries are measured."""
-    s1 = 4 if tokens <= 2 else 2 if tokens <= 8 else 1
+    """K splits of the two GEMMs.  gemm 1 runs unsplit: its epilogue then applies silu(gate) * up itself and
+    the activation kernel and the FP32 partials between the GEMMs disappear (a unit is 32 blocks of 9 KB, long
+    enough to stream at full rate).  gemm 2's units are 6 blocks: with few expert-groups (few tokens, or few
+    local experts under expert parallelism) two splits give every SM a few of them."""
     s2 = 2 if tokens <= 4 else 1
     groups = max(1, min(local_count, tokens * top_k))  # expert-groups (<= 32 pairs each) touched, roughly
-
-    def widen(s, units, chunks, cap):
-        while s < cap and units * s < 3 * sms and chunks % (2 * s) == 0 and chunks // (2 * s) >= 2:
-            s *= 2
-        return s
-
-    s1 = widen(s1, groups * (2 * inner // 128), h // 128, 4)
-    s2 = widen(s2, groups * (h // 128), inner // 128, 2)
-    while (h // 128) % s1:
-        s1 //= 2
-    while (inner // 128) % s2:
+    chunks = inner // 128
+    while s2 < 2 and groups * (h // 128) * s2 < 3 * sms and chunks % (2 * s2) == 0 and chunks // (2 * s2) >= 2:
+        s2 *= 2
+    while chunks % s2:
         s2 //= 2
-    return max(s1, 1), max(s2, 1)
+    return 1, max(s2, 1)
 
 
 def prepare(weights: dict, weights_start: int = 0) -> dict:
@@ -65,15 +59,16 @@ def prepare(weights: dict, weights_start: int = 0) -> dict:
 
 
 def scratch(state: dict, tokens: int, top_k: int, s1: int, s2: int, device):
-    """The scratch buffers (FP32 partials, activations, gathered inputs, routing list), kept per (tokens, splits) in `state` (allocated once, outside timing)."""
+    """The scratch buffers (FP32 partials, FP16 activations and staged inputs, routing list), kept per
+    (tokens, splits) in `state` (allocated once, outside timing)."""
     key = (tokens, top_k, s1, s2)
     if key not in state["scratch"]:
         pairs = tokens * top_k
-        h1 = torch.empty((s1, pairs, 2 * state["I"]), dtype=torch.float32, device=device)
+        h1 = torch.empty((s1, pairs, 2 * state["I"]), dtype=torch.float32, device=device) if s1 > 1 else None
         y = torch.empty((s2, pairs, state["H"]), dtype=torch.float32, device=device)
-        inter = torch.empty((pairs, state["I"]), dtype=torch.bfloat16, device=device)
-        xs = torch.empty((pairs, state["H"]), dtype=torch.bfloat16, device=device) if tokens > 32 else None
-        pub = torch.zeros((2 + pairs,), dtype=torch.int32, device=device)
+        inter = torch.empty((pairs, state["I"]), dtype=torch.float16, device=device)
+        xs = torch.empty((pairs if tokens > 32 else tokens, state["H"]), dtype=torch.float16, device=device)
+        pub = torch.zeros((2 + pairs,), dtype=torch.int32, device=device) if s1 > 1 else None
         state["scratch"][key] = (h1, y, inter, xs, pub)
     return state["scratch"][key]
 
@@ -87,7 +82,9 @@ def forward(x, ids, wts, state, local_start, local_count, out=None, logits=None,
     if out is None:
         out = torch.empty((t, h), dtype=torch.bfloat16, device=x.device)
     # the argument block depends only on addresses, strides and scalars: rebuilt when one changes, not per call
-    key = (x.data_ptr(), x.stride(0), ids.data_ptr(), wts.data_ptr(), ids.stride(0), out.data_ptr(), out.stride(0), out.dtype,
+    if x.dtype not in (torch.bfloat16, torch.float16):
+        raise abi.MskError("the expert input must be bfloat16 or float16")
+    key = (x.data_ptr(), x.stride(0), x.dtype, ids.data_ptr(), wts.data_ptr(), ids.stride(0), out.data_ptr(), out.stride(0), out.dtype,
            t, top_k, local_start, local_count, splits, pdl,
            None if logits is None else (logits.data_ptr(), logits.stride(0)),
            None if pre_norm is None else (pre_norm[0].data_ptr(), tuple(pre_norm[0].shape), pre_norm[0].stride(0), pre_norm[1], pre_norm[2]),
@@ -100,7 +97,7 @@ def forward(x, ids, wts, state, local_start, local_count, out=None, logits=None,
     s1, s2 = splits or splits_for(t, state["H"], state["I"], local_count, top_k)
     h1, y, inter, xs, pub = scratch(state, t, top_k, s1, s2, x.device)
     p = abi.MoeParams()
-    p.x, p.ldx = abi.ptr(x), x.stride(0)
+    p.x, p.ldx, p.x_fp16 = abi.ptr(x), x.stride(0), int(x.dtype == torch.float16)
     if pre_norm is not None:
         ssq, dim, eps = pre_norm  # [parts, T] contiguous, or one value per token with any stride
         p.x_ssq, p.x_inv_dim, p.x_eps = abi.ptr(ssq), 1.0 / dim, eps
@@ -139,29 +136,39 @@ def kernel_fn(data: dict, state: dict) -> torch.Tensor:
                    logits=logits, pre_norm=data.get("pre_norm"))
 
 
-def dequant(packed: torch.Tensor, e: int, rows: int, k: int) -> torch.Tensor:
-    """Test hook: BF16 [e, rows, k] = e2m1 * block scale, as the kernels' decoder produces it."""
+def dequant(packed: torch.Tensor, e: int, rows: int, k: int, gate_up: bool = False) -> torch.Tensor:
+    """Test hook: BF16 [e, rows, k] = e2m1 * block scale, as the kernels' decoder produces it (rows in the
+    original order; gate_up=True for a packed W13)."""
     out = torch.empty((e, rows, k), dtype=torch.bfloat16, device=packed.device)
-    abi.check(abi.lib().msk_moe_dequant(abi.ptr(packed), abi.ptr(out), e, rows, k, abi.stream_ptr()), "msk_moe_dequant")
+    abi.check(abi.lib().msk_moe_dequant(abi.ptr(packed), abi.ptr(out), e, rows, k, int(gate_up), abi.stream_ptr()), "msk_moe_dequant")
     return out
 
 
-STATIC_SCRATCH_FLOATS = 1 << 20
+STATIC_SCRATCH_BYTES = 4 << 20
+
+
+def static_scratch_bytes(tokens: int, top_k: int, h: int, inner: int, s1: int, s2: int) -> int:
+    """What a call of `msk_moe_forward_static` takes out of the library's built-in array: the five sizes
+    `msk_moe_scratch_bytes` reports, each rounded up to 256 bytes."""
+    parts = [C.c_size_t() for _ in range(5)]
+    abi.check(abi.lib().msk_moe_scratch_bytes(tokens, top_k, h, inner, s1, s2, *[C.byref(v) for v in parts]), "msk_moe_scratch_bytes")
+    return sum((v.value + 255) // 256 * 256 for v in parts)
 
 
 def forward_no_alloc(x, ids, wts, state, local_start, local_count, out, splits=None):
     """The routed experts through `msk_moe_forward_static`: for hosts that cannot give the library scratch
     memory and cannot let it allocate (their pool owns the device, or the step must not stall on an
-    allocation).  The partial buffers sit in a 4 MiB array inside the library, so the call is limited to
-    s1*T*k*2I + s2*T*k*H <= STATIC_SCRATCH_FLOATS; `out` is the caller's.  Calls share that array: keep
+    allocation).  All scratch sits in a 4 MiB array inside the library, so the call is accepted while
+    `static_scratch_bytes(...)` <= STATIC_SCRATCH_BYTES; `out` is the caller's.  Calls share that array: keep
     them in stream order.  Make the first call on a device outside any stream capture."""
     t, h = x.shape
     top_k = ids.shape[1]
     s1, s2 = splits or splits_for(t, state["H"], state["I"], local_count, top_k)
-    if 4 * (s1 * t * top_k * 2 * state["I"] + s2 * t * top_k * state["H"]) + 2 * t * top_k * state["I"] + 4096 > 4 * STATIC_SCRATCH_FLOATS:
-        raise abi.MskError("this step needs more scratch than the library's built-in 4 MiB: use forward()")
+    need = static_scratch_bytes(t, top_k, state["H"], state["I"], s1, s2)
+    if need > STATIC_SCRATCH_BYTES:
+        raise abi.MskError(f"this step needs {need} bytes of scratch, more than the library's built-in {STATIC_SCRATCH_BYTES}: use forward()")
     p = abi.MoeParams()
-    p.x, p.ldx = abi.ptr(x), x.stride(0)
+    p.x, p.ldx, p.x_fp16 = abi.ptr(x), x.stride(0), int(x.dtype == torch.float16)
     p.topk_ids, p.topk_weights, p.T, p.top_k = abi.ptr(ids), abi.ptr(wts), t, top_k
     first = local_start - state["weights_start"]
     blob13 = (2 * state["I"] // 128) * (state["H"] // 128) * 9216

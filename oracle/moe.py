@@ -25,19 +25,20 @@ def post_expert_norm(y: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + POST_NORM_EPS)
 
 
-def expert_forward(x: torch.Tensor, weights, e: int, round_inter: bool = False) -> torch.Tensor:
-    """y = (silu(h[:, :I]) * h[:, I:]) @ W2[e]^T with h = x @ W13[e]^T, FP32 (reference.py:101-103)."""
+def expert_forward(x: torch.Tensor, weights, e: int, round_inter=False) -> torch.Tensor:
+    """y = (silu(h[:, :I]) * h[:, I:]) @ W2[e]^T with h = x @ W13[e]^T, FP32 (reference.py:101-103).
+    round_inter: False, True (= bfloat16) or a 16-bit dtype the activations are rounded to."""
     w13 = nvfp4.dequantize(weights["w13"][e], weights["w13_sf"][e], weights["w13_gs"][e])
     w2 = nvfp4.dequantize(weights["w2"][e], weights["w2_sf"][e], weights["w2_gs"][e])
     inner = w13.shape[0] // 2
     h = x.float() @ w13.T
     inter = torch.nn.functional.silu(h[:, :inner]) * h[:, inner:]
     if round_inter:  # the rounding point kernels add and the rules allow (reference submission.py:478-485)
-        inter = inter.to(torch.bfloat16).float()
+        inter = inter.to(torch.bfloat16 if round_inter is True else round_inter).float()
     return inter @ w2.T
 
 
-def ref_kernel(data, weights, fp32_out: bool = False, round_inter: bool = False) -> torch.Tensor:
+def ref_kernel(data, weights, fp32_out: bool = False, round_inter=False) -> torch.Tensor:
     """out[t] = sum over local (t, slot) pairs of topk_weight * post_norm(expert(x[t]));  bf16 [T,H].
 
     Tokens with no local pair stay zero (reference.py:93-107).

@@ -69,13 +69,13 @@ def _run_and_check(weights, data, what, **tune):
     assert torch.equal(ids.sort(-1).values, buf["logits"].topk(8, -1).indices.sort(-1).values), what
     _check_ids(ids, lg_ref, what)
     # 6. experts + second residual from the kernel's own values, with the kernel's rounding points: the expert
-    #    input is bf16(stream1 * (1 + w)) times the FP32 row scale, silu(gate) * up is rounded to BF16
+    #    input is fp16(stream1 * (1 + w)) times the FP32 row scale, silu(gate) * up is rounded to FP16
     rs = torch.rsqrt(buf["ssq1"][-1] / stream.shape[1] + 1e-5)
     pk = torch.softmax(buf["logits"], -1).gather(1, ids)
     md = {"hidden_states": buf["xn1"].float() * rs[:, None], "topk_ids": ids.to(torch.int32), "topk_weights": pk / pk.sum(-1, keepdim=True),
           "config": {"local_start": 0, "local_count": weights["router"].shape[0]}}
     mw = dict(weights, post_norm_w=weights["post_expert_norm"])
-    ref_stream = buf["stream1"] + omoe.ref_kernel(md, mw, fp32_out=True, round_inter=True)
+    ref_stream = buf["stream1"] + omoe.ref_kernel(md, mw, fp32_out=True, round_inter=torch.float16)
     close(stream, ref_stream, "stream out")
     close(hidden, ref_stream.to(torch.bfloat16), "hidden out")
     # 7. end to end against the pure oracle with the kernel's expert choice

@@ -33,7 +33,7 @@ def test_dequant_is_bit_exact():
     sf[0, 0, :4] = torch.tensor([0, 1, 7, 126], dtype=torch.uint8)
     w["w13_sf"] = sf.view(FP8)
     state = moe.prepare(_dev(w))
-    got = moe.dequant(state["w13"], 2, 256, 256).cpu()
+    got = moe.dequant(state["w13"], 2, 256, 256, gate_up=True).cpu()
     want = nvfp4.dequantize_tile_bf16(w["w13"], w["w13_sf"])
     assert torch.equal(got.view(torch.int16), want.view(torch.int16)) or torch.equal(got.float(), want.float())
     got2 = moe.dequant(state["w2"], 2, 256, 128).cpu()
