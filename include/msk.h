@@ -49,7 +49,8 @@ typedef struct {
     const void* x;          /* bf16 [M, K], row stride K */
     const void* w;          /* bf16 [N, K], row stride K */
     int M, N, K;
-    int splits;             /* split-K ways = cluster size, 1..8; 0 = pick for the device */
+    int splits;             /* split-K ways, 1..16; 0 = pick so that tiles x splits fills the device */
+    int token_splits;       /* CTAs sharing the tokens of a tile, 1..16; 0 = pick (more than one from 128 tokens up) */
     void* out;              /* [M, ldo] bf16, or fp32 when out_fp32 != 0; may be NULL */
     int out_fp32;
     int ldo;
@@ -66,13 +67,20 @@ typedef struct {
     int pdl;                /* launch with programmatic stream serialization (the kernel waits for its
                                predecessor only after it has started streaming W) */
     int normed_fp16;        /* out_normed is written as FP16 (saturating), what the experts' GEMM consumes */
+    void* scratch;          /* split-K workspace, msk_proj_scratch_bytes() bytes, 16-byte aligned: tile tickets (its
+                               first 4096 bytes, zero before the first launch; every launch leaves them zero) and
+                               the FP32 partial tiles.  May be NULL when the launch runs unsplit.  Launches that may
+                               overlap on the GPU need a workspace each. */
+    size_t scratch_bytes;
 } MskProjParams;
 
 int msk_proj_skinny(const MskProjParams* p, int* status, void* stream);
 
-/* Tuning aid (no reference counterpart): clusters of `splits` CTAs with `smem_bytes` of dynamic shared
- * memory that fit on the device at once. */
-int msk_proj_max_active_clusters(int splits, int smem_bytes);
+/* Bytes of the split-K workspace for a launch of that shape on the current device (splits and token_splits as
+ * in MskProjParams).
+ * Stands in for the reference's per-(layer, m) split table (muse_bf16_proj/submission.py:288-314,352-364),
+ * whose partials live in distributed shared memory instead. */
+int msk_proj_scratch_bytes(int M, int N, int K, int splits, int token_splits, size_t* bytes);
 
 /* ---------------------------------------------------------------- gated attention decode / verify
  * One decode step (L = 1) or one 8-token verify block (L = 8, causal inside the block) of gated
@@ -237,6 +245,9 @@ typedef struct {
     float* ssq1;                   /* fp32 [H/128 + 1, T]: per-128-column partial sums of squares, last row their total */
     float* router_part;            /* fp32 [H/128, T, E] */
     int32_t* router_ticket;        /* int32 [ceil(T/32) * (ceil(E/32) + 1)], zero before the first call */
+    void* qkv_scratch;             /* split-K workspaces of the two projections (msk_proj_scratch_bytes for   */
+    void* o_scratch;               /*   [T, (2Hq+2Hkv)*d, H] and [T, H, Hq*d]), first 4096 bytes zero before the */
+    size_t qkv_scratch_bytes, o_scratch_bytes; /* first call */
     float* logits;                 /* fp32 [T, E] */
     int top_k;                     /* <= 8 */
     int32_t* topk_ids;             /* int32 [T, top_k]: softmax -> top-k -> renormalise of the logits, written by */

@@ -30,11 +30,12 @@ class MskError(RuntimeError):
 class ProjParams(C.Structure):
     _fields_ = [
         ("x", C.c_void_p), ("w", C.c_void_p), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("splits", C.c_int),
-        ("out", C.c_void_p), ("out_fp32", C.c_int), ("ldo", C.c_int),
+        ("token_splits", C.c_int), ("out", C.c_void_p), ("out_fp32", C.c_int), ("ldo", C.c_int),
         ("in_ssq", C.c_void_p), ("in_ssq_parts", C.c_int), ("in_inv_dim", C.c_float), ("in_eps", C.c_float),
         ("resid", C.c_void_p), ("ldr", C.c_int),
         ("next_norm_w", C.c_void_p), ("out_normed", C.c_void_p), ("ldn", C.c_int),
         ("out_ssq", C.c_void_p), ("pdl", C.c_int), ("normed_fp16", C.c_int),
+        ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t),
     ]
 
 
@@ -53,7 +54,7 @@ def lib() -> C.CDLL:
         _lib.msk_device_info.argtypes = [vp, vp]
         _lib.msk_selftest_umma.argtypes = [ci, vp, vp, vp, ci, vp, vp]
         _lib.msk_proj_skinny.argtypes = [vp, vp, vp]
-        _lib.msk_proj_max_active_clusters.argtypes = [ci, ci]
+        _lib.msk_proj_scratch_bytes.argtypes = [ci, ci, ci, ci, ci, vp]
         _lib.msk_attn_decode.argtypes = [vp, vp, vp]
         _lib.msk_moe_packed_bytes.argtypes = [ci, ci, ci, vp, vp]
         _lib.msk_moe_pack.argtypes = [vp, vp, vp, vp]
@@ -70,7 +71,7 @@ def lib() -> C.CDLL:
 
 
 # every symbol include/msk.h declares
-EXPORTS = ["msk_version", "msk_device_info", "msk_selftest_umma", "msk_proj_skinny", "msk_proj_max_active_clusters", "msk_attn_decode",
+EXPORTS = ["msk_version", "msk_device_info", "msk_selftest_umma", "msk_proj_skinny", "msk_proj_scratch_bytes", "msk_attn_decode",
            "msk_moe_packed_bytes", "msk_moe_pack", "msk_moe_dequant", "msk_moe_scratch_bytes", "msk_moe_forward", "msk_moe_forward_static", "msk_layer_front", "msk_layer_decode",
            "msk_ep_row_bytes", "msk_ep_pack", "msk_ep_reduce"]
 
@@ -169,6 +170,7 @@ class LayerFront(C.Structure):
         ("router_w", C.c_void_p), ("router_bias", C.c_void_p), ("E", C.c_int),
         ("xn0", C.c_void_p), ("ssq0", C.c_void_p), ("qkv", C.c_void_p), ("attn", C.c_void_p), ("stream1", C.c_void_p),
         ("xn1", C.c_void_p), ("ssq1", C.c_void_p), ("router_part", C.c_void_p), ("router_ticket", C.c_void_p),
+        ("qkv_scratch", C.c_void_p), ("o_scratch", C.c_void_p), ("qkv_scratch_bytes", C.c_size_t), ("o_scratch_bytes", C.c_size_t),
         ("logits", C.c_void_p), ("top_k", C.c_int), ("topk_ids", C.c_void_p), ("topk_weights", C.c_void_p),
         ("attn_chunks", C.c_int), ("attn_stages", C.c_int), ("attn_issuers", C.c_int), ("qkv_splits", C.c_int),
         ("o_splits", C.c_int),

@@ -247,6 +247,7 @@ extern "C" int msk_layer_front(const MskLayerFront* f, int* status, void* stream
     MskProjParams q = {};
     q.x = f->xn0, q.w = f->w_qkv, q.M = T, q.N = nqkv, q.K = H, q.splits = f->qkv_splits;
     q.out = f->qkv, q.out_fp32 = 0, q.ldo = nqkv;
+    q.scratch = f->qkv_scratch, q.scratch_bytes = f->qkv_scratch_bytes;
     q.pdl = 1;
     rc = msk_proj_skinny(&q, status, stream);
     if (rc != 0) return rc;
@@ -266,6 +267,7 @@ extern "C" int msk_layer_front(const MskLayerFront* f, int* status, void* stream
     o.x = f->attn, o.w = f->w_o, o.M = T, o.N = H, o.K = no, o.splits = f->o_splits;
     o.out = f->stream1, o.out_fp32 = 1, o.ldo = H;
     o.resid = f->stream, o.ldr = H;
+    o.scratch = f->o_scratch, o.scratch_bytes = f->o_scratch_bytes;
     o.next_norm_w = f->pre_expert_norm_w, o.out_normed = f->xn1, o.ldn = H, o.normed_fp16 = 1, o.out_ssq = f->ssq1, o.pdl = 1;
     rc = msk_proj_skinny(&o, status, stream);
     if (rc != 0) return rc;

@@ -56,7 +56,10 @@ constexpr int kBSlot = 8192;       // B tile of one stage: 32 rows x 256 bytes (
 // issues one wait, one bulk copy and one tensor copy per 2 chunks (its issue rate was the limit with one chunk
 // per stage).  Units with an odd number of chunks use stages of one chunk (second halves unused).
 constexpr int kStage = 2 * (kBlob + kBSlot);
-constexpr int kNRaw = 5;           // ring stages
+#ifndef MSK_MOE_NRAW
+#define MSK_MOE_NRAW 5
+#endif
+constexpr int kNRaw = MSK_MOE_NRAW;  // ring stages
 // nanoseconds a waiting warp of each role sleeps between polls (the dequant warps, which bound the rate, poll)
 constexpr int kSleepProducer = 200, kSleepIssuer = 40, kSleepEpilogue = 60;
 constexpr int kNA = 4;             // A slots in tensor memory, 64 columns each

@@ -15,7 +15,7 @@ import ctypes as C
 
 import torch
 
-from . import abi, attention, moe
+from . import abi, attention, moe, proj
 
 RMS_EPS = 1e-5
 TOP_K = 8
@@ -76,6 +76,14 @@ def fill_front(f: abi.LayerFront, data: dict, state: dict, buf: dict, tune: dict
     for name in ("xn0", "ssq0", "qkv", "attn", "stream1", "xn1", "ssq1", "router_part", "router_ticket", "logits",
                  "topk_ids", "topk_weights"):
         setattr(f, name, abi.ptr(buf[name]))
+    # split-K workspaces of the two projections (one each: their launches are chained programmatically), kept per
+    # (shape, splits) and allocated on first use
+    t, h = buf["xn0"].shape
+    dev = buf["xn0"].device
+    qs = proj.scratch_for(t, buf["qkv"].shape[1], h, tune.get("qkv_splits", 0), dev, tag=("qkv", id(state)))
+    os_ = proj.scratch_for(t, h, buf["attn"].shape[1], tune.get("o_splits", 0), dev, tag=("o", id(state)))
+    f.qkv_scratch, f.o_scratch = abi.ptr(qs), abi.ptr(os_)
+    f.qkv_scratch_bytes, f.o_scratch_bytes = qs.numel(), os_.numel()
     f.top_k = TOP_K
     f.attn_chunks, f.attn_stages = tune.get("attn_chunks", 0), tune.get("attn_stages", 0)
     f.attn_issuers = tune.get("attn_issuers", 0)

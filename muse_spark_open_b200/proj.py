@@ -37,8 +37,23 @@ def prepare(weights: dict) -> dict:
     return state
 
 
+_scratch: dict = {}
+
+
+def scratch_for(m: int, n: int, k: int, splits: int, device, tag: str = "", token_splits: int = 0) -> torch.Tensor:
+    """The split-K workspace of a launch of that shape (tickets + FP32 partial tiles), allocated and zeroed once
+    per (shape, tag, device) and reused: launches sharing one must be ordered on the stream (they are,
+    unless they overlap by programmatic launch - give those different tags)."""
+    key = (m, n, k, splits, token_splits, tag, torch.device(device).index or 0)
+    if key not in _scratch:
+        nbytes = C.c_size_t()
+        abi.check(abi.lib().msk_proj_scratch_bytes(m, n, k, splits, token_splits, C.byref(nbytes)), "msk_proj_scratch_bytes")
+        _scratch[key] = torch.zeros(nbytes.value, dtype=torch.uint8, device=device)
+    return _scratch[key]
+
+
 def skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, fp32_out: bool = False,
-           splits: int = 0, pdl: bool = False, in_ssq=None, in_dim: int = 0, in_eps: float = 0.0, resid=None,
+           splits: int = 0, token_splits: int = 0, pdl: bool = False, in_ssq=None, in_dim: int = 0, in_eps: float = 0.0, resid=None,
            next_norm_w=None, out_normed=None, out_ssq=None) -> torch.Tensor:
     """One launch of msk_proj_skinny.  x bf16 [M, K] contiguous, w bf16 [N, K] contiguous."""
     m, k = x.shape
@@ -46,7 +61,7 @@ def skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, fp
     if out is None and out_normed is None:
         out = torch.empty((m, n), dtype=torch.float32 if fp32_out else torch.bfloat16, device=x.device)
     p = abi.ProjParams()
-    p.x, p.w, p.M, p.N, p.K, p.splits = abi.ptr(x), abi.ptr(w), m, n, k, splits
+    p.x, p.w, p.M, p.N, p.K, p.splits, p.token_splits = abi.ptr(x), abi.ptr(w), m, n, k, splits, token_splits
     if out is not None:
         p.out, p.out_fp32, p.ldo = abi.ptr(out), int(out.dtype == torch.float32), out.stride(0)
     if in_ssq is not None:
@@ -58,6 +73,8 @@ def skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, fp
     if out_ssq is not None:
         p.out_ssq = abi.ptr(out_ssq)
     p.pdl = int(pdl)
+    ws = scratch_for(m, n, k, splits, x.device, token_splits=token_splits)
+    p.scratch, p.scratch_bytes = abi.ptr(ws), ws.numel()
     st = abi.status_for(x.device)
     abi.check(abi.lib().msk_proj_skinny(C.byref(p), st.p, abi.stream_ptr()), "msk_proj_skinny")
     return out
@@ -70,5 +87,14 @@ def kernel_fn(data: dict, state: dict) -> torch.Tensor:
         raise abi.MskError(f"projection built for decode/verify steps of up to {MAX_M} tokens, got {m}")
     w = state["w"][layer][:n]
     if layer in state["fp32"]:
-        return skinny(torch.cat([x, x], dim=1), w, fp32_out=True)
+        # x against [hi | lo]: the doubled activation row lives in a persistent buffer (two strided copies, no
+        # allocation and no concatenation kernel in the timed call)
+        key = ("xx", m, x.shape[1], x.device)
+        if key not in state:
+            state[key] = torch.empty((m, 2 * x.shape[1]), dtype=x.dtype, device=x.device)
+        xx = state[key]
+        k1 = x.shape[1]
+        xx[:, :k1].copy_(x)
+        xx[:, k1:].copy_(x)
+        return skinny(xx, w, fp32_out=True)
     return skinny(x, w, out=data.get("out"), out_ssq=data.get("ssq"))

@@ -12,7 +12,8 @@ def _check(out, ref, rtol=2e-2, atol=1e-2):
 
 
 @pytest.mark.parametrize("m,n,k,splits", [(16, 6144, 4096, 0), (1, 256, 128, 1), (3, 384, 512, 2), (32, 4096, 4096, 4),
-                                          (17, 200, 192, 3), (33, 1024, 1024, 8), (256, 512, 1024, 2)])
+                                          (17, 200, 192, 3), (33, 1024, 1024, 8), (256, 512, 1024, 2), (200, 384, 512, 0),
+                                          (256, 9216, 4096, 0), (96, 4096, 4096, 0)])
 def test_proj_matches_oracle(m, n, k, splits):
     from muse_spark_open_b200 import abi, proj
     x, w = oproj.make_input(m, n, k, seed=m + n, probes=True)
@@ -43,9 +44,12 @@ def test_proj_golden(golden):
         assert err < (1e-4 if cfg["layer"] == "router" else 1e-2), (name, float(err))
 
 
-def test_proj_fused_epilogue():
+@pytest.mark.parametrize("m,splits,token_splits", [(5, 2, 0), (130, 2, 3), (256, 1, 0), (77, 3, 1)])
+def test_proj_fused_epilogue(m, splits, token_splits):
+    """Row scale from partial sums of squares, FP32 residual, next op's input and per-tile sums of squares, with
+    K splits (partials through the workspace), token splits (each CTA its own tokens) and both."""
     from muse_spark_open_b200 import abi, proj
-    m, n, k = 5, 384, 256
+    n, k = 384, 256
     g = torch.Generator().manual_seed(3)
     xs = torch.randn((m, k), generator=g)
     nw = (0.1 * torch.randn((k,), generator=g)).to(torch.bfloat16)
@@ -57,7 +61,7 @@ def test_proj_fused_epilogue():
     out = torch.empty((m, n), dtype=torch.float32, device="cuda")
     normed = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
     oss = torch.zeros((3, m), dtype=torch.float32, device="cuda")
-    proj.skinny(x_un.cuda(), w.cuda(), out=out, splits=2, in_ssq=ssq.cuda(), in_dim=k, in_eps=1e-5,
+    proj.skinny(x_un.cuda(), w.cuda(), out=out, splits=splits, token_splits=token_splits, in_ssq=ssq.cuda(), in_dim=k, in_eps=1e-5,
                 resid=resid.cuda(), next_norm_w=nxt.cuda(), out_normed=normed, out_ssq=oss)
     torch.cuda.synchronize()
     abi.status_for("cuda").raise_if_set("proj epilogue")
