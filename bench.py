@@ -8,8 +8,15 @@ config: 256 concurrent requests, context uniform in [2048, 16384], full attentio
 heads of 128, page 64, 128 NVFP4 experts (top-8, router logits + per-expert bias N(0, 0.5)).  At N GPUs
 requests and experts are split evenly (strong scaling); at N = 1 one GPU holds everything.  A step is
 one decode step of the layer for all 256 requests; value = tokens / s over all ranks.
-One JSON line on stdout (rank 0).  Extra keys at N = 1: `layer_us_per_step` (the single-GPU layer at
-batch 1 / 16 / 32, context 8192, cold L2), `kernels`, `roofline`, `cpu_baseline`.
+
+Timing: W warm-up steps, then several windows of exactly K steps each, every window bracketed by a barrier
+and a device synchronize and timed with CUDA events on the launching stream (max over ranks); the line
+reports the median window.  `e2e` is the same with the step's inputs copied from pinned host memory and
+its results copied back inside the window.  Untimed, at every N: `parity_check` runs the CPU oracle on the
+first requests of the very workload that is timed and compares.
+One JSON line on stdout (rank 0).  Extra keys at N = 1: `configs` (the benchmark's single-GPU configs: skinny
+projection, attention decode / verify, experts, the layer at batch 1 / 16 / 32 decode and verify, each from a
+cold L2), `layer_us_per_step`, `kernels`, `roofline`, `cpu_baseline`.
 """
 from __future__ import annotations
 
@@ -33,12 +40,20 @@ HIDDEN, HQ, HKV, HEAD, PAGE, NEXP, INNER = 4096, 32, 4, 128, 64, 128, 768
 BIAS_STD = 0.5
 SEED = 0
 METRIC, UNIT = "decoder_layer_decode_tokens_per_s", "tokens/s"
+WINDOWS = 5
+PARITY_REQUESTS = 4
+CPU_SAMPLE_REQUESTS = 64
 
 
-def workload_name(n):
-    return (f"expert-parallel decoder layer decode step: {REQUESTS} requests, ctx U[{CTX_LO},{CTX_HI}], full attention, "
-            f"hidden {HIDDEN}, {HQ}/{HKV} heads x {HEAD}, page {PAGE}, {NEXP} NVFP4 experts top-8 "
-            f"(gate_up [1536,4096], down [4096,768]), requests and experts split over {n} GPU(s)")
+def bench_config(n):
+    """The `config` object of the JSON line; both arms print the same one."""
+    return {
+        "workload": (f"expert-parallel decoder layer decode step: {REQUESTS} requests, ctx U[{CTX_LO},{CTX_HI}], full attention, "
+                     f"hidden {HIDDEN}, {HQ}/{HKV} heads x {HEAD}, page {PAGE}, {NEXP} NVFP4 experts top-8 "
+                     f"(gate_up [1536,4096], down [4096,768]), requests and experts split over {n} GPU(s)"),
+        "l2": "inputs larger than L2 (KV cache 2.4 GB, experts 0.68 GB per step)",
+        "parallelism": f"dp{n} attention x ep{n} experts",
+    }
 
 
 def seq_lens_all():
@@ -55,9 +70,9 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms from before the warm-up to after the last window."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,utilization.gpu")
 
     def __init__(self, index):
         self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
@@ -76,30 +91,22 @@ class ClockSampler:
         self.f.flush()
         rows = [r.split(",") for r in open(self.f.name).read().strip().splitlines() if r.strip()]
         os.unlink(self.f.name)
-        sm = [float(r[0]) for r in rows if r[0].strip().replace(".", "").isdigit()]
+        rows = [r for r in rows if len(r) >= 6 and r[0].strip().replace(".", "").isdigit()]
+        busy = [r for r in rows if len(r) >= 7 and r[6].strip().isdigit() and int(r[6]) > 0] or rows
+        sm = [float(r[0]) for r in busy]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({names[i] for r in rows for i in range(4) if len(r) >= 6 and "Active" in r[2 + i] and "Not" not in r[2 + i]})
+        reasons = sorted({names[i] for r in rows for i in range(4) if "Active" in r[2 + i] and "Not" not in r[2 + i]})
         return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": float(rows[0][1]) if rows else None, "reasons": reasons, "samples": len(rows)}
-
-
-def event_time_ms(fn, steps, stream=None):
-    """Device time of `steps` calls of fn() between two CUDA events on the launching stream."""
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    a.record()
-    for _ in range(steps):
-        fn()
-    b.record()
-    b.synchronize()
-    return a.elapsed_time(b)
+                "sm_max_mhz": float(rows[0][1]) if rows else None, "reasons": reasons, "samples": len(rows),
+                "samples_under_load": len(busy)}
 
 
 def dist_env():
     return int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
 
 
-def cpu_sample(weights_cpu, n_req, threads):
+# ------------------------------------------------------------------------------------------- CPU arm
+def cpu_sample(weights_cpu, n_req, threads, reps=8):
     """The oracle's layer (plain PyTorch restatement of the reference math) on host cores, for the first
     n_req requests of the workload.  Returns seconds for one step of those requests."""
     from oracle import layer as olayer
@@ -107,7 +114,6 @@ def cpu_sample(weights_cpu, n_req, threads):
     seqs = seq_lens_all()[:n_req].tolist()
     data = olayer.make_input(n_req, seqs, SEED + 1, hidden=HIDDEN, hq=HQ, hkv=HKV, d=HEAD, page=PAGE, window=0,
                              rope_theta=0.0)
-    reps = 8  # one step of n_req requests is under a second on a many-core host: repeat it
     t0 = time.perf_counter()
     for _ in range(reps):
         olayer.ref_kernel(data, weights_cpu)
@@ -121,42 +127,131 @@ def run_reference(args):
         return
     from oracle import layer as olayer
     threads = os.cpu_count() or 1
-    n_req = 64
+    n_req = CPU_SAMPLE_REQUESTS
     weights = olayer.make_weights(SEED, hidden=HIDDEN, hq=HQ, hkv=HKV, d=HEAD, n_experts=NEXP, inner=INNER, bias_std=BIAS_STD)
     times = [cpu_sample(weights, n_req, threads) for _ in range(args.warmup + args.steps)][args.warmup:]
-    sec = sum(times) / len(times)
+    sec = statistics.median(times)
     val = n_req / sec
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic", "config": {"workload": workload_name(args.gpus)},
+        "warmup": args.warmup, "ms_per_step": sec * 1e3 * REQUESTS / n_req, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": bench_config(args.gpus),
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": f"8 layer steps for the first {n_req} of the {REQUESTS} requests per timed step"},
+                         "sample": f"per timed step: 8 layer steps of the first {n_req} of the {REQUESTS} requests (same shapes, "
+                                   f"context lengths and weights distribution); tokens/s = {n_req} / seconds per such step"},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
-def single_gpu_extras(weights, dev):
-    """Single-GPU layer at batch 1 / 16 / 32 (context 8192, full attention) from a cold L2, and the
-    four main kernels of the 256-request step timed on their own."""
-    from muse_spark_open_b200 import layer, synth, timing
-    state = layer.prepare(weights)
+# ------------------------------------------------------------------------------------------- parity
+def subset_on_cpu(data, n):
+    """The first n requests of a step's inputs as CPU tensors, with only their KV pages (renumbered)."""
+    cfg = data["config"]
+    page, l = cfg["page_size"], cfg["q_len"]
+    table = data["page_table"][:n].cpu().long()
+    used = torch.unique(table[table >= 0])
+    remap = torch.full((data["k_cache"].shape[0],), -1, dtype=torch.long)
+    remap[used] = torch.arange(used.numel())
+    new_table = torch.where(table >= 0, remap[table.clamp(min=0)], torch.full_like(table, -1))
+    fp8 = data["k_cache"].dtype
+    pick = lambda c: c.view(torch.uint8)[used.to(c.device)].cpu().view(fp8)  # noqa: E731
+    seq = data["seq_lens"][:n].cpu()
+    pos = seq.long()[:, None] + torch.arange(l)
+    sub = {
+        "stream": data["stream"][:n * l].float().cpu(), "seq_lens": seq, "page_table": new_table.to(torch.int32),
+        "k_cache": pick(data["k_cache"]), "v_cache": pick(data["v_cache"]),
+        "k_scale": data["k_scale"].cpu(), "v_scale": data["v_scale"].cpu(), "positions": pos.reshape(-1),
+        "cache_loc": (torch.gather(new_table, 1, pos // page) * page + pos % page).reshape(-1),
+        "config": dict(cfg, batch=n, tokens=n * l),
+    }
+    return sub
+
+
+def parity_check(data, outputs, weights_cpu, n=PARITY_REQUESTS):
+    """Oracle (CPU) against the step's outputs for the first n requests: expert ids (equal, or differing only where
+    the oracle's own logits tie within 1e-4), and the relative L2 error of the residual update per request."""
+    from oracle import layer as olayer
+    from oracle import moe as omoe
+    hidden, stream, ids = (t[:n * data["config"]["q_len"]].cpu() for t in outputs)
+    sub = subset_on_cpu(data, n)
+    fr = olayer.front(sub, weights_cpu)
+    ref_ids = omoe.route_softmax(fr["logits"])[0].long()
+    ids = ids.long()
+    ids_equal = True
+    for t in range(ids.shape[0]):
+        got, want = set(ids[t].tolist()), set(ref_ids[t].tolist())
+        if got != want:
+            a, b = fr["logits"][t, sorted(got - want)], fr["logits"][t, sorted(want - got)]
+            if (a.sort().values - b.sort().values).abs().max() >= 1e-4:
+                ids_equal = False
+    ref_stream, _ = olayer.back(fr, weights_cpu, ids)
+    upd, ref_upd = stream.float() - sub["stream"], ref_stream - sub["stream"]
+    rel = ((upd - ref_upd).norm(dim=-1) / ref_upd.norm(dim=-1)).max()
+    hid_err = (hidden.float() - ref_stream.to(torch.bfloat16).float()).abs().max()
+    ok = bool(ids_equal and rel < 3e-2)
+    return {"requests": n, "max_rel_l2": round(float(rel), 5), "ids_equal": ids_equal, "hidden_max_abs_err": round(float(hid_err), 4),
+            "bound_rel_l2": 3e-2, "pass": ok}
+
+
+# ------------------------------------------------------------------------------------------- single-GPU configs
+def entry(us, byt, peak):
+    gbs = byt / us / 1e3
+    return {"us": round(us, 1), "algorithmic_mb": round(byt / 1e6, 1), "gbs": round(gbs, 1),
+            "frac_of_measured": round(gbs / peak, 3), "frac_of_8tbs": round(gbs / 8000, 3)}
+
+
+def single_gpu_configs(weights, dev, peak):
+    """The benchmark's single-GPU configs, each from a cold L2 (CUDA graph of flush + op, flush subtracted)."""
+    from muse_spark_open_b200 import attention, layer, moe, proj, synth, timing
     out = {}
-    for b in (1, 16, 32):
-        data = synth.make_layer_input(SEED + 100 + b, dev, [8192] * b)
-        _, _, ids = layer.kernel_fn(data, state)
-        torch.cuda.synchronize()
-        us = timing.graph_time_us(lambda: layer.kernel_fn(data, state), reps=5)
-        byt = synth.layer_bytes(weights, data, int(torch.unique(ids).numel()))
-        out[f"batch{b}"] = {"us_per_step": round(us, 1), "algorithmic_mb": round(byt / 1e6, 1), "hbm_gbs": round(byt / us / 1e3, 1),
-                            "frac_of_8tbs": round(byt / us / 1e3 / 8000, 3)}
-        del data
-    return out, state
+    # config 1: skinny projection x[16,4096] . W[6144,4096]^T
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn((16, 4096), generator=g, device=dev).to(torch.bfloat16)
+    w = (0.02 * torch.randn((6144, 4096), generator=g, device=dev)).to(torch.bfloat16)
+    o = torch.empty((16, 6144), dtype=torch.bfloat16, device=dev)
+    out["proj_16x6144x4096"] = entry(timing.graph_time_us(lambda: proj.skinny(x, w, out=o), reps=5),
+                                     6144 * 4096 * 2 + 16 * 4096 * 2 + 16 * 6144 * 2, peak)
+    del x, w, o
+    # config 2: attention, 16 requests with context U[1024, 8192], sliding window 1024, decode and 8-token verify
+    gs = torch.Generator().manual_seed(1)
+    seqs = torch.randint(1024, 8193, (16,), generator=gs).tolist()
+    for l, name in ((1, "decode"), (8, "verify8")):
+        data = synth.make_layer_input(2, dev, seqs, q_len=l, window=1024, rope_theta=1e6)
+        t = 16 * l
+        qkv = torch.randn((t, 9216), generator=g, device=dev).to(torch.bfloat16)
+        ao = torch.empty((t, 4096), dtype=torch.bfloat16, device=dev)
+        keys = sum(min(s, 1023) for s in seqs)
+        us = timing.graph_time_us(lambda: attention.launch(qkv, ao, data, data["config"]), reps=5)
+        out[f"attention_16req_window1024_{name}"] = entry(us, keys * HKV * HEAD * 2 + t * (9216 + 4096) * 2, peak)
+        del data, qkv, ao
+    # config 3: experts, 32 tokens, ids and weights given (softmax top-8 of N(0,1) logits), BF16 input
+    ms = moe.prepare(weights)
+    x = torch.randn((32, HIDDEN), generator=g, device=dev).to(torch.bfloat16)
+    pk, ids = torch.softmax(torch.randn((32, NEXP), generator=g, device=dev), -1).topk(8, -1)
+    ids, wts = ids.to(torch.int32).contiguous(), (pk / pk.sum(-1, keepdim=True)).contiguous()
+    mo = torch.empty((32, HIDDEN), dtype=torch.bfloat16, device=dev)
+    per_exp = sum(weights[k][0].numel() * weights[k][0].element_size() for k in ("w13", "w13_sf", "w2", "w2_sf"))
+    us = timing.graph_time_us(lambda: moe.forward(x, ids, wts, ms, 0, NEXP, out=mo), reps=5)
+    e = entry(us, int(torch.unique(ids).numel()) * per_exp + 2 * 32 * HIDDEN * 2, peak)
+    e["touched_experts"] = int(torch.unique(ids).numel())
+    out["experts_32tokens"] = e
+    del ms, x, mo
+    # config 4: the layer at batch 1 / 16 / 32, context 8192, full attention, decode and 8-token verify
+    state = layer.prepare(weights)
+    for l, name in ((1, "decode"), (8, "verify8")):
+        for b in (1, 16, 32):
+            data = synth.make_layer_input(SEED + 100 + b, dev, [8192] * b, q_len=l)
+            _, _, ids = layer.kernel_fn(data, state)
+            torch.cuda.synchronize()
+            us = timing.graph_time_us(lambda: layer.kernel_fn(data, state), reps=5)
+            out[f"layer_batch{b}_ctx8192_{name}"] = entry(us, synth.layer_bytes(weights, data, int(torch.unique(ids).numel())), peak)
+            del data
+    return out
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes, from the captures summarised under profiles/
 # (attention 32 requests x 8192; experts 32 tokens; projection 16 x 6144 x 4096)
-NCU_TRAFFIC_RATIO = {"attn_decode": 1.014, "moe": 1.019, "proj_skinny": 0.997}
+NCU_TRAFFIC_RATIO = {"attn_decode": 1.014, "experts": 1.019, "proj_skinny": 0.997}
 
 
 def run_ours(args):
@@ -166,6 +261,7 @@ def run_ours(args):
         raise RuntimeError("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
@@ -175,19 +271,18 @@ def run_ours(args):
                                        bias_std=BIAS_STD, expert_range=(e_first, e_count))
     seqs = seq_lens_all()[r_first:r_first + r_count].tolist()
     data = synth.make_layer_input(SEED + 1 + rank, dev, seqs, max_len=CTX_HI)
+    exchange = None
     if world == 1:
         state = layer.prepare(weights)
         step = lambda: layer.kernel_fn(data, state)  # noqa: E731
-        # prep_norm, qkv projection, attention, o projection, router, [gather when > 32 tokens], gemm 1, activation,
-        # gemm 2, combine
-        launches = 9 + (r_count > 32)
+        launches = layer.launches_per_step(r_count)
     else:
         ops = ep.CudaOps(weights, rank, world, NEXP)
         step = lambda: ep.step(data, ops)  # noqa: E731
-        # the five kernels up to the router, the row pack, the experts over all ranks' tokens (4 or 5), the reduce;
-        # NCCL's own kernels (all-gather, all-to-all) are not counted
-        launches = 5 + 1 + 4 + (REQUESTS > 32) + 1
-    for _ in range(max(args.warmup, 3)):
+        launches = ops.launches_per_step(r_count)
+        exchange = ops.exchange
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
         out = step()
     torch.cuda.synchronize()
     abi.status_for(dev).raise_if_set("bench warm-up")
@@ -204,12 +299,18 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t)
 
-    # ---- device-resident timing
-    barrier()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    ms = event_time_ms(step, args.steps)
-    barrier()
-    ms = max_over_ranks(ms)
+    def window(fn):
+        """Device time in ms of exactly args.steps calls, bracketed by barrier + synchronize, max over ranks."""
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        a.record()
+        for _ in range(args.steps):
+            fn()
+        b.record()
+        b.synchronize()
+        barrier()
+        return max_over_ranks(a.elapsed_time(b))
+
     # ---- end to end: this step's inputs come from pinned host memory, its results go back
     host = {k: data[k].cpu().pin_memory() for k in ("stream", "seq_lens", "cache_loc", "page_table")}
     hid_h = torch.empty((r_count, HIDDEN), dtype=torch.bfloat16).pin_memory()
@@ -223,12 +324,40 @@ def run_ours(args):
         ids_h.copy_(ids, non_blocking=True)
 
     e2e_step()
-    barrier()
-    ms_e2e = event_time_ms(e2e_step, args.steps)
-    barrier()
-    ms_e2e = max_over_ranks(ms_e2e)
-    clocks = sampler.stop() if sampler else None
+    # windows of the two kinds alternate, so that drift (clocks, other tenants of the host) hits both alike
+    res, res_e2e = [], []
+    for _ in range(WINDOWS):
+        res.append(window(step))
+        res_e2e.append(window(e2e_step))
+    ms, ms_e2e = statistics.median(res), statistics.median(res_e2e)
     abi.status_for(dev).raise_if_set("bench")
+
+    # ---- parity, untimed: the oracle on the first requests of this very workload (rank 0's requests)
+    par = None
+    if rank == 0:
+        w_full = weights if world == 1 else synth.make_layer_weights(
+            SEED, dev, hidden=HIDDEN, hq=HQ, hkv=HKV, d=HEAD, n_experts=NEXP, inner=INNER, bias_std=BIAS_STD)
+        w_cpu = {k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in w_full.items()}
+    out = step()
+    torch.cuda.synchronize()
+    if rank == 0:
+        par = parity_check(data, out, w_cpu)
+        if world > 1:  # and the expert-parallel step against the single-GPU layer on the same requests
+            n = PARITY_REQUESTS
+            st1 = layer.prepare(w_full)
+            sub = dict(data, config=dict(data["config"], batch=n, tokens=n))
+            for k in ("stream", "seq_lens", "cache_loc", "page_table", "positions"):
+                sub[k] = data[k][:n].contiguous()
+            h1, s1, i1 = layer.kernel_fn(sub, st1)
+            torch.cuda.synchronize()
+            par["vs_single_gpu_layer"] = {"ids_equal": bool(torch.equal(i1, out[2][:n])),
+                                          "stream_max_abs_diff": round(float((s1 - out[1][:n]).abs().max()), 6)}
+            par["pass"] = bool(par["pass"] and par["vs_single_gpu_layer"]["ids_equal"]
+                               and par["vs_single_gpu_layer"]["stream_max_abs_diff"] < 1e-3)
+            del st1, w_full
+        if not par["pass"]:
+            sys.stderr.write(f"bench.py: PARITY CHECK FAILED: {par}\n")
+    clocks = sampler.stop() if sampler else None
     if rank != 0:
         if world > 1:
             dist.barrier()
@@ -238,38 +367,46 @@ def run_ours(args):
     peak, peak_src = peaks()
     h2d = sum(v.numel() * v.element_size() for v in host.values())
     d2h = hid_h.numel() * 2 + ids_h.numel() * 4
+    cfg = bench_config(world)
+    if exchange:
+        cfg["exchange"] = exchange
     line = {
         "metric": METRIC, "value": REQUESTS * args.steps / (ms / 1e3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": workload_name(world), "l2": "inputs larger than L2 (KV cache 2.4 GB, experts 0.68 GB per step)",
-                   "parallelism": f"dp{world} attention x ep{world} experts"},
+        "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg,
         "e2e": {"value": REQUESTS * args.steps / (ms_e2e / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d * world,
                 "d2h_bytes_per_step": d2h * world},
         "gpu_launches": launches * args.steps, "clocks": clocks,
+        "windows": {"count": WINDOWS, "ms_per_step": [round(v / args.steps, 4) for v in res],
+                    "e2e_ms_per_step": [round(v / args.steps, 4) for v in res_e2e], "reported": "median"},
+        "parity_check": par,
     }
+    if ms_e2e < ms:
+        line["e2e"]["note"] = "the end-to-end windows ran faster than the device-resident ones: timing noise exceeds the copies' cost"
     if world == 1 and not args.skip_extras:
         hidden, stream_out, ids = out
         touched = int(torch.unique(ids).numel())
         buf = state["bufs"][r_count]
         ms_state = state["moe"]
-        cfg = data["config"]
+        cfgd = data["config"]
         from muse_spark_open_b200 import attention, moe, proj
         mo = torch.empty((r_count, HIDDEN), dtype=torch.float32, device=dev)
         kv_bytes = sum(seqs) * HKV * HEAD * 2
         per_exp = sum(weights[k][0].numel() * weights[k][0].element_size() for k in ("w13", "w13_sf", "w2", "w2_sf"))
         kern = {
-            "attn_decode": (lambda: attention.launch(buf["qkv"], buf["attn"], data, cfg), kv_bytes + r_count * 9216 * 2 + r_count * 4096 * 2),
-            "moe (gather + gemm1 + act + gemm2 + combine)": (lambda: moe.forward(buf["xn1"], ids, buf["topk_weights"], ms_state, 0, NEXP, out=mo,
-                                                                                 pre_norm=(buf["ssq1"][-1], HIDDEN, 1e-5)),
-                                                             touched * per_exp + 2 * r_count * HIDDEN * 2),
+            "attn_decode": (lambda: attention.launch(buf["qkv"], buf["attn"], data, cfgd), kv_bytes + r_count * 9216 * 2 + r_count * 4096 * 2),
+            "experts (stage + gemm1 + gemm2 + combine)": (lambda: moe.forward(buf["xn1"], ids, buf["topk_weights"], ms_state, 0, NEXP, out=mo,
+                                                                              pre_norm=(buf["ssq1"][-1], HIDDEN, 1e-5)),
+                                                          touched * per_exp + 2 * r_count * HIDDEN * 2),
             "proj_skinny qkv": (lambda: proj.skinny(buf["xn0"], state["qkv_gate"], out=buf["qkv"]), 9216 * 4096 * 2 + r_count * (4096 + 9216) * 2),
             "proj_skinny o": (lambda: proj.skinny(buf["attn"], state["o"], out=buf["stream1"], resid=data["stream"]), 4096 * 4096 * 2 + r_count * 4096 * 10),
         }
         kernels = {}
         for name, (fn, byt) in kern.items():
             us = timing.graph_time_us(fn, reps=3, replays=5, rounds=2)
-            kernels[name] = {"us": round(us, 1), "algorithmic_mb": round(byt / 1e6, 1), "gbs": round(byt / us / 1e3, 1)}
+            kernels[name] = entry(us, byt, peak)
+            ratio = next((r for key, r in NCU_TRAFFIC_RATIO.items() if name.startswith(key)), None)
+            kernels[name]["traffic_mb"] = round(byt * ratio / 1e6, 1) if ratio else None
         top = max(kernels, key=lambda k: kernels[k]["us"])
         line["kernels"] = kernels
         # DRAM traffic of one launch: the kernel's dram__bytes (read + write) from the ncu capture of a smaller case
@@ -282,16 +419,19 @@ def run_ours(args):
         step_bytes = synth.layer_bytes(weights, data, touched)
         line["step_algorithmic_mb"] = round(step_bytes / 1e6, 1)
         line["step_hbm_gbs"] = round(step_bytes / (ms / args.steps) / 1e6, 1)
-        del data, state
+        line["step_frac_of_measured"] = round(step_bytes / (ms / args.steps) / 1e6 / peak, 3)
+        del data, state, buf, ms_state
         torch.cuda.empty_cache()
-        line["layer_us_per_step"], _ = single_gpu_extras(weights, dev)
+        line["configs"] = single_gpu_configs(weights, dev, peak)
+        line["layer_us_per_step"] = {f"batch{b}": {"us_per_step": line["configs"][f"layer_batch{b}_ctx8192_decode"]["us"],
+                                                    "verify8_us_per_step": line["configs"][f"layer_batch{b}_ctx8192_verify8"]["us"],
+                                                    "frac_of_8tbs": line["configs"][f"layer_batch{b}_ctx8192_decode"]["frac_of_8tbs"]}
+                                     for b in (1, 16, 32)}
         # CPU baseline: the oracle on the host cores, a bounded sample of the same workload
-        w_cpu = {k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in weights.items()}
         threads = os.cpu_count() or 1
-        n_req = 64
-        sec = cpu_sample(w_cpu, n_req, threads)
-        line["cpu_baseline"] = {"value": n_req / sec, "unit": UNIT, "cores": threads, "kind": "port",
-                                "sample": f"8 layer steps for the first {n_req} of the {REQUESTS} requests ({8 * sec:.1f} s of CPU time)"}
+        sec = cpu_sample(w_cpu, CPU_SAMPLE_REQUESTS, threads)
+        line["cpu_baseline"] = {"value": CPU_SAMPLE_REQUESTS / sec, "unit": UNIT, "cores": threads, "kind": "port",
+                                "sample": f"8 layer steps for the first {CPU_SAMPLE_REQUESTS} of the {REQUESTS} requests ({8 * sec:.1f} s of CPU time)"}
     print(json.dumps(line))
     if world > 1:
         dist.barrier()
@@ -305,7 +445,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-extras", action="store_true",
-                    help="only the timed step (no per-kernel, per-batch or CPU legs): what a profiler launch list wants")
+                    help="only the timed step (no per-kernel, per-config or CPU legs): what a profiler launch list wants")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.steps > 5:

@@ -86,6 +86,13 @@ class CudaOps:
         self.rank, self.world, self.n_experts, self.tune = rank, world, n_experts, tune
         self.bufs: dict = {}
 
+    exchange = "nccl all-gather (dispatch) + all-to-all (combine)"
+
+    def launches_per_step(self, tokens_local: int) -> int:
+        """This repo's kernels per step and rank (NCCL's own are not counted): the five up to the router, the row
+        pack, the experts over all ranks' tokens (gather, two GEMMs, combine) and the reduce."""
+        return 5 + 1 + 4 + 1
+
     def buffer(self, name, shape, dtype):
         key = (name, shape, dtype)
         if key not in self.bufs:

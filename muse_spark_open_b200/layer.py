@@ -21,6 +21,13 @@ RMS_EPS = 1e-5
 TOP_K = 8
 
 
+def launches_per_step(tokens: int) -> int:
+    """Kernels one layer step launches: input norm, QKV projection, attention, o projection, router, the two expert
+    GEMMs (the first applies the activation) and the combine; above 32 tokens also the pass that gathers the
+    expert inputs into expert-list order."""
+    return 8 + (tokens > 32)
+
+
 def prepare(weights: dict, local_start: int = 0, local_count: int | None = None) -> dict:
     """weights: input_norm, qkv_gate, o, pre_expert_norm, router (fp32), router_bias (optional),
     w13, w13_sf, w13_gs, w2, w2_sf, w2_gs, post_expert_norm (the experts given may be only this
