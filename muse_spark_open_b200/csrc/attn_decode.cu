@@ -22,6 +22,11 @@
 // The L new tokens never travel through global memory: the last CTA of the cluster applies
 // RMSNorm + RoPE to the new keys, quantises keys and values to E4M3, writes them to the cache
 // rows `cache_loc` and attends them from registers / shared memory in FP32.
+// Verify blocks (64 query rows per KV head) run the same tile loop with 512 threads: four row groups of 16 rows,
+// each a full set of four warps (one per 32-key quarter of the tile), so that a thread's serial work per tile is
+// 16 rows, four warps share every scheduler and the instruction latencies overlap (with one warp per scheduler the
+// 64-row loop ran ten times longer per tile than decode's 8 rows); the next tile's scores are issued as soon as
+// this tile's have been read into registers.
 // Merge: every CTA pushes its (m, l, o) partials for the query rows another CTA owns into that
 // CTA's shared memory (DSMEM), one cluster barrier, then each owner merges, applies the per-head
 // RMSNorm and the sigmoid gate and stores BF16.
@@ -104,10 +109,19 @@ __device__ __forceinline__ void norm_rope_row(float (&x)[4], float post_scale, c
     }
 }
 
+template <int L>
+struct AttnShape {
+    static constexpr int RG = L == 1 ? 1 : 4;   // row groups (sets of four warps that split the query rows)
+    static constexpr int kThreads = 128 * RG;
+};
+
 template <int L, int ISS>  // ISS: MMA-issuing warps (one thread issues only ~1 MMA per 100 clocks)
-__global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUtensorMap tm_k,
+__global__ void __launch_bounds__(AttnShape<L>::kThreads) attn_kernel(const __grid_constant__ CUtensorMap tm_k,
                                                    const __grid_constant__ CUtensorMap tm_v, AttnArgs p) {
     constexpr int NR = 8 * L;                 // query rows per KV head
+    constexpr int RG = AttnShape<L>::RG, NTHR = AttnShape<L>::kThreads, NWARP = NTHR / 32;
+    constexpr int NRG = NR / RG;              // query rows per row group: a thread's serial work per tile
+    static_assert(NRG % 8 == 0, "row groups work on blocks of 8 rows");
     constexpr int NP = 2 * NR;                // UMMA N: rows [0, NR) hold the first split term, [NR, 2 NR) the second
     constexpr int SBUF = L == 1 ? 2 : 1;      // score buffers in TMEM (2: the next tile's scores are computed ahead)
     // SBUF * ISS * NP score columns, then ISS * NP output columns, as a power of two
@@ -125,6 +139,9 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
     __shared__ float sc_tail[NR][L];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kq = warp & 3, rg = warp >> 2;  // 32-key quarter of the tile (= tensor-memory lane quarter), row group
+    const int ktid = tid & 127;               // key inside the tile / channel d, depending on the phase
+    const int r_lo = rg * NRG;                // this thread's query rows: [r_lo, r_lo + NRG)
     const int C = gridDim.x, rank = blockIdx.x, h = blockIdx.y;
     int b = blockIdx.z;
     if (p.longest_first) {
@@ -133,9 +150,9 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
         // short requests (list scheduling, longest first).  Every CTA ranks the <= 256 lengths itself.
         __shared__ int lens_s[256];
         __shared__ int b_s;
-        for (int i = threadIdx.x; i < p.B; i += 128) lens_s[i] = p.seq_lens[i];
+        for (int i = threadIdx.x; i < p.B; i += NTHR) lens_s[i] = p.seq_lens[i];
         __syncthreads();
-        for (int j = threadIdx.x; j < p.B; j += 128) {
+        for (int j = threadIdx.x; j < p.B; j += NTHR) {
             const int lj = lens_s[j];
             int r = 0;
             for (int i = 0; i < p.B; ++i) {
@@ -185,7 +202,7 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
         nt = kMaxTilesPerCta;
     }
     const int ppt = kTileKeys / p.page_size;  // pages per tile
-    for (int i = tid; i < nt * ppt; i += 128) {
+    for (int i = tid; i < nt * ppt; i += NTHR) {
         const int pg = t_begin * ppt + i;
         int id = pg < p.max_pages ? p.page_table[b * p.max_pages + pg] : -1;
         if (id >= p.num_pages || id < -1) {
@@ -194,7 +211,7 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
         }
         page_ids[i] = id;
     }
-    for (int i = tid; i < 2 * QP_BYTES / 16; i += 128) reinterpret_cast<uint4*>(g_q)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < 2 * QP_BYTES / 16; i += NTHR) reinterpret_cast<uint4*>(g_q)[i] = make_uint4(0, 0, 0, 0);
     if (tid < NR) m_s[tid] = kNeg;
     tc_fence_before();
     __syncthreads();
@@ -245,7 +262,7 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
     pdl_wait();
     const float k_scale = __ldg(p.k_scale), v_scale = __ldg(p.v_scale);
     const float qs = p.q_split_scale;
-    for (int n = warp; n < NR; n += 4) {
+    for (int n = warp; n < NR; n += NWARP) {
         const int j = n >> 3, g = n & 7;
         const size_t tok = static_cast<size_t>(b) * L + j;
         const __nv_bfloat16* src = p.qkv + tok * p.ld_qkv + (h * 8 + g) * 128 + 4 * lane;
@@ -268,11 +285,11 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
     __syncthreads();
 
     // ---------------- main loop over this CTA's cached tiles
-    float l_part[NR], o_acc[NR];
+    float l_part[NRG], o_acc[NRG];  // of rows r_lo + n
 #pragma unroll
-    for (int n = 0; n < NR; ++n) l_part[n] = 0.0f, o_acc[n] = 0.0f;
+    for (int n = 0; n < NRG; ++n) l_part[n] = 0.0f, o_acc[n] = 0.0f;
     const float s_scale = k_scale * p.sm_scale * 1.4426950408889634f / qs;
-    const uint32_t trow = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    const uint32_t trow = tmem + (static_cast<uint32_t>(kq * 32) << 16);
     bool ok = true;
     // decode keeps the running maxima and the rescale factors replicated in every thread's registers
     float m_r[L == 1 ? 8 : 1], alpha_r[L == 1 ? 8 : 1];
@@ -303,12 +320,12 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
         ok = mbar_wait(bar_o, j & 1, p.status, where | 6) && ok;
         tc_fence_after();
 #pragma unroll
-        for (int c0 = 0; c0 < NR; c0 += 8) {
+        for (int c0 = 0; c0 < NRG; c0 += 8) {
             uint32_t hi[ISS][8], lo[ISS][8];
 #pragma unroll
             for (int w = 0; w < ISS; ++w) {
-                tmem_ld8(trow + kOCol + w * NP + c0, hi[w]);
-                tmem_ld8(trow + kOCol + w * NP + NR + c0, lo[w]);
+                tmem_ld8(trow + kOCol + w * NP + r_lo + c0, hi[w]);
+                tmem_ld8(trow + kOCol + w * NP + NR + r_lo + c0, lo[w]);
             }
             tmem_wait_ld();
 #pragma unroll
@@ -316,7 +333,7 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
                 float a = 0.0f, b = 0.0f;
 #pragma unroll
                 for (int w = 0; w < ISS; ++w) a += __uint_as_float(hi[w][g]), b += __uint_as_float(lo[w][g]);
-                const float al = L == 1 ? alpha_r[g] : alpha_s[c0 + g];
+                const float al = L == 1 ? alpha_r[g] : alpha_s[r_lo + c0 + g];
                 o_acc[c0 + g] = o_acc[c0 + g] * al + (a + b * (1.0f / kLoScale));
             }
         }
@@ -340,24 +357,25 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
         __syncwarp();
         ok = mbar_wait(sbar(i), (SBUF == 2 ? (i >> 1) : i) & 1, p.status, where | 5) && ok;
         tc_fence_after();
-        const int pos = (t_begin + i) * kTileKeys + tid;  // this thread's key position
-        float skeep[L == 1 ? 8 : 1];
+        const int pos = (t_begin + i) * kTileKeys + ktid;  // this thread's key position
+        float skeep[NRG];  // this key's scaled scores of the thread's rows
         // pass 1: tile maximum per query row
 #pragma unroll
-        for (int c0 = 0; c0 < NR; c0 += 8) {
+        for (int c0 = 0; c0 < NRG; c0 += 8) {
             float sc[8];
-            load_scores(i, c0, sc);
-            const int j = c0 >> 3;
+            load_scores(i, r_lo + c0, sc);
+            const int j = (r_lo + c0) >> 3;
             const bool vis = pos < seq && (W == 0 || pos > seq + j - W);
 #pragma unroll
             for (int g = 0; g < 8; ++g) {
                 const float sv = vis ? sc[g] * s_scale : kNeg;
-                if (L == 1) skeep[g] = sv;
+                skeep[c0 + g] = sv;
                 const float mx = redux_max(sv);
-                if (lane == 0) wred[warp][c0 + g] = mx;
+                if (lane == 0) wred[kq][r_lo + c0 + g] = mx;
             }
         }
         if (i > 0) finish_tile(i - 1);
+        if constexpr (SBUF == 1) tc_fence_before();  // the scores are in registers: their buffer may be overwritten
         __syncthreads();
         if constexpr (L == 1) {
             // every thread folds the four warps' maxima itself: no second barrier, no shared-memory round trip
@@ -376,37 +394,43 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
                 alpha_r[g] = ex2(m_r[g] - mn);
                 m_r[g] = mn;
             }
-        } else if (tid < NR) {
-            const float mo = m_s[tid];
-            const float mn = fmaxf(fmaxf(fmaxf(wred[0][tid], wred[1][tid]), fmaxf(wred[2][tid], wred[3][tid])), mo);
-            alpha_s[tid] = ex2(mo - mn);
-            m_s[tid] = mn;
+        } else {
+            if (tid < NR) {
+                const float mo = m_s[tid];
+                const float mn = fmaxf(fmaxf(fmaxf(wred[0][tid], wred[1][tid]), fmaxf(wred[2][tid], wred[3][tid])), mo);
+                alpha_s[tid] = ex2(mo - mn);
+                m_s[tid] = mn;
+            }
+            // one score buffer: the next tile's scores start now, under this tile's exponentials
+            if (issuer && ok && i + 1 < nt) {
+                ok = mbar_wait(full((i + 1) % nst), ((i + 1) / nst) & 1, p.status, where | 4);
+                tc_fence_after();
+                if (ok) issue_mma1(i + 1);
+            }
+            __syncwarp();
         }
         // V rows past the cached length may hold anything (even NaN bytes): zero them so that 0 * V stays 0
-        if (pos >= seq) {
-            uint8_t* vrow = gbase + (i % nst) * kStageBytes + kTileKeys * 128 + tid * 128;
+        if (rg == 0 && pos >= seq) {
+            uint8_t* vrow = gbase + (i % nst) * kStageBytes + kTileKeys * 128 + ktid * 128;
 #pragma unroll
             for (int c = 0; c < 8; ++c) reinterpret_cast<uint4*>(vrow)[c] = make_uint4(0, 0, 0, 0);
         }
         if constexpr (L != 1) __syncthreads();
         // pass 2: p = 2^(s - m) as two E4M3 terms (the second times 16), bytes of the B operand P[row][key]
 #pragma unroll
-        for (int c0 = 0; c0 < NR; c0 += 8) {
-            float sc[8];
-            if (L != 1) load_scores(i, c0, sc);
-            const int j = c0 >> 3;
+        for (int c0 = 0; c0 < NRG; c0 += 8) {
+            const int j = (r_lo + c0) >> 3;
             const bool vis = pos < seq && (W == 0 || pos > seq + j - W);
 #pragma unroll
             for (int g = 0; g < 8; ++g) {
-                const int n = c0 + g;
-                const float sv = L == 1 ? skeep[g] : (vis ? sc[g] * s_scale : kNeg);
-                const float pr = vis ? ex2(sv - (L == 1 ? m_r[g] : m_s[n])) : 0.0f;
-                l_part[n] = l_part[n] * (L == 1 ? alpha_r[g] : alpha_s[n]) + pr;
+                const int n = r_lo + c0 + g;
+                const float pr = vis ? ex2(skeep[c0 + g] - (L == 1 ? m_r[g] : m_s[n])) : 0.0f;
+                l_part[c0 + g] = l_part[c0 + g] * (L == 1 ? alpha_r[g] : alpha_s[n]) + pr;
                 const float ps = pr * kPScale;
                 const uint32_t bh = f_to_e4m3(ps);
                 const uint32_t bl = f_to_e4m3((ps - e4m3_to_f(bh)) * kLoScale);
-                g_p[swz128(n, tid)] = static_cast<uint8_t>(bh);
-                g_p[swz128(NR + n, tid)] = static_cast<uint8_t>(bl);
+                g_p[swz128(n, ktid)] = static_cast<uint8_t>(bh);
+                g_p[swz128(NR + n, ktid)] = static_cast<uint8_t>(bl);
             }
         }
         tc_fence_before();
@@ -415,11 +439,6 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
         if (issuer && ok) {
             tc_fence_after();
             issue_mma2(i);
-            if (SBUF == 1 && i + 1 < nt) {  // one score buffer: the next tile's scores can only start now
-                ok = mbar_wait(full((i + 1) % nst), ((i + 1) / nst) & 1, p.status, where | 4);
-                tc_fence_after();
-                if (ok) issue_mma1(i + 1);
-            }
         }
         __syncwarp();
     }
@@ -436,7 +455,7 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
         float* knew = reinterpret_cast<float*>(gbase);                 // [L][128] E4M3 values of the new keys
         float* vnew = knew + L * 128;                                  // [L][128]
         __nv_bfloat16* qf = reinterpret_cast<__nv_bfloat16*>(vnew + L * 128);  // [NR][128] BF16 queries
-        for (int j = warp; j < L; j += 4) {
+        for (int j = warp; j < L; j += NWARP) {
             const size_t tok = static_cast<size_t>(b) * L + j;
             const long long row = p.cache_loc[tok];
             const bool row_ok = row >= 0 && row < static_cast<long long>(p.num_pages) * p.page_size;
@@ -463,7 +482,7 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
             }
         }
         // BF16 queries again (the MMA operands hold them split)
-        for (int n = warp; n < NR; n += 4) {
+        for (int n = warp; n < NR; n += NWARP) {
             const int j = n >> 3, g = n & 7;
             const size_t tok = static_cast<size_t>(b) * L + j;
             const uint2 raw = *reinterpret_cast<const uint2*>(p.qkv + tok * p.ld_qkv + (h * 8 + g) * 128 + 4 * lane);
@@ -474,7 +493,7 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
         __syncthreads();
         // scores of (row n, new token r), r <= token of n (causal) and inside the window
         const float t_scale = k_scale * p.sm_scale * 1.4426950408889634f;
-        for (int e = tid; e < NR * L; e += 128) {
+        for (int e = tid; e < NR * L; e += NTHR) {
             const int n = e / L, r = e % L, j = n >> 3;
             float acc = 0.0f;
             for (int d = 0; d < 128; d += 2) {
@@ -494,16 +513,16 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
         }
         __syncthreads();
 #pragma unroll
-        for (int n = 0; n < NR; ++n) {
-            const float a = alpha_s[n], m = m_s[n];
+        for (int n = 0; n < NRG; ++n) {
+            const float a = alpha_s[r_lo + n], m = m_s[r_lo + n];
             float o = o_acc[n] * a;
             l_part[n] *= a;
 #pragma unroll
             for (int r = 0; r < L; ++r) {
-                const float sc = sc_tail[n][r];
+                const float sc = sc_tail[r_lo + n][r];
                 const float pr = sc > 0.5f * kNeg ? ex2(sc - m) : 0.0f;
-                o += pr * kPScale * vnew[r * 128 + tid];
-                if (tid == r) l_part[n] += pr;
+                o += pr * kPScale * vnew[r * 128 + ktid];
+                if (ktid == r) l_part[n] += pr;
             }
             o_acc[n] = o;
         }
@@ -511,9 +530,9 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
 
     // ---------------- merge across the cluster
 #pragma unroll
-    for (int n = 0; n < NR; ++n) {
+    for (int n = 0; n < NRG; ++n) {
         const float s = warp_sum(l_part[n]);
-        if (lane == 0) wred[warp][n] = s;
+        if (lane == 0) wred[kq][r_lo + n] = s;
     }
     __syncthreads();
     const int rows_per = NR / C;  // query rows each CTA finalises (C divides NR)
@@ -524,15 +543,17 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
         dsmem_st_f32(dsmem_addr(smem_u32(&mrg_l[rank * rows_per + nl]), owner), lsum);
     }
 #pragma unroll
-    for (int n = 0; n < NR; ++n) {
-        const int owner = n / rows_per, nl = n % rows_per;
-        dsmem_st_f32(dsmem_addr(s_mrg + ((rank * rows_per + nl) * 128 + tid) * 4, owner), o_acc[n]);
+    for (int n = 0; n < NRG; ++n) {
+        const int owner = (r_lo + n) / rows_per, nl = (r_lo + n) % rows_per;
+        dsmem_st_f32(dsmem_addr(s_mrg + ((rank * rows_per + nl) * 128 + ktid) * 4, owner), o_acc[n]);
     }
     cluster_sync_all();
 
-    float val[NR];
+    // this CTA's rows nl = rg, rg + RG, ...: thread = channel d
+    float val[NRG];
 #pragma unroll
-    for (int nl = 0; nl < NR; ++nl) {
+    for (int k = 0; k < NRG; ++k) {
+        const int nl = rg + k * RG;
         if (nl >= rows_per) break;
         float mx = kNeg;
         for (int src = 0; src < C; ++src) mx = fmaxf(mx, mrg_m[src * rows_per + nl]);
@@ -540,35 +561,34 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ CUten
         for (int src = 0; src < C; ++src) {
             const float wgt = ex2(mrg_m[src * rows_per + nl] - mx);
             lsum += wgt * mrg_l[src * rows_per + nl];
-            o += wgt * mrg_o[(src * rows_per + nl) * 128 + tid];
+            o += wgt * mrg_o[(src * rows_per + nl) * 128 + ktid];
         }
         const float vv = lsum > 0.0f ? o * (v_scale / kPScale) / lsum : 0.0f;
-        val[nl] = vv;
+        val[k] = vv;
         const float ss = warp_sum(vv * vv);
-        if (lane == 0) wred[warp][nl] = ss;
+        if (lane == 0) wred[kq][nl] = ss;
     }
-    // decode: the gates of this CTA's rows are requested together (a load between two stores is not moved up by
-    // the compiler, and one global round trip per row is most of this epilogue)
-    float gate_r[L == 1 ? NR : 1];
-    if constexpr (L == 1) {
+    // the gates of this thread's rows are requested together (a load between two stores is not moved up by the
+    // compiler, and one global round trip per row is most of this epilogue)
+    float gate_r[NRG];
 #pragma unroll
-        for (int nl = 0; nl < NR; ++nl) {
-            const int n = rank * rows_per + nl;
-            gate_r[nl] = nl < rows_per ? __bfloat162float(p.qkv[static_cast<size_t>(b) * p.ld_qkv + (p.Hq + 2 * p.Hkv + h * 8 + (n & 7)) * 128 + tid]) : 0.0f;
-        }
+    for (int k = 0; k < NRG; ++k) {
+        const int nl = rg + k * RG, n = rank * rows_per + nl;
+        const size_t tok = static_cast<size_t>(b) * L + (n >> 3);
+        gate_r[k] = nl < rows_per ? __bfloat162float(p.qkv[tok * p.ld_qkv + (p.Hq + 2 * p.Hkv + h * 8 + (n & 7)) * 128 + ktid]) : 0.0f;
     }
     __syncthreads();
     if (ok) {
 #pragma unroll
-        for (int nl = 0; nl < NR; ++nl) {
+        for (int k = 0; k < NRG; ++k) {
+            const int nl = rg + k * RG;
             if (nl >= rows_per) break;
             const int n = rank * rows_per + nl, j = n >> 3, g = n & 7;
             const size_t tok = static_cast<size_t>(b) * L + j;
             const float ss = (wred[0][nl] + wred[1][nl]) + (wred[2][nl] + wred[3][nl]);
             const float r = 1.0f / sqrtf(ss * (1.0f / 128.0f) + 1e-5f);
-            const float gate = L == 1 ? gate_r[nl] : __bfloat162float(p.qkv[tok * p.ld_qkv + (p.Hq + 2 * p.Hkv + h * 8 + g) * 128 + tid]);
-            const float sg = 1.0f / (1.0f + __expf(-gate));
-            p.out[tok * p.ld_out + (h * 8 + g) * 128 + tid] = __float2bfloat16(val[nl] * r * sg);
+            const float sg = 1.0f / (1.0f + __expf(-gate_r[k]));
+            p.out[tok * p.ld_out + (h * 8 + g) * 128 + ktid] = __float2bfloat16(val[k] * r * sg);
         }
     }
     tc_fence_before();
@@ -630,15 +650,17 @@ int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
     while (qs * qmax > 448.0f && qs > 1.0f / 65536.0f) qs *= 0.5f;
     a.q_split_scale = qs, a.status = status;
 
-    static int configured = 0;
-    if (smem > configured) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MSK_ERR_CUDA;
+    static int configured[64] = {};  // per device, like the attribute itself
+    if (smem > configured[dev]) {
         if (cudaFuncSetAttribute(attn_kernel<L, ISS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return MSK_ERR_CUDA;
-        configured = smem;
+        configured[dev] = smem;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(C, q->Hkv, q->B);
-    cfg.blockDim = dim3(128, 1, 1);
+    cfg.blockDim = dim3(AttnShape<L>::kThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attrs[2];
