@@ -271,7 +271,6 @@ def run_ours(args):
                                        bias_std=BIAS_STD, expert_range=(e_first, e_count))
     seqs = seq_lens_all()[r_first:r_first + r_count].tolist()
     data = synth.make_layer_input(SEED + 1 + rank, dev, seqs, max_len=CTX_HI)
-    exchange = None
     if world == 1:
         state = layer.prepare(weights)
         step = lambda: layer.kernel_fn(data, state)  # noqa: E731
@@ -280,7 +279,6 @@ def run_ours(args):
         ops = ep.CudaOps(weights, rank, world, NEXP)
         step = lambda: ep.step(data, ops)  # noqa: E731
         launches = ops.launches_per_step(r_count)
-        exchange = ops.exchange
     warm = max(args.warmup, 3)
     for _ in range(warm):
         out = step()
@@ -350,10 +348,12 @@ def run_ours(args):
                 sub[k] = data[k][:n].contiguous()
             h1, s1, i1 = layer.kernel_fn(sub, st1)
             torch.cuda.synchronize()
-            par["vs_single_gpu_layer"] = {"ids_equal": bool(torch.equal(i1, out[2][:n])),
-                                          "stream_max_abs_diff": round(float((s1 - out[1][:n]).abs().max()), 6)}
-            par["pass"] = bool(par["pass"] and par["vs_single_gpu_layer"]["ids_equal"]
-                               and par["vs_single_gpu_layer"]["stream_max_abs_diff"] < 1e-3)
+            upd1, upd = s1 - sub["stream"], out[1][:n] - sub["stream"]
+            rel = float(((upd - upd1).norm(dim=-1) / upd1.norm(dim=-1)).max())
+            # (the four requests alone take the experts' few-token path: other K splits, so FP32 sums in another order)
+            par["vs_single_gpu_layer"] = {"ids_equal": bool(torch.equal(i1, out[2][:n])), "update_max_rel_l2": round(rel, 6),
+                                          "bound_rel_l2": 1e-2}
+            par["pass"] = bool(par["pass"] and par["vs_single_gpu_layer"]["ids_equal"] and rel < 1e-2)
             del st1, w_full
         if not par["pass"]:
             sys.stderr.write(f"bench.py: PARITY CHECK FAILED: {par}\n")
@@ -368,8 +368,11 @@ def run_ours(args):
     h2d = sum(v.numel() * v.element_size() for v in host.values())
     d2h = hid_h.numel() * 2 + ids_h.numel() * 4
     cfg = bench_config(world)
-    if exchange:
-        cfg["exchange"] = exchange
+    exchange = None
+    if world > 1:
+        exchange = {"kind": ops.exchange}
+        if ops.peer_error:
+            exchange["peer_exchange_unavailable"] = ops.peer_error
     line = {
         "metric": METRIC, "value": REQUESTS * args.steps / (ms / 1e3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
@@ -379,7 +382,7 @@ def run_ours(args):
         "gpu_launches": launches * args.steps, "clocks": clocks,
         "windows": {"count": WINDOWS, "ms_per_step": [round(v / args.steps, 4) for v in res],
                     "e2e_ms_per_step": [round(v / args.steps, 4) for v in res_e2e], "reported": "median"},
-        "parity_check": par,
+        "parity_check": par, "exchange": exchange,
     }
     if ms_e2e < ms:
         line["e2e"]["note"] = "the end-to-end windows ran faster than the device-resident ones: timing noise exceeds the copies' cost"

@@ -147,6 +147,23 @@ int msk_moe_dequant(const void* packed, void* out_bf16, int E, int R, int K, int
 int msk_moe_scratch_bytes(int T, int top_k, int H, int I, int s1, int s2, size_t* h1_bytes, size_t* y_bytes,
                           size_t* inter_bytes, size_t* x_sorted_bytes, size_t* route_bytes);
 
+/* Hooks that turn msk_moe_forward into one rank's share of the expert-parallel step (see msk_ep_step): the
+ * input rows arrive from other GPUs (the first kernel waits for their flags) and every token's partial result
+ * row is stored straight into its home GPU's memory; when all rows are written the last block sets a flag in
+ * every peer.  No counterpart in the reference (one GPU, collectives stated as identities,
+ * muse_decode_layer/reference.py:8-10). */
+typedef struct {
+    const int32_t* wait_flags;  /* local device int32[wait_count]; the first kernel waits (bounded) until each >= wait_value */
+    int wait_count, wait_value;
+    long long wait_cycles;      /* budget of one wait in SM clocks; 0 = about half a second */
+    void* const* peers;         /* device array [n_peers] of the peers' regions as mapped on this GPU; NULL = rows stay local */
+    int n_peers, rows_per_peer; /* token t is at home on peer t / rows_per_peer */
+    size_t out_off;             /* byte offset, inside a peer's region, of this rank's block of FP32 rows [rows_per_peer, ldo] */
+    size_t flag_off;            /* byte offset of the int32 this rank sets to flag_value in every peer's region at the end */
+    int flag_value;
+    int32_t* done_counter;      /* local device int32, zero before the first call (left zero by every call) */
+} MskEpHooks;
+
 typedef struct {
     const void* x;              /* [T, ldx] bf16, or fp16 when x_fp16 != 0 */
     int ldx;
@@ -185,6 +202,7 @@ typedef struct {
     int ldc;
     int pdl;
     int x_fp16;                 /* x is FP16 already (the layer's o_proj epilogue writes it so) */
+    const MskEpHooks* ep;       /* expert-parallel hooks (host pointer, read during the call); NULL = single GPU */
 } MskMoeParams;
 
 int msk_moe_forward(const MskMoeParams* p, int* status, void* stream);
@@ -265,18 +283,70 @@ typedef struct {
 
 int msk_layer_decode(const MskLayerParams* p, int* status, void* stream);
 
-/* ---------------------------------------------------------------- expert-parallel exchange helpers
+/* ---------------------------------------------------------------- expert-parallel step
  * The reference runs one GPU and states its collectives as identities (muse_decode_layer/reference.py:8-10,
- * :467 "the all-reduce: identity"); these kernels sit on either side of the real exchange that replaces
- * that identity: rows packed by msk_ep_pack (expert input, expert choice, row scale) are gathered to every rank (dispatch), each rank runs
- * msk_moe_forward over all tokens with its own experts, the FP32 partials go back to the tokens' home
- * ranks (combine) and msk_ep_reduce adds them to the residual in rank order.
+ * :467 "the all-reduce: identity"); here the exchange is real.  Requests are data-parallel (rank r owns T_local
+ * tokens), experts expert-parallel (rank r holds experts [r*E/world, (r+1)*E/world)), dense weights replicated.
+ *
+ * Device-initiated exchange (msk_ep_step): every rank owns one "region" of device memory that all peers map
+ * (CUDA IPC).  Per step, with buffers chosen by the parity of the step number:
+ *   dispatch   a kernel packs each local token's row (expert input fp16 | expert ids | weights | sum of squares)
+ *              and stores it into EVERY peer's region (plain stores over NVLink); the last block sets
+ *              dispatch_flag[rank] = step in every peer.
+ *   experts    msk_moe_forward over all world * T_local rows of the own region with the local experts; its first
+ *              kernel waits (bounded) for every source's dispatch flag; the combine kernel stores each token's
+ *              weighted, post-normed partial row into the token's home region (tokens without a local expert
+ *              send nothing) and finally sets combine_flag[rank] = step in every peer.
+ *   reduce     waits (bounded) for every rank's combine flag, then out[t] = stream1[t] + the partial rows of the
+ *              ranks that hold one of the token's experts, added in rank order (bitwise reproducible).
+ * No collective library call, no host synchronisation; an expired wait records MSK_ERR_TIMEOUT in `status` and
+ * the kernels run to their end.  A buffer is reused two steps later, by which time every reader is done (a rank
+ * starts step s only after its reduce of step s - 1, which needed every peer's combine of step s - 1).
+ *
+ * Region layout (msk_ep_region_bytes): int32 dispatch flags [2][64] | int32 combine flags [2][64] |
+ * rows uint8 [2][world * T_local][row_bytes] | partials fp32 [2][world][T_local][H].
  */
 int msk_ep_row_bytes(int H, int top_k); /* 2H (x, 2-byte elements) + 4k ids + 4k weights (padded to 16) + 16 (sum of squares, padding) */
+int msk_ep_region_bytes(int world, int T_local, int H, int top_k, size_t* bytes);
+
+/* Set-up helpers, the only entry points of this library that allocate or map memory: a zeroed region from
+ * cudaMalloc with its 64-byte CUDA IPC handle; a peer's region opened from its handle; their release. */
+int msk_ep_region_alloc(size_t bytes, void** ptr, void* handle64);
+int msk_ep_region_open(const void* handle64, void** ptr);
+int msk_ep_region_close(void* ptr);
+int msk_ep_region_free(void* ptr);
+
+typedef struct {
+    int rank, world, T_local, n_experts;
+    int step;                  /* 1, 2, 3, ...: the same on every rank, one more each call */
+    void* self;                /* this rank's region */
+    void* const* peers;        /* device array [world]: every rank's region as mapped on this GPU (peers[rank] = self) */
+    int32_t* counters;         /* local device int32[2], zero before the first step */
+    long long wait_cycles;     /* budget of one wait for a peer's flag, SM clocks; 0 = about half a second */
+} MskEpComm;
+
+typedef struct {
+    MskLayerFront front;       /* this rank's requests up to the router's expert choice */
+    MskMoeParams moe;          /* local experts and scratch for world * T_local tokens; x, ids, weights, x_ssq, T, resid,
+                                  out and ep are filled in from `comm` */
+    MskEpComm comm;
+    float* out;                /* fp32 [T_local, H] stream after the layer */
+    void* hidden;              /* bf16 [T_local, H] copy, or NULL */
+} MskEpStep;
+
+int msk_ep_step(const MskEpStep* p, int* status, void* stream);
+
+/* The same step's kernels for an exchange done by a collective library instead (NCCL all-gather of the rows,
+ * all-to-all of the partials): rows packed by msk_ep_pack, msk_moe_forward over the gathered rows, msk_ep_reduce
+ * adds the ranks' partials to the residual in rank order. */
 int msk_ep_pack(const void* xn, const int32_t* topk_ids, const float* topk_weights, const float* ssq, int ssq_parts,
                 void* rows, int T, int H, int top_k, void* stream);
 int msk_ep_reduce(const float* stream1, const float* recv /* [ranks, T, H] */, int ranks, float* out, void* out_bf16,
                   int T, int H, void* stream);
+
+/* Test hook for the bounded wait between GPUs: one block waits wait_cycles SM clocks for an int32 flag that
+ * nothing sets, must record MSK_ERR_TIMEOUT in status and return (no fault, no hang). */
+int msk_selftest_flag_timeout(const int32_t* flag, long long wait_cycles, int* status, void* stream);
 
 #ifdef __cplusplus
 }

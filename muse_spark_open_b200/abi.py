@@ -65,6 +65,13 @@ def lib() -> C.CDLL:
         _lib.msk_layer_front.argtypes = [vp, vp, vp]
         _lib.msk_layer_decode.argtypes = [vp, vp, vp]
         _lib.msk_ep_row_bytes.argtypes = [ci, ci]
+        _lib.msk_ep_region_bytes.argtypes = [ci, ci, ci, ci, vp]
+        _lib.msk_ep_region_alloc.argtypes = [C.c_size_t, vp, vp]
+        _lib.msk_ep_region_open.argtypes = [vp, vp]
+        _lib.msk_ep_region_close.argtypes = [vp]
+        _lib.msk_ep_region_free.argtypes = [vp]
+        _lib.msk_ep_step.argtypes = [vp, vp, vp]
+        _lib.msk_selftest_flag_timeout.argtypes = [vp, C.c_longlong, vp, vp]
         _lib.msk_ep_pack.argtypes = [vp, vp, vp, vp, ci, vp, ci, ci, ci, vp]
         _lib.msk_ep_reduce.argtypes = [vp, vp, ci, vp, vp, ci, ci, vp]
     return _lib
@@ -73,7 +80,8 @@ def lib() -> C.CDLL:
 # every symbol include/msk.h declares
 EXPORTS = ["msk_version", "msk_device_info", "msk_selftest_umma", "msk_proj_skinny", "msk_proj_scratch_bytes", "msk_attn_decode",
            "msk_moe_packed_bytes", "msk_moe_pack", "msk_moe_dequant", "msk_moe_scratch_bytes", "msk_moe_forward", "msk_moe_forward_static", "msk_layer_front", "msk_layer_decode",
-           "msk_ep_row_bytes", "msk_ep_pack", "msk_ep_reduce"]
+           "msk_ep_row_bytes", "msk_ep_pack", "msk_ep_reduce", "msk_ep_region_bytes", "msk_ep_region_alloc", "msk_ep_region_open",
+           "msk_ep_region_close", "msk_ep_region_free", "msk_ep_step", "msk_selftest_flag_timeout"]
 
 
 def ptr(t: torch.Tensor | None) -> int | None:
@@ -155,6 +163,7 @@ class MoeParams(C.Structure):
         ("route_pub", C.c_void_p), ("s1", C.c_int), ("s2", C.c_int),
         ("resid", C.c_void_p), ("ldr", C.c_int), ("out", C.c_void_p), ("out_fp32", C.c_int), ("ldo", C.c_int),
         ("out_copy", C.c_void_p), ("ldc", C.c_int), ("pdl", C.c_int), ("x_fp16", C.c_int),
+        ("ep", C.c_void_p),
     ]
 
 
@@ -180,3 +189,12 @@ class LayerFront(C.Structure):
 
 class LayerParams(C.Structure):
     _fields_ = [("front", LayerFront), ("moe", MoeParams)]
+
+
+class EpComm(C.Structure):
+    _fields_ = [("rank", C.c_int), ("world", C.c_int), ("T_local", C.c_int), ("n_experts", C.c_int), ("step", C.c_int),
+                ("self", C.c_void_p), ("peers", C.c_void_p), ("counters", C.c_void_p), ("wait_cycles", C.c_longlong)]
+
+
+class EpStep(C.Structure):
+    _fields_ = [("front", LayerFront), ("moe", MoeParams), ("comm", EpComm), ("out", C.c_void_p), ("hidden", C.c_void_p)]

@@ -309,6 +309,9 @@ struct MoeStageArgs {
     const void* x;     // [T, ldx] BF16, or FP16 when x_fp16
     int ldx, H, x_fp16, direct;
     __half* x16;       // [T, H] (direct) or [T*top_k, H]
+    const int* wait_flags;  // expert parallelism: the rows of x arrive from other GPUs; entry i >= wait_value when
+    int wait_count, wait_value;  // source i's rows are complete
+    long long wait_cycles;
     int* status;
 };
 
@@ -322,6 +325,11 @@ __global__ void __launch_bounds__(kRouteThreads) moe_stage_kernel(MoeStageArgs p
     __shared__ RouteTables rt;
     pdl_wait();
     pdl_launch_dependents();
+    if (p.wait_flags != nullptr) {
+        if (static_cast<int>(threadIdx.x) < p.wait_count)
+            flag_wait_ge(p.wait_flags + threadIdx.x, p.wait_value, p.wait_cycles, p.status, (MSK_K_EP << 8) | 1);
+        __syncthreads();
+    }
     int n_rows = p.route.T;
     if (!p.direct) {
         RouteArgs ra = p.route;
@@ -678,12 +686,36 @@ struct MoeCombineArgs {
     int out_fp32, ldo;
     __nv_bfloat16* out_copy;  // optional BF16 copy of the result
     int ldc;
+    // expert parallelism: the row of token t goes to GPU t / rows_per_peer, at byte offset out_off of its region,
+    // row t % rows_per_peer; tokens without a local expert send nothing.  The last block to finish sets the
+    // int32 at flag_off of every peer's region to flag_value.
+    void* const* peers;
+    int n_peers, rows_per_peer;
+    size_t out_off, flag_off;
+    int flag_value;
+    int* done_counter;
 };
 
 // One CTA per token, 512 threads, each owning 4 output channels per 2048 of H: all the token's slots and K
 // splits are loaded back to back (memory-level parallelism instead of a dependent loop), kept in registers
 // for the second pass.
 constexpr int kCombineThreads = 512;
+
+// Expert parallelism: every block, after its row is on its way, takes a ticket; the last one tells every peer
+// that this GPU's partial rows of the step are complete.
+__device__ __forceinline__ void combine_signal(const MoeCombineArgs& p, int tid) {
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) {
+        const int old = atomicAdd(p.done_counter, 1);
+        if (old == static_cast<int>(gridDim.x) - 1) {
+            *p.done_counter = 0;
+            __threadfence_system();
+            for (int r = 0; r < p.n_peers; ++r)
+                st_release_sys(reinterpret_cast<int*>(static_cast<char*>(p.peers[r]) + p.flag_off), p.flag_value);
+        }
+    }
+}
 
 template <int ITERS, int KS>  // ITERS * 2048 >= H; KS = K splits of gemm 2 (0: any, rolled loop)
 __global__ void __launch_bounds__(kCombineThreads) moe_combine_kernel(MoeCombineArgs p) {
@@ -692,6 +724,10 @@ __global__ void __launch_bounds__(kCombineThreads) moe_combine_kernel(MoeCombine
     const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     pdl_wait();
     pdl_launch_dependents();
+    float* peer_row = nullptr;
+    if (p.peers != nullptr)
+        peer_row = reinterpret_cast<float*>(static_cast<char*>(p.peers[t / p.rows_per_peer]) + p.out_off) +
+                   static_cast<size_t>(t % p.rows_per_peer) * p.ldo;
     int local[8];
     float w[8];
 #pragma unroll
@@ -702,6 +738,13 @@ __global__ void __launch_bounds__(kCombineThreads) moe_combine_kernel(MoeCombine
             local[s] = e >= 0 && e < p.local_count;
             w[s] = __ldcg(p.wts + t * p.ld_ids + s);
         }
+    }
+    bool any_local = false;
+#pragma unroll
+    for (int s = 0; s < 8; ++s) any_local = any_local || local[s];
+    if (p.peers != nullptr && !any_local) {  // nothing to send for this token
+        combine_signal(p, tid);
+        return;
     }
     float4 z[ITERS][8];
     float ss[8];
@@ -771,7 +814,9 @@ __global__ void __launch_bounds__(kCombineThreads) moe_combine_kernel(MoeCombine
             const float c = w[s] * rnorm[s];
             acc.x += z[it][s].x * c, acc.y += z[it][s].y * c, acc.z += z[it][s].z * c, acc.w += z[it][s].w * c;
         }
-        if (p.out_fp32) {
+        if (peer_row != nullptr) {
+            *reinterpret_cast<float4*>(peer_row + d) = acc;
+        } else if (p.out_fp32) {
             *reinterpret_cast<float4*>(static_cast<float*>(p.out) + static_cast<size_t>(t) * p.ldo + d) = acc;
         } else {
             *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(t) * p.ldo + d) =
@@ -781,6 +826,7 @@ __global__ void __launch_bounds__(kCombineThreads) moe_combine_kernel(MoeCombine
             *reinterpret_cast<uint2*>(p.out_copy + static_cast<size_t>(t) * p.ldc + d) =
                 make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
     }
+    if (p.peers != nullptr) combine_signal(p, tid);
 }
 
 template <typename Kern, typename Args>
@@ -860,8 +906,9 @@ extern "C" int msk_moe_scratch_bytes(int T, int top_k, int H, int I, int s1, int
 extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream) {
     using namespace msk;
     if (q == nullptr || !q->x || !q->w13_packed || !q->w2_packed || !q->w13_gs || !q->w2_gs || !q->post_norm_w ||
-        !q->y_part || !q->inter_sorted || !q->out || !q->topk_ids || !q->topk_weights)
+        !q->y_part || !q->inter_sorted || !q->topk_ids || !q->topk_weights)
         return MSK_ERR_INVALID;
+    if (!q->out && !(q->ep != nullptr && q->ep->peers != nullptr)) return MSK_ERR_INVALID;
     if (q->s1 > 1 && (!q->h1_part || !q->route_pub)) return MSK_ERR_INVALID;  // only the K-split gemm 1 leaves FP32 partials
     const int P = q->T * q->top_k;
     if (q->T < 1 || q->top_k < 1 || q->top_k > 8 || P > kMaxPairs || q->local_count < 1 || q->local_count > kMaxExperts ||
@@ -869,8 +916,12 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
         return MSK_ERR_UNSUPPORTED;
     if (q->H % 128 != 0 || q->I % 128 != 0 || q->ldx % 8 != 0 || q->H > 16 * kCombineThreads) return MSK_ERR_UNSUPPORTED;
     if (q->logits != nullptr && (q->n_logits > 256 || q->n_logits < q->top_k)) return MSK_ERR_UNSUPPORTED;
+    const MskEpHooks* ep = q->ep;
+    if (ep != nullptr && ep->peers != nullptr && (ep->n_peers < 1 || ep->rows_per_peer < 1 || ep->done_counter == nullptr || !q->out_fp32))
+        return MSK_ERR_INVALID;
     const int direct = q->T <= kGroup;
-    const int stage = !(direct && q->x_fp16);  // the GEMM reads x itself only when it is FP16 and needs no gathering
+    // the GEMM reads x itself only when it is FP16 and needs no gathering (and no wait for other GPUs' rows)
+    const int stage = !(direct && q->x_fp16) || (ep != nullptr && ep->wait_flags != nullptr);
     if (stage && q->x_sorted == nullptr) return MSK_ERR_INVALID;
     const int s1 = q->s1 > 0 ? q->s1 : 1, s2 = q->s2 > 0 ? q->s2 : 1;
     if ((q->H / 128) % s1 != 0 || (q->I / 128) % s2 != 0) return MSK_ERR_INVALID;
@@ -907,6 +958,10 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
         MoeStageArgs g{};
         g.route = ra, g.x = q->x, g.ldx = q->ldx, g.H = q->H, g.x_fp16 = q->x_fp16, g.direct = direct;
         g.x16 = static_cast<__half*>(q->x_sorted), g.status = status;
+        if (ep != nullptr && ep->wait_flags != nullptr) {
+            g.wait_flags = ep->wait_flags, g.wait_count = ep->wait_count, g.wait_value = ep->wait_value;
+            g.wait_cycles = ep->wait_cycles > 0 ? ep->wait_cycles : kWaitBudgetCycles;
+        }
         const int rows = direct ? q->T : P;
         rc = launch_pdl(moe_stage_kernel, dim3(rows < sms ? rows : sms), dim3(kRouteThreads), 0, s, pdl, g);
         if (rc != 0) return rc;
@@ -919,7 +974,8 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
     a.x_ssq_ts = q->x_ssq_tstride > 0 ? q->x_ssq_tstride : 1;
     a.route_pub = q->route_pub, a.outp = q->h1_part, a.S = s1, a.status = status;
     a.inter = static_cast<__half*>(q->inter_sorted), a.inner = q->I, a.fuse_act = s1 == 1;
-    a.route_early = stage && q->logits == nullptr;  // the staging kernel precedes
+    // the staging kernel precedes: the ids are final, unless they arrive from other GPUs during that kernel
+    a.route_early = stage && q->logits == nullptr && !(ep != nullptr && ep->wait_flags != nullptr);
     a.share_chunks = q->T <= 4;
     rc = launch_pdl2(moe_gemm_kernel<1>, dim3(sms), dim3(kMoeThreads), smem, s, pdl, tm_b1, a);
     if (rc != 0) return rc;
@@ -951,6 +1007,10 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
     c.post_w = static_cast<const __nv_bfloat16*>(q->post_norm_w), c.eps = q->post_eps, c.resid = q->resid, c.ldr = q->ldr;
     c.out = q->out, c.out_fp32 = q->out_fp32, c.ldo = q->ldo;
     c.out_copy = static_cast<__nv_bfloat16*>(q->out_copy), c.ldc = q->ldc;
+    if (ep != nullptr && ep->peers != nullptr) {
+        c.peers = ep->peers, c.n_peers = ep->n_peers, c.rows_per_peer = ep->rows_per_peer, c.out_off = ep->out_off;
+        c.flag_off = ep->flag_off, c.flag_value = ep->flag_value, c.done_counter = ep->done_counter;
+    }
     if (q->H <= 2 * kCombineThreads * 4 && s2 == 1) return launch_pdl(moe_combine_kernel<2, 1>, dim3(q->T), dim3(kCombineThreads), 0, s, 1, c);
     if (q->H <= 2 * kCombineThreads * 4 && s2 == 2) return launch_pdl(moe_combine_kernel<2, 2>, dim3(q->T), dim3(kCombineThreads), 0, s, 1, c);
     if (q->H <= 2 * kCombineThreads * 4) return launch_pdl(moe_combine_kernel<2, 0>, dim3(q->T), dim3(kCombineThreads), 0, s, 1, c);

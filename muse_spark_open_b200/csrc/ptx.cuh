@@ -300,6 +300,30 @@ __device__ __forceinline__ void pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// ---------------------------------------------------------------- flags between GPUs (peer memory over NVLink)
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// Bounded wait until *flag >= value (a flag another GPU sets in this GPU's memory).  On expiry records
+// MSK_ERR_TIMEOUT and returns false; the caller carries on to its exit, so the context stays usable.
+__device__ __forceinline__ bool flag_wait_ge(const int* flag, int value, long long budget_cycles, int* status, int where) {
+    if (ld_acquire_sys(flag) >= value) return true;
+    const long long t0 = clock64();
+    for (;;) {
+        __nanosleep(100);
+        if (ld_acquire_sys(flag) >= value) return true;
+        if (clock64() - t0 > budget_cycles) {
+            report(status, MSK_ERR_TIMEOUT, where, value, ld_acquire_sys(flag));
+            return false;
+        }
+    }
+}
+
 // ---------------------------------------------------------------- small helpers
 __device__ __forceinline__ float bf16lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }

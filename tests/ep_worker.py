@@ -32,14 +32,19 @@ def main():
     for k in ("seq_lens", "page_table", "stream", "cache_loc", "positions"):
         mine[k] = full[k][r0:r0 + rc].contiguous()
     mine["config"] = dict(full["config"], batch=rc, tokens=rc)
-    ops = ep.CudaOps(mine_w, rank, world, NEXP)
-    for _ in range(2):
-        hidden, stream, ids = ep.step(mine, ops)
-    torch.cuda.synchronize()
-    abi.status_for(dev).raise_if_set("ep")
-    ok = torch.equal(ids, ref_ids[r0:r0 + rc])
-    ok = ok and torch.allclose(stream, ref_stream[r0:r0 + rc], rtol=1e-4, atol=1e-4)
-    ok = ok and torch.allclose(hidden.float(), ref_hidden[r0:r0 + rc].float(), rtol=2e-2, atol=1e-2)
+    ok = True
+    for exchange in ("peer", "nccl"):  # device-initiated stores into peers' memory, then the collective-library form
+        ops = ep.CudaOps(mine_w, rank, world, NEXP, exchange=exchange)
+        for _ in range(3):  # both buffer parities, and a buffer's reuse
+            hidden, stream, ids = ep.step(mine, ops)
+        torch.cuda.synchronize()
+        abi.status_for(dev).raise_if_set("ep " + exchange)
+        ok = ok and torch.equal(ids, ref_ids[r0:r0 + rc])
+        ok = ok and torch.allclose(stream, ref_stream[r0:r0 + rc], rtol=1e-4, atol=1e-4)
+        ok = ok and torch.allclose(hidden.float(), ref_hidden[r0:r0 + rc].float(), rtol=2e-2, atol=1e-2)
+        if ops.peer is not None:
+            dist.barrier()
+            ops.peer.close()
     flag = torch.tensor([int(ok)], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:

@@ -101,3 +101,21 @@ def test_shard_and_row_layout():
     raw = rows.view(torch.float32).view(3, -1)
     assert (rows.view(torch.int32).view(3, -1)[:, 32:40] == 7).all() and (raw[:, 40:48] == 2.0).all()
     assert (raw[:, 48] == 3.0).all() and (raw[:, 49:] == 0).all()
+
+
+def test_peer_exchange_index_math():
+    """Who sends a token a partial row, and where a rank writes inside a peer's region (the index math of the
+    device-initiated exchange, restated in ep.py for the tests)."""
+    from muse_spark_open_b200 import ep
+    ids = torch.tensor([[0, 1, 2, 3, 4, 5, 6, 7], [0, 16, 32, 48, 64, 80, 96, 112], [127, 126, 125, 124, 123, 122, 121, 120]])
+    own = ep.owner_ranks(ids, 128, 8)
+    assert own[0].tolist() == [True] + [False] * 7 and own[1].all() and own[2].tolist() == [False] * 7 + [True]
+    own2 = ep.owner_ranks(ids, 128, 2)
+    assert own2.tolist() == [[True, False], [True, True], [False, True]]
+    seen = set()
+    for r in range(4):
+        sl = ep.region_slots(4, r, 8)
+        rows = range(sl["dispatch_first_row"], sl["dispatch_first_row"] + 8)
+        assert not seen & set(rows) and max(rows) < sl["rows"]
+        seen |= set(rows)
+    assert seen == set(range(32))  # the ranks' rows tile a region's row buffer exactly
