@@ -1,5 +1,6 @@
-// Expert choice of one token by one warp: softmax -> top-k -> renormalise (the routing rule of the
-// reference's MoE layer: models/moe.py).  Shared by the router kernel and the experts' GEMM.
+// Expert choice of one token by one warp: softmax -> top-k -> renormalise over the chosen (the benchmark's
+// routing rule; the renormalisation is the one of muse_moe_w4a16/reference.py:82).  Shared by the router kernel
+// and the experts' GEMM.
 #pragma once
 #include <cstdint>
 

@@ -118,11 +118,31 @@ def front(data: dict, state: dict, **tune) -> dict:
     return buf
 
 
+MAX_TOKENS = 256
+
+
 def kernel_fn(data: dict, state: dict, **tune):
     stream = data["stream"]
     if stream.dtype != torch.float32 or not stream.is_cuda:
         raise abi.MskError("stream must be a float32 CUDA tensor")
     t, h = stream.shape
+    if t > MAX_TOKENS:
+        # the chain is built for decode / verify steps of up to MAX_TOKENS tokens; larger batches run as consecutive
+        # groups of requests over the same cache (each group streams the weights again)
+        cfg = data["config"]
+        l = cfg["q_len"]
+        per = max(1, MAX_TOKENS // l)
+        outs = []
+        for b0 in range(0, cfg["batch"], per):
+            b1 = min(cfg["batch"], b0 + per)
+            sub = dict(data, config=dict(cfg, batch=b1 - b0, tokens=(b1 - b0) * l))
+            for k in ("seq_lens", "page_table"):
+                sub[k] = data[k][b0:b1]
+            for k in ("stream", "cache_loc", "positions"):
+                if k in data:
+                    sub[k] = data[k][b0 * l:b1 * l]
+            outs.append(kernel_fn(sub, state, **tune))
+        return tuple(torch.cat([o[i] for o in outs]) for i in range(3))
     buf = buffers(state, t, stream.device)
     ms = state["moe"]
     s1, s2 = tune.get("moe_splits") or moe.splits_for(t, ms["H"], ms["I"], state["local_count"], TOP_K)

@@ -77,10 +77,21 @@ def forward(x, ids, wts, state, local_start, local_count, out=None, logits=None,
             splits=None, pdl=False):
     t, h = x.shape
     top_k = ids.shape[1]
-    if t > MAX_TOKENS:
-        raise abi.MskError(f"experts built for decode/verify steps of up to {MAX_TOKENS} tokens, got {t}")
     if out is None:
         out = torch.empty((t, h), dtype=torch.bfloat16, device=x.device)
+    if t > MAX_TOKENS:
+        # the kernels are built for decode / verify steps; more tokens (the reference's 257-token case,
+        # muse_moe_w4a16/bench.py:15) run as consecutive blocks of MAX_TOKENS, each streaming its experts again
+        for r0 in range(0, t, MAX_TOKENS):
+            r1 = min(t, r0 + MAX_TOKENS)
+            pn = None
+            if pre_norm is not None:
+                ssq = pre_norm[0]
+                pn = ((ssq[:, r0:r1].contiguous() if ssq.dim() == 2 else ssq[r0:r1]), pre_norm[1], pre_norm[2])
+            forward(x[r0:r1], ids[r0:r1], wts[r0:r1], state, local_start, local_count, out=out[r0:r1],
+                    logits=None if logits is None else logits[r0:r1], pre_norm=pn,
+                    resid=None if resid is None else resid[r0:r1], splits=splits, pdl=pdl)
+        return out
     # the argument block depends only on addresses, strides and scalars: rebuilt when one changes, not per call
     if x.dtype not in (torch.bfloat16, torch.float16):
         raise abi.MskError("the expert input must be bfloat16 or float16")

@@ -84,7 +84,23 @@ def kernel_fn(data: dict, state: dict) -> torch.Tensor:
     x, cfg = data["x"], data["config"]
     m, n, layer = cfg["m"], cfg["n"], cfg["layer"]
     if m > MAX_M:
-        raise abi.MskError(f"projection built for decode/verify steps of up to {MAX_M} tokens, got {m}")
+        # the kernel is built for decode / verify steps; larger token counts (the reference's m = 512 and 1000 cases,
+        # muse_bf16_proj/bench.py:14-16) run as consecutive blocks of MAX_M rows, each streaming the weights again
+        if data.get("ssq") is not None:
+            raise abi.MskError(f"the sum-of-squares hook is built for up to {MAX_M} tokens, got {m}")
+        fp32 = layer in state["fp32"]
+        out = data.get("out")
+        if out is None:
+            out = torch.empty((m, n), dtype=torch.float32 if fp32 else torch.bfloat16, device=x.device)
+        for r0 in range(0, m, MAX_M):
+            r1 = min(m, r0 + MAX_M)
+            sub = {"x": x[r0:r1], "config": dict(cfg, m=r1 - r0)}
+            if fp32:
+                out[r0:r1].copy_(kernel_fn(sub, state))
+            else:
+                sub["out"] = out[r0:r1]
+                kernel_fn(sub, state)
+        return out
     w = state["w"][layer][:n]
     if layer in state["fp32"]:
         # x against [hi | lo]: the doubled activation row lives in a persistent buffer (two strided copies, no

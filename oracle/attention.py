@@ -66,10 +66,12 @@ def new_slots(data) -> torch.Tensor:
     return cache_rows(data, pos)
 
 
-def ref_kernel(data, new_kv=None):
+def ref_kernel(data, new_kv=None, scale_after_rope: bool = False):
     """(out fp32 [B,L,Hq*d], k_new e4m3 [B,L,Hkv,d], v_new e4m3 [B,L,Hkv,d]).  reference.py:294-337.
 
     With new_kv the block attends those FP8 entries as its own (reference.py:316-317).
+    scale_after_rope: multiply the queries by qk_scale_factor after RoPE instead of before it, the order of the
+    layer's reference (muse_decode_layer/reference.py:364-372); the same value up to FP32 rounding.
     """
     cfg = data["config"]
     b_n, l_n = cfg["batch"], cfg["q_len"]
@@ -77,10 +79,12 @@ def ref_kernel(data, new_kv=None):
     grp = hq // hkv
     q_in, k_in, v_in, gate = split_qkv(data)
     pos = data["seq_lens"].long()[:, None] + torch.arange(l_n)
-    q = rms(q_in) * cfg["qk_scale_factor"]
+    q = rms(q_in) if scale_after_rope else rms(q_in) * cfg["qk_scale_factor"]
     k = rms(k_in)
     if cfg["rope_theta"]:
         q, k = rope(q, pos, cfg["rope_theta"]), rope(k, pos, cfg["rope_theta"])
+    if scale_after_rope:
+        q = q * cfg["qk_scale_factor"]
     q = q.to(torch.bfloat16).float()  # queries rounded to BF16 (reference.py:308-310)
     k_new = quant_e4m3(k, data["k_scale"])
     v_new = quant_e4m3(v_in, data["v_scale"])

@@ -106,6 +106,84 @@ def ref_kernel(data, weights, topk_ids=None):
     return stream2.to(torch.bfloat16), stream2, ids, fr["k_new"], fr["v_new"]
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# The reference's own form of the layer (muse_decode_layer/reference.py:339-477): the attention input arrives
+# normalised, both residual boundaries are norm-preserving gated mixes, the router scores are sigmoids chosen by
+# score + bias, and the experts sit between a pooler and an unpooler projection.  Shapes come from the weights and
+# the config instead of module constants.
+RESIDUAL_TEMPERATURE = 0.3   # reference.py:52
+RESIDUAL_GATE_EPS = 1e-3     # reference.py:53
+ROUTER_MULTIPLIER = 0.1767766952966369  # reference.py:49
+ROUTE_EPS = 1e-15            # reference.py:51
+SLICED_MAX_TOKENS = 8        # reference.py:56
+BRANCH_EPS = 1e-8            # the boundary's RMSNorm of the branch (POST_NORM_EPS, reference.py:40)
+
+
+def residual_coefficients(gate: torch.Tensor):
+    """(alpha, beta) of new = alpha * stream + beta * branch (reference.py:339-344)."""
+    w = gate.float() / RESIDUAL_TEMPERATURE
+    beta = torch.sigmoid(w)
+    alpha = torch.sqrt(torch.clamp(torch.sigmoid(-w) * (1.0 + beta), min=RESIDUAL_GATE_EPS))
+    return alpha, beta
+
+
+def route_sigmoid(h: torch.Tensor, weights):
+    """(unbiased sigmoid scores, biased scores that choose the experts), FP32 [T, E]; logits in FP64
+    (reference.py:419-424)."""
+    logits = h.double() @ weights["router"].double().T
+    scores = torch.sigmoid(logits * ROUTER_MULTIPLIER).float()
+    return scores, scores + weights["router_bias"].float()
+
+
+def native_front(data, weights):
+    """Everything up to the router in the reference's form (reference.py:447-457)."""
+    cfg = data["config"]
+    a_in = dict(data)
+    qkv = data["attn_input"].float() @ weights["qkv_gate"].float().T   # stays FP32 (reference.py:360)
+    a_in["qkv"] = qkv.view(cfg["batch"], cfg["q_len"], -1)
+    o, k_new, v_new = attn.ref_kernel(a_in, scale_after_rope=True)
+    a = o.reshape(cfg["tokens"], -1) @ weights["o"].float().T
+    alpha1, beta1 = residual_coefficients(weights["attn_residual_gate"])
+    stream1 = alpha1 * data["stream"].float() + beta1 * attn.rms(a, BRANCH_EPS)
+    h = attn.rms(stream1, RMS_EPS) * (1.0 + weights["pre_ffn_norm"].float())
+    scores, biased = route_sigmoid(h, weights)
+    return {"stream1": stream1, "h": h, "scores": scores, "biased": biased, "k_new": k_new, "v_new": v_new,
+            "local_start": int(data["local_start"])}
+
+
+def native_back(fr, weights, ids: torch.Tensor):
+    """Pooler, local experts, (sliced) unpooler and the second boundary (reference.py:460-477)."""
+    n_exp = weights["router"].shape[0]
+    picked = fr["scores"].gather(1, ids.long())
+    tw = picked / (picked.sum(-1, keepdim=True) + ROUTE_EPS)
+    p = attn.rms(fr["h"] @ weights["pooler"].float().T, RMS_EPS) * (1.0 + weights["pre_expert_norm"].float())
+    local = (ids.long() - fr["local_start"]) % n_exp
+    md = {"hidden_states": p, "topk_ids": local.to(torch.int32), "topk_weights": tw,
+          "config": {"local_start": 0, "local_count": weights["w13"].shape[0]}}
+    mw = dict(weights, post_norm_w=weights["post_expert_norm"])
+    y = moe.ref_kernel(md, mw, fp32_out=True)
+    hidden_dim = fr["stream1"].shape[1]
+    if y.shape[0] <= SLICED_MAX_TOKENS:   # few tokens: this GPU computes only its eighth of the unpooler's columns
+        f = torch.zeros_like(fr["stream1"])
+        sl = hidden_dim // 8
+        f[:, :sl] = y @ weights["unpooler"][:sl].float().T
+    else:
+        f = y @ weights["unpooler"].float().T
+    f = f * (1.0 + weights["post_ffn_norm"].float())
+    alpha2, beta2 = residual_coefficients(weights["ffn_residual_gate"])
+    stream2 = alpha2 * fr["stream1"] + beta2 * attn.rms(f, BRANCH_EPS)
+    hidden = attn.rms(stream2, RMS_EPS) * (1.0 + weights["next_pre_attn_norm"].float())
+    return hidden.to(torch.bfloat16), stream2
+
+
+def native_ref_kernel(data, weights, topk_ids=None, top_k: int = 8):
+    """(hidden bf16, stream fp32, ids int32, k_new, v_new) in the reference's form (reference.py:559-566)."""
+    fr = native_front(data, weights)
+    ids = fr["biased"].topk(top_k, dim=-1).indices.to(torch.int32) if topk_ids is None else topk_ids
+    hidden, stream = native_back(fr, weights, ids)
+    return hidden, stream, ids, fr["k_new"], fr["v_new"]
+
+
 def algorithmic_bytes(data, weights, ids: torch.Tensor) -> int:
     """Dense weights + router + visible KV + touched experts + 12 B per token-channel of activations."""
     cfg = data["config"]

@@ -107,6 +107,30 @@ def proj_cases(ref):
     return cases
 
 
+def layer_cases(ref):
+    """The reference's own layer functions (ref_front / ref_back behind ref_kernel) at small shapes, head_dim 128."""
+    ref.HIDDEN, ref.HEAD_DIM, ref.HQ, ref.HKV = 512, 128, 4, 1
+    ref.Q_SIZE, ref.KV_SIZE = ref.HQ * ref.HEAD_DIM, ref.HKV * ref.HEAD_DIM
+    ref.QKV_SIZE = 2 * ref.Q_SIZE + 2 * ref.KV_SIZE
+    ref.SM_SCALE = ref.HEAD_DIM ** -0.5
+    ref.SLIDING_WINDOW, ref.ROPE_THETA = 48, 1e6
+    ref.D_EXPERT, ref.N_EXPERTS, ref.LOCAL_EXPERTS = 256, 16, 8
+    ref.UNPOOL_SLICE = ref.HIDDEN // 8
+    ref._stream_basis.cache_clear()
+    weights = ref.generate_weights(41, device="cpu")
+    cases = [("weights", pack(weights))]
+    for name, kw in (("full_decode", dict(batch=3, ctx=70, layer="full", seed=42, q_len=1, page=16, local_start=8)),
+                     ("sliding_verify", dict(batch=2, ctx=90, layer="sliding", seed=43, q_len=8, page=16, spread="agentic"))):
+        data = ref.generate_input(device="cpu", **kw)
+        front = ref.ref_front(data, weights)
+        hidden, stream, ids, k_new, v_new = ref.ref_kernel(data, weights)
+        item = pack(data)
+        item.update(expect_hidden=hidden, expect_stream=stream, expect_ids=ids, expect_stream1=front["stream1"],
+                    expect_scores=front["scores"], expect_k_new=as_bytes(k_new), expect_v_new=as_bytes(v_new))
+        cases.append((name, item))
+    return cases
+
+
 def main():
     if len(sys.argv) < 2:
         raise SystemExit("usage: make_golden.py <checkout of Kushagrabainsla/muse-spark-open>")
@@ -118,6 +142,8 @@ def main():
     out["moe"] = dict(moe_cases(m, nv))
     p, _ = load(ref_root, "muse_bf16_proj")
     out["proj"] = dict(proj_cases(p))
+    lay, _ = load(ref_root, "muse_decode_layer")
+    out["layer"] = dict(layer_cases(lay))
     for name, blob in out.items():
         path = os.path.join(HERE, f"{name}.pt")
         torch.save(blob, path)

@@ -132,3 +132,21 @@ def test_layer_256_requests(bench_weights):
     b = layer.kernel_fn(dd, state)
     torch.cuda.synchronize()
     assert torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])
+
+
+def test_layer_more_than_256_tokens():
+    """40 requests x 8-token verify blocks = 320 tokens: the layer runs as groups of requests over the same cache."""
+    from muse_spark_open_b200 import abi, layer
+    weights = olayer.make_weights(3, hidden=1024, hq=8, hkv=1, d=128, n_experts=16, inner=128)
+    seqs = [40 + 13 * i for i in range(40)]
+    data = olayer.make_input(40, seqs, 11, q_len=8, hidden=1024, hq=8, hkv=1, d=128, window=0, rope_theta=0.0)
+    state = layer.prepare(_dev(weights))
+    dd = _dev(data)
+    hidden, stream, ids = layer.kernel_fn(dd, state)
+    torch.cuda.synchronize()
+    abi.status_for("cuda").raise_if_set("layer 320 tokens")
+    assert stream.shape == (320, 1024) and ids.shape == (320, 8)
+    fr = olayer.front(data, weights)
+    ref_stream, _ = olayer.back(fr, weights, ids.cpu())
+    upd, ref = stream.cpu() - data["stream"], ref_stream - data["stream"]
+    assert float((upd - ref).norm() / ref.norm()) < 3e-2

@@ -114,3 +114,11 @@ def test_moe_benchmark_shape():
     from muse_spark_open_b200 import moe
     again = moe.kernel_fn(dd, state).cpu()
     assert torch.equal(out, again)  # bitwise reproducible
+
+
+def test_moe_more_than_256_tokens():
+    """257 tokens (a case of the reference's list, muse_moe_w4a16/bench.py:15): blocks of 256 tokens."""
+    weights = omoe.make_weights(7, n_experts=8, hidden=256, inner=128, std=0.05)
+    data = omoe.make_input(257, 8, n_experts=8, hidden=256)
+    out, _, _ = _run(data, weights)
+    torch.testing.assert_close(out.float(), omoe.ref_kernel(data, weights).float(), rtol=2e-2, atol=1e-2)

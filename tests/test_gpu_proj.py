@@ -70,3 +70,16 @@ def test_proj_fused_epilogue(m, splits, token_splits):
     _check(out, want, rtol=1e-3, atol=1e-3)
     _check(normed, want * (1 + nxt.float()))
     torch.testing.assert_close(oss.sum(0).cpu(), want.pow(2).sum(-1), rtol=1e-3, atol=1e-3)
+
+
+def test_proj_more_than_256_tokens():
+    """Token counts beyond a decode / verify step (the reference's m = 512 and 1000 cases) run as blocks of 256 rows."""
+    from muse_spark_open_b200 import abi, proj
+    for m in (512, 1000):
+        x, w = oproj.make_input(m, 384, 256, seed=m)
+        state = proj.prepare({"w": w.cuda()})
+        out = proj.kernel_fn({"x": x.cuda(), "config": {"m": m, "n": 384, "k": 256, "layer": "w"}}, state)
+        torch.cuda.synchronize()
+        abi.status_for("cuda").raise_if_set("proj blocks")
+        assert tuple(out.shape) == (m, 384)
+        _check(out, oproj.ref_kernel(x, w), rtol=1e-2, atol=1e-2)

@@ -82,3 +82,26 @@ def test_proj_matches_reference(golden):
 def test_quant_e4m3_saturates():
     x = torch.tensor([448.0, 460.0, 1000.0, -5000.0])
     assert attention.quant_e4m3(x, 1.0).float().tolist() == [448.0, 448.0, 448.0, -448.0]
+
+
+def test_native_layer_matches_reference(golden):
+    """The layer in the reference's own form (norm-preserving gated residuals, sigmoid + bias routing, pooler /
+    sliced unpooler) against the reference's ref_front / ref_back outputs (tests/golden/layer.pt)."""
+    from oracle import layer
+    blob = golden("layer")
+    weights = dict(blob["weights"])
+    for k in ("w13_sf", "w2_sf"):
+        weights[k] = weights[k].view(FP8)
+    for name in ("full_decode", "sliding_verify"):
+        item = blob[name]
+        data = {k: v for k, v in item.items() if not k.startswith("expect_")}
+        for k in ("k_cache", "v_cache"):
+            data[k] = data[k].view(FP8)
+        fr = layer.native_front(data, weights)
+        torch.testing.assert_close(fr["stream1"], item["expect_stream1"], rtol=1e-5, atol=1e-5, msg=name)
+        torch.testing.assert_close(fr["scores"], item["expect_scores"], rtol=1e-5, atol=1e-6, msg=name)
+        assert (fr["k_new"].view(torch.uint8) != item["expect_k_new"]).float().mean() < 2e-3, name
+        hidden, stream, ids, _, _ = layer.native_ref_kernel(data, weights)
+        assert torch.equal(ids.long().sort(-1).values, item["expect_ids"].long().sort(-1).values), name
+        torch.testing.assert_close(stream, item["expect_stream"], rtol=1e-4, atol=1e-4, msg=name)
+        assert (hidden != item["expect_hidden"]).float().mean() < 0.01, name
