@@ -113,6 +113,7 @@ typedef struct {
     int stages;               /* K/V tile ring depth (3 or 4); 0 = pick */
     int issuers;              /* decode: MMA-issuing warps, 2 (128 tensor-memory columns, more CTAs per SM) or 4; 0 = pick */
     int pdl;
+    int row_groups;           /* decode: sets of four warps that split the 8 query rows of a KV head, 1 or 2; 0 = pick */
 } MskAttnParams;
 
 int msk_attn_decode(const MskAttnParams* p, int* status, void* stream);
@@ -271,6 +272,7 @@ typedef struct {
     int32_t* topk_ids;             /* int32 [T, top_k]: softmax -> top-k -> renormalise of the logits, written by */
     float* topk_weights;           /* fp32 [T, top_k]    the router kernel's last block per 32 tokens */
     int attn_chunks, attn_stages, attn_issuers, qkv_splits, o_splits;
+    int attn_row_groups;
     int pdl;                       /* also chain the first kernel to whatever precedes it */
 } MskLayerFront;
 

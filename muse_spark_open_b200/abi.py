@@ -140,7 +140,7 @@ class AttnParams(C.Structure):
         ("B", C.c_int), ("L", C.c_int), ("Hq", C.c_int), ("Hkv", C.c_int), ("d", C.c_int), ("page_size", C.c_int),
         ("num_pages", C.c_int), ("window", C.c_int),
         ("qk_scale_factor", C.c_float), ("sm_scale", C.c_float),
-        ("chunks", C.c_int), ("stages", C.c_int), ("issuers", C.c_int), ("pdl", C.c_int),
+        ("chunks", C.c_int), ("stages", C.c_int), ("issuers", C.c_int), ("pdl", C.c_int), ("row_groups", C.c_int),
     ]
 
 
@@ -182,7 +182,7 @@ class LayerFront(C.Structure):
         ("qkv_scratch", C.c_void_p), ("o_scratch", C.c_void_p), ("qkv_scratch_bytes", C.c_size_t), ("o_scratch_bytes", C.c_size_t),
         ("logits", C.c_void_p), ("top_k", C.c_int), ("topk_ids", C.c_void_p), ("topk_weights", C.c_void_p),
         ("attn_chunks", C.c_int), ("attn_stages", C.c_int), ("attn_issuers", C.c_int), ("qkv_splits", C.c_int),
-        ("o_splits", C.c_int),
+        ("o_splits", C.c_int), ("attn_row_groups", C.c_int),
         ("pdl", C.c_int),
     ]
 

@@ -28,7 +28,7 @@ def inv_freq(theta: float, d: int, device) -> torch.Tensor | None:
 
 
 def launch(qkv2d: torch.Tensor, out2d: torch.Tensor, data: dict, cfg: dict, chunks: int = 0, stages: int = 0, issuers: int = 0,
-           pdl: bool = False) -> None:
+           pdl: bool = False, row_groups: int = 0) -> None:
     """qkv2d bf16 [B*L, >= (2Hq+2Hkv)*d] (row stride free), out2d bf16 [B*L, Hq*d]."""
     p = abi.AttnParams()
     p.qkv, p.ld_qkv, p.out, p.ld_out = abi.ptr(qkv2d), qkv2d.stride(0), abi.ptr(out2d), out2d.stride(0)
@@ -43,7 +43,7 @@ def launch(qkv2d: torch.Tensor, out2d: torch.Tensor, data: dict, cfg: dict, chun
     p.B, p.L, p.Hq, p.Hkv, p.d = cfg["batch"], cfg["q_len"], cfg["num_q_heads"], cfg["num_kv_heads"], cfg["head_dim"]
     p.page_size, p.num_pages, p.window = cfg["page_size"], kc.shape[0], cfg["window"]
     p.qk_scale_factor, p.sm_scale = cfg["qk_scale_factor"], cfg["sm_scale"]
-    p.chunks, p.stages, p.issuers, p.pdl = chunks, stages, issuers, int(pdl)
+    p.chunks, p.stages, p.issuers, p.pdl, p.row_groups = chunks, stages, issuers, int(pdl), row_groups
     st = abi.status_for(qkv2d.device)
     abi.check(abi.lib().msk_attn_decode(C.byref(p), st.p, abi.stream_ptr()), "msk_attn_decode")
 

@@ -109,19 +109,23 @@ __device__ __forceinline__ void norm_rope_row(float (&x)[4], float post_scale, c
     }
 }
 
-template <int L>
-struct AttnShape {
-    static constexpr int RG = L == 1 ? 1 : 4;   // row groups (sets of four warps that split the query rows)
-    static constexpr int kThreads = 128 * RG;
-};
+// TMEM load of BR (4 or 8) consecutive 32-bit columns
+template <int BR>
+__device__ __forceinline__ void tmem_ld_rows(uint32_t taddr, uint32_t (&r)[BR]) {
+    if constexpr (BR == 8) tmem_ld8(taddr, r);
+    else tmem_ld4(taddr, r);
+}
 
-template <int L, int ISS>  // ISS: MMA-issuing warps (one thread issues only ~1 MMA per 100 clocks)
-__global__ void __launch_bounds__(AttnShape<L>::kThreads) attn_kernel(const __grid_constant__ CUtensorMap tm_k,
+// L: tokens per request (1 decode, 8 verify); ISS: MMA-issuing warps (one thread issues only ~1 MMA per 100
+// clocks); RG: row groups = sets of four warps (one per 32-key quarter of a tile) that split the 8 L query rows.
+template <int L, int ISS, int RG>
+__global__ void __launch_bounds__(128 * RG, (L == 1 && RG <= 2) ? 2 : 1) attn_kernel(const __grid_constant__ CUtensorMap tm_k,
                                                    const __grid_constant__ CUtensorMap tm_v, AttnArgs p) {
     constexpr int NR = 8 * L;                 // query rows per KV head
-    constexpr int RG = AttnShape<L>::RG, NTHR = AttnShape<L>::kThreads, NWARP = NTHR / 32;
+    constexpr int NTHR = 128 * RG, NWARP = NTHR / 32;
     constexpr int NRG = NR / RG;              // query rows per row group: a thread's serial work per tile
-    static_assert(NRG % 8 == 0, "row groups work on blocks of 8 rows");
+    constexpr int BR = NRG < 8 ? NRG : 8;     // rows per tensor-memory round trip
+    static_assert(NRG % BR == 0 && (BR == 4 || BR == 8), "row groups work on blocks of 4 or 8 rows");
     constexpr int NP = 2 * NR;                // UMMA N: rows [0, NR) hold the first split term, [NR, 2 NR) the second
     constexpr int SBUF = L == 1 ? 2 : 1;      // score buffers in TMEM (2: the next tile's scores are computed ahead)
     // SBUF * ISS * NP score columns, then ISS * NP output columns, as a power of two
@@ -292,22 +296,23 @@ __global__ void __launch_bounds__(AttnShape<L>::kThreads) attn_kernel(const __gr
     const uint32_t trow = tmem + (static_cast<uint32_t>(kq * 32) << 16);
     bool ok = true;
     // decode keeps the running maxima and the rescale factors replicated in every thread's registers
-    float m_r[L == 1 ? 8 : 1], alpha_r[L == 1 ? 8 : 1];
+    float m_r[L == 1 ? NRG : 1], alpha_r[L == 1 ? NRG : 1];  // of rows r_lo + g
 #pragma unroll
-    for (int g = 0; g < (L == 1 ? 8 : 1); ++g) m_r[g] = kNeg, alpha_r[g] = 1.0f;
+    for (int g = 0; g < (L == 1 ? NRG : 1); ++g) m_r[g] = kNeg, alpha_r[g] = 1.0f;
 
     // scores of 8 query rows (c0 .. c0+7) for this thread's key: both split terms, all issuing warps' partials
-    auto load_scores = [&](int i, int c0, float (&sc)[8]) {
-        uint32_t hi[ISS][8], lo[ISS][8];
+    // scores of BR query rows (c0 .. c0+BR-1) for this thread's key: both split terms, all issuing warps' partials
+    auto load_scores = [&](int i, int c0, float (&sc)[BR]) {
+        uint32_t hi[ISS][BR], lo[ISS][BR];
 #pragma unroll
         for (int w = 0; w < ISS; ++w) {
             const uint32_t col = trow + ((i % SBUF) * ISS + w) * NP + c0;
-            tmem_ld8(col, hi[w]);
-            tmem_ld8(col + NR, lo[w]);
+            tmem_ld_rows<BR>(col, hi[w]);
+            tmem_ld_rows<BR>(col + NR, lo[w]);
         }
         tmem_wait_ld();
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
+        for (int g = 0; g < BR; ++g) {
             float a = 0.0f, b = 0.0f;
 #pragma unroll
             for (int w = 0; w < ISS; ++w) a += __uint_as_float(hi[w][g]), b += __uint_as_float(lo[w][g]);
@@ -320,20 +325,20 @@ __global__ void __launch_bounds__(AttnShape<L>::kThreads) attn_kernel(const __gr
         ok = mbar_wait(bar_o, j & 1, p.status, where | 6) && ok;
         tc_fence_after();
 #pragma unroll
-        for (int c0 = 0; c0 < NRG; c0 += 8) {
-            uint32_t hi[ISS][8], lo[ISS][8];
+        for (int c0 = 0; c0 < NRG; c0 += BR) {
+            uint32_t hi[ISS][BR], lo[ISS][BR];
 #pragma unroll
             for (int w = 0; w < ISS; ++w) {
-                tmem_ld8(trow + kOCol + w * NP + r_lo + c0, hi[w]);
-                tmem_ld8(trow + kOCol + w * NP + NR + r_lo + c0, lo[w]);
+                tmem_ld_rows<BR>(trow + kOCol + w * NP + r_lo + c0, hi[w]);
+                tmem_ld_rows<BR>(trow + kOCol + w * NP + NR + r_lo + c0, lo[w]);
             }
             tmem_wait_ld();
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
+            for (int g = 0; g < BR; ++g) {
                 float a = 0.0f, b = 0.0f;
 #pragma unroll
                 for (int w = 0; w < ISS; ++w) a += __uint_as_float(hi[w][g]), b += __uint_as_float(lo[w][g]);
-                const float al = L == 1 ? alpha_r[g] : alpha_s[r_lo + c0 + g];
+                const float al = L == 1 ? alpha_r[c0 + g] : alpha_s[r_lo + c0 + g];
                 o_acc[c0 + g] = o_acc[c0 + g] * al + (a + b * (1.0f / kLoScale));
             }
         }
@@ -361,13 +366,13 @@ __global__ void __launch_bounds__(AttnShape<L>::kThreads) attn_kernel(const __gr
         float skeep[NRG];  // this key's scaled scores of the thread's rows
         // pass 1: tile maximum per query row
 #pragma unroll
-        for (int c0 = 0; c0 < NRG; c0 += 8) {
-            float sc[8];
+        for (int c0 = 0; c0 < NRG; c0 += BR) {
+            float sc[BR];
             load_scores(i, r_lo + c0, sc);
             const int j = (r_lo + c0) >> 3;
             const bool vis = pos < seq && (W == 0 || pos > seq + j - W);
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
+            for (int g = 0; g < BR; ++g) {
                 const float sv = vis ? sc[g] * s_scale : kNeg;
                 skeep[c0 + g] = sv;
                 const float mx = redux_max(sv);
@@ -378,18 +383,20 @@ __global__ void __launch_bounds__(AttnShape<L>::kThreads) attn_kernel(const __gr
         if constexpr (SBUF == 1) tc_fence_before();  // the scores are in registers: their buffer may be overwritten
         __syncthreads();
         if constexpr (L == 1) {
-            // every thread folds the four warps' maxima itself: no second barrier, no shared-memory round trip
-            const float4* w4 = reinterpret_cast<const float4*>(&wred[0][0]);
-            float tm[8];
+            // every thread folds the four warps' maxima of its rows itself: no second barrier, no shared-memory round trip
+            float tm[NRG];
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
-                const float4 a = w4[2 * w], b4 = w4[2 * w + 1];
-                const float v8[8] = {a.x, a.y, a.z, a.w, b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
-                for (int g = 0; g < 8; ++g) tm[g] = w == 0 ? v8[g] : fmaxf(tm[g], v8[g]);
+                for (int q4 = 0; q4 < NRG / 4; ++q4) {
+                    const float4 a = *reinterpret_cast<const float4*>(&wred[w][r_lo + 4 * q4]);
+                    const float v4[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) tm[4 * q4 + g] = w == 0 ? v4[g] : fmaxf(tm[4 * q4 + g], v4[g]);
+                }
             }
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
+            for (int g = 0; g < NRG; ++g) {
                 const float mn = fmaxf(tm[g], m_r[g]);
                 alpha_r[g] = ex2(m_r[g] - mn);
                 m_r[g] = mn;
@@ -418,14 +425,14 @@ __global__ void __launch_bounds__(AttnShape<L>::kThreads) attn_kernel(const __gr
         if constexpr (L != 1) __syncthreads();
         // pass 2: p = 2^(s - m) as two E4M3 terms (the second times 16), bytes of the B operand P[row][key]
 #pragma unroll
-        for (int c0 = 0; c0 < NRG; c0 += 8) {
+        for (int c0 = 0; c0 < NRG; c0 += BR) {
             const int j = (r_lo + c0) >> 3;
             const bool vis = pos < seq && (W == 0 || pos > seq + j - W);
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
+            for (int g = 0; g < BR; ++g) {
                 const int n = r_lo + c0 + g;
-                const float pr = vis ? ex2(skeep[c0 + g] - (L == 1 ? m_r[g] : m_s[n])) : 0.0f;
-                l_part[c0 + g] = l_part[c0 + g] * (L == 1 ? alpha_r[g] : alpha_s[n]) + pr;
+                const float pr = vis ? ex2(skeep[c0 + g] - (L == 1 ? m_r[c0 + g] : m_s[n])) : 0.0f;
+                l_part[c0 + g] = l_part[c0 + g] * (L == 1 ? alpha_r[c0 + g] : alpha_s[n]) + pr;
                 const float ps = pr * kPScale;
                 const uint32_t bh = f_to_e4m3(ps);
                 const uint32_t bl = f_to_e4m3((ps - e4m3_to_f(bh)) * kLoScale);
@@ -445,8 +452,8 @@ __global__ void __launch_bounds__(AttnShape<L>::kThreads) attn_kernel(const __gr
     if (nt > 0) finish_tile(nt - 1);
     if constexpr (L == 1) {
 #pragma unroll
-        for (int g = 0; g < 8; ++g)
-            if (tid == g) m_s[g] = m_r[g];
+        for (int g = 0; g < NRG; ++g)
+            if (ktid == g) m_s[r_lo + g] = m_r[g];
     }
     __syncthreads();
 
@@ -596,7 +603,7 @@ __global__ void __launch_bounds__(AttnShape<L>::kThreads) attn_kernel(const __gr
     if (warp == 0) tmem_dealloc(tmem, kCols);
 }
 
-template <int L, int ISS>
+template <int L, int ISS, int RG>
 int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
     constexpr int NR = 8 * L, NP = 2 * NR;
     constexpr int kColsHost = ((L == 1 ? 3 : 2) * ISS * NP <= 128) ? 128 : ((L == 1 ? 3 : 2) * ISS * NP <= 256) ? 256 : 512;
@@ -654,13 +661,13 @@ int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MSK_ERR_CUDA;
     static int configured[64] = {};  // per device, like the attribute itself
     if (smem > configured[dev]) {
-        if (cudaFuncSetAttribute(attn_kernel<L, ISS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(attn_kernel<L, ISS, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return MSK_ERR_CUDA;
         configured[dev] = smem;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(C, q->Hkv, q->B);
-    cfg.blockDim = dim3(AttnShape<L>::kThreads, 1, 1);
+    cfg.blockDim = dim3(128 * RG, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attrs[2];
@@ -677,7 +684,7 @@ int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
     }
     cfg.attrs = attrs;
     cfg.numAttrs = na;
-    return cudaLaunchKernelEx(&cfg, attn_kernel<L, ISS>, tm_k, tm_v, a) == cudaSuccess ? 0 : MSK_ERR_CUDA;
+    return cudaLaunchKernelEx(&cfg, attn_kernel<L, ISS, RG>, tm_k, tm_v, a) == cudaSuccess ? 0 : MSK_ERR_CUDA;
 }
 
 }  // namespace msk
@@ -691,8 +698,11 @@ extern "C" int msk_attn_decode(const MskAttnParams* q, int* status, void* stream
     if (q->page_size < 8 || q->page_size > 128 || (q->page_size & (q->page_size - 1)) != 0) return MSK_ERR_UNSUPPORTED;
     if (q->issuers != 0 && q->issuers != 2 && q->issuers != 4) return MSK_ERR_INVALID;
     // decode: two issuing warps (128 tensor-memory columns) measured a little faster than four
-    if (q->L == 1 && q->issuers == 4) return launch_attn<1, 4>(q, status, static_cast<cudaStream_t>(stream));
-    if (q->L == 1) return launch_attn<1, 2>(q, status, static_cast<cudaStream_t>(stream));
-    if (q->L == 8) return launch_attn<8, 2>(q, status, static_cast<cudaStream_t>(stream));
+    if (q->row_groups != 0 && q->row_groups != 1 && q->row_groups != 2) return MSK_ERR_INVALID;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (q->L == 1 && q->issuers == 4) return launch_attn<1, 4, 1>(q, status, s);
+    if (q->L == 1 && q->row_groups == 1) return launch_attn<1, 2, 1>(q, status, s);
+    if (q->L == 1) return launch_attn<1, 2, 2>(q, status, s);
+    if (q->L == 8) return launch_attn<8, 2, 4>(q, status, s);
     return MSK_ERR_UNSUPPORTED;
 }

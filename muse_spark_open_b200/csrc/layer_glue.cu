@@ -259,7 +259,7 @@ extern "C" int msk_layer_front(const MskLayerFront* f, int* status, void* stream
     a.inv_freq = f->inv_freq, a.B = f->B, a.L = f->L, a.Hq = f->Hq, a.Hkv = f->Hkv, a.d = f->d;
     a.page_size = f->page_size, a.num_pages = f->num_pages, a.window = f->window;
     a.qk_scale_factor = f->qk_scale_factor, a.sm_scale = f->sm_scale;
-    a.chunks = f->attn_chunks, a.stages = f->attn_stages, a.issuers = f->attn_issuers, a.pdl = 1;
+    a.chunks = f->attn_chunks, a.stages = f->attn_stages, a.issuers = f->attn_issuers, a.row_groups = f->attn_row_groups, a.pdl = 1;
     rc = msk_attn_decode(&a, status, stream);
     if (rc != 0) return rc;
 

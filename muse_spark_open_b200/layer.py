@@ -93,7 +93,7 @@ def fill_front(f: abi.LayerFront, data: dict, state: dict, buf: dict, tune: dict
     f.qkv_scratch_bytes, f.o_scratch_bytes = qs.numel(), os_.numel()
     f.top_k = TOP_K
     f.attn_chunks, f.attn_stages = tune.get("attn_chunks", 0), tune.get("attn_stages", 0)
-    f.attn_issuers = tune.get("attn_issuers", 0)
+    f.attn_issuers, f.attn_row_groups = tune.get("attn_issuers", 0), tune.get("attn_row_groups", 0)
     f.qkv_splits, f.o_splits, f.pdl = tune.get("qkv_splits", 0), tune.get("o_splits", 0), 0
 
 

@@ -62,7 +62,8 @@ def run_attn(a):
     g = torch.Generator(device=DEV).manual_seed(2)
     qkv = torch.randn((t, 9216), generator=g, device=DEV).to(torch.bfloat16)
     out = torch.empty((t, 4096), dtype=torch.bfloat16, device=DEV)
-    us = _time(lambda: attention.launch(qkv, out, data, cfg, chunks=a.chunks, stages=a.stages, issuers=a.issuers), a)
+    us = _time(lambda: attention.launch(qkv, out, data, cfg, chunks=a.chunks, stages=a.stages, issuers=a.issuers,
+                                         row_groups=a.row_groups), a)
     keys = sum(min(s, a.window - 1) if a.window else s for s in seqs)
     _emit("attn_decode", us, keys * 4 * 128 * 2 + t * (9216 + 4096) * 2, batch=a.batch, q_len=a.q_len, window=a.window,
           ctx=a.ctx, chunks=a.chunks, stages=a.stages, issuers=a.issuers)
@@ -115,6 +116,7 @@ def main():
     ap.add_argument("--chunks", type=int, default=0)
     ap.add_argument("--stages", type=int, default=0)
     ap.add_argument("--issuers", type=int, default=0)
+    ap.add_argument("--row-groups", type=int, default=0)
     ap.add_argument("--tokens", type=int, default=32)
     ap.add_argument("--logits", action="store_true")
     ap.add_argument("--s1", type=int, default=0)
