@@ -60,6 +60,7 @@ constexpr int kStage = 2 * (kBlob + kBSlot);
 #define MSK_MOE_NRAW 5
 #endif
 constexpr int kNRaw = MSK_MOE_NRAW;  // ring stages
+static_assert(kNRaw >= 4, "a dequant group steps up to 4 stages at a time and wraps at most once per step");
 // nanoseconds a waiting warp of each role sleeps between polls (the dequant warps, which bound the rate, poll)
 constexpr int kSleepProducer = 200, kSleepIssuer = 40, kSleepEpilogue = 60;
 constexpr int kNA = 4;             // A slots in tensor memory, 64 columns each
@@ -409,7 +410,12 @@ struct MoeGemmArgs {
 };
 
 struct MoeBars {
-    uint64_t raw_full[kNRaw], raw_empty[kNRaw], a_full[kNA], a_empty[kNA], d_full[2], d_empty[2];
+    // raw_full: two barriers per ring stage, used by the stage's even and odd fills.  A dequant group does not see
+    // every fill of a stage (its sibling groups take the chunks in between), so with one barrier per stage its
+    // parity wait could meet a barrier still one fill behind - when a later stage's copies land before an earlier
+    // one's - and pass on the parity of two fills ago.  With alternating barriers a barrier's previous fill is two
+    // fills of the stage back, and that one was consumed before the stage could be refilled at all.
+    uint64_t raw_full[2][kNRaw], raw_empty[kNRaw], a_full[kNA], a_empty[kNA], d_full[2], d_empty[2];
     uint32_t tmem_slot;
 };
 
@@ -433,7 +439,10 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
     if (tid == 32) {
         // a ring stage (weight block + B tile) is free again when the 4 dequant warps have read the block and
         // the MMAs that read the B tile (one issuing warp per chunk) have completed
-        for (int i = 0; i < kNRaw; ++i) mbar_init(smem_u32(&bar.raw_full[i]), 1), mbar_init(smem_u32(&bar.raw_empty[i]), (4 + (p.share_chunks ? kIssuers : 1)) << psh);
+        for (int i = 0; i < kNRaw; ++i) {
+            mbar_init(smem_u32(&bar.raw_full[0][i]), 1), mbar_init(smem_u32(&bar.raw_full[1][i]), 1);
+            mbar_init(smem_u32(&bar.raw_empty[i]), (4 + (p.share_chunks ? kIssuers : 1)) << psh);
+        }
         for (int i = 0; i < kNA; ++i) mbar_init(smem_u32(&bar.a_full[i]), 4), mbar_init(smem_u32(&bar.a_empty[i]), p.share_chunks ? kIssuers : 1);
         for (int i = 0; i < 2; ++i) mbar_init(smem_u32(&bar.d_full[i]), kIssuers), mbar_init(smem_u32(&bar.d_empty[i]), 4);
         fence_mbar_init();
@@ -470,7 +479,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
     if (warp == 0) {
         // ------------------------------------------------ producer: weight block (bulk copy) + B tile (2 TMA boxes)
         if (lane == 0) {
-            int pc = 0, s = 0, sph = 1;  // stages filled so far, stage, parity of the stage's previous use
+            int pc = 0, s = 0, sph = 1, fill = 0;  // stages filled so far, stage, parity of the stage's previous use, fills of the stage so far
             const int per = 1 << psh;
             bool ok = true;
             for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
@@ -485,12 +494,12 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
                 for (int c = 0; c < nch; c += per, ++pc) {
                     if (pc >= kNRaw) ok = mbar_wait<kSleepProducer>(smem_u32(&bar.raw_empty[s]), sph, p.status, where | 2);
                     if (!ok) break;
-                    const uint32_t full = smem_u32(&bar.raw_full[s]), dst = base + s * kStage;
+                    const uint32_t full = smem_u32(&bar.raw_full[fill & 1][s]), dst = base + s * kStage;
                     mbar_expect_tx(full, per * kBlob + 2 * kBSlot);  // the B box always spans 2 chunks
                     bulk_load(dst, src + static_cast<size_t>(ii) * (per * kBlob), per * kBlob, full);
                     tma_load_3d(dst + 2 * kBlob, &tm_b, full, 0, row0, kg0 + ii * 2 * per);
                     if (++ii == nstg) ii = 0;
-                    if (++s == kNRaw) s = 0, sph ^= 1;
+                    if (++s == kNRaw) s = 0, sph ^= 1, ++fill;
                 }
             }
         }
@@ -636,12 +645,12 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
         const int my_units = blockIdx.x < n_units ? (n_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
         const int total = my_units * nch;
         bool ok = true;
-        int s = (grp >> psh) % kNRaw, sph = 0, aph = 0;
+        int s = (grp >> psh) % kNRaw, fill = 0, aph = 0;  // ring stage of the group's chunk, fills of that stage before it
         const int as = grp;  // this group's A slot
         const int sub = grp & ((1 << psh) - 1), sstep = kDqGroups >> psh;  // place in the stage; stages per step
         for (int cc = grp; cc < total && ok; cc += kDqGroups) {
             {
-                ok = mbar_wait(smem_u32(&bar.raw_full[s]), sph, p.status, where | 7);
+                ok = mbar_wait(smem_u32(&bar.raw_full[fill & 1][s]), (fill >> 1) & 1, p.status, where | 7);
                 if (ok && cc >= kNA) ok = mbar_wait(smem_u32(&bar.a_empty[as]), aph ^ 1, p.status, where | 8);
                 if (!ok) break;
                 tc_fence_after();
@@ -662,7 +671,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bar.a_full[as]));
                 s += sstep;
-                if (s >= kNRaw) s -= kNRaw, sph ^= 1;
+                if (s >= kNRaw) s -= kNRaw, ++fill;  // sstep <= 4 <= kNRaw: at most one wrap
                 aph ^= 1;
             }
         }
