@@ -302,6 +302,56 @@ __device__ void build_routing(RouteTables& rt, const RouteArgs& a, int* status, 
     __syncthreads();
 }
 
+// Up to 32 tokens: the same tables from one warp, in a fraction of the code (this runs at the head of every GEMM
+// CTA, from a cold instruction cache, before the first weight byte can be requested).  A token meets an expert at
+// most once, so an expert's pairs are a 32-bit token mask and every touched expert is exactly one group:
+//   g_expert / g_off / g_n as above, offs[g] = token mask of group g, ids_s = the ids.  Row r of an expert's list
+//   is its r-th token in ascending order: the same order build_routing produces.
+// list / pos_s are not filled: only gemm 1 in its token-per-column form uses these tables, and there a pair's row
+// follows from its expert's mask (see the epilogue).
+__device__ void build_routing_small(RouteTables& rt, const RouteArgs& a, int lane) {
+    const int P = a.T * a.top_k;
+    unsigned* emask = reinterpret_cast<unsigned*>(rt.counts);  // per local expert: tokens routed to it
+    for (int e = lane; e < kMaxExperts; e += 32) emask[e] = 0u;
+    __syncwarp();
+    for (int i = lane; i < P; i += 32) {
+        const int id = __ldcg(a.ids + (i / a.top_k) * a.ld_ids + i % a.top_k);
+        rt.ids_s[i] = static_cast<unsigned short>(id < 0 || id > 65534 ? 65535 : id);
+        const int e = id - a.local_start;
+        if (e >= 0 && e < a.local_count) atomicOr(&emask[e], 1u << (i / a.top_k));
+    }
+    __syncwarp();
+    // lane l owns experts 8 l .. 8 l + 7: exclusive scans of (touched, pairs) over the warp
+    unsigned m[8];
+    int touched = 0, pairs = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int e = lane * 8 + i;
+        m[i] = e < a.local_count ? emask[e] : 0u;
+        touched += m[i] != 0u;
+        pairs += __popc(m[i]);
+    }
+    int inc_t = touched, inc_p = pairs;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int vt = __shfl_up_sync(0xffffffffu, inc_t, o), vp = __shfl_up_sync(0xffffffffu, inc_p, o);
+        if (lane >= o) inc_t += vt, inc_p += vp;
+    }
+    int gi = inc_t - touched, off = inc_p - pairs;
+    __syncwarp();  // emask (aliasing counts) has been read by everyone
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        if (m[i] == 0u) continue;
+        rt.g_expert[gi] = static_cast<unsigned short>(lane * 8 + i);
+        rt.g_off[gi] = static_cast<unsigned short>(off);
+        rt.g_n[gi] = static_cast<unsigned short>(__popc(m[i]));
+        rt.offs[gi] = static_cast<int>(m[i]);
+        off += __popc(m[i]);
+        ++gi;
+    }
+    if (lane == 31) rt.n_groups = inc_t, rt.n_local = inc_p;
+}
+
 // ---------------------------------------------------------------- B-operand helpers
 // FP16 copy of the expert input.  Up to 32 tokens: row = token (the GEMM's B tile is the tokens themselves).
 // More: rows in expert-list order, so that an expert-group's B tile is one TMA box.
@@ -405,6 +455,7 @@ struct MoeGemmArgs {
     int inner, fuse_act;
     int S;
     int route_early;   // the routing input is final before the previous kernel ends
+    int small;         // <= 32 tokens, ids given: one warp builds the compact tables (build_routing_small)
     int share_chunks;  // 1: the issuing warps split every chunk's K steps (short units); 0: a warp per A slot
     int* status;
 };
@@ -451,10 +502,18 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
     // The expert ids are complete before this kernel can start whenever its predecessor in the stream is one
     // of this file's own kernels (gather, activation): those release their dependents only after their own
     // wait on the kernel before them.  The tables are then built while the predecessor still runs.
-    if (p.route_early) build_routing(rt, p.route, p.status, where);
+    auto route = [&]() {
+        if (p.small) {
+            if (warp == 0) build_routing_small(rt, p.route, lane);
+            __syncthreads();
+        } else {
+            build_routing(rt, p.route, p.status, where);
+        }
+    };
+    if (p.route_early) route();
     pdl_wait();  // x and the gemm-1 activations come from the previous kernels
     pdl_launch_dependents();
-    if (!p.route_early) build_routing(rt, p.route, p.status, where);
+    if (!p.route_early) route();
     if (MODE == 1 && p.x_ssq != nullptr) {
         for (int t = tid; t < p.route.T; t += kMoeThreads) {
             float s = 0.0f;
@@ -463,7 +522,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
             rs_s[t] = rsqrtf(s * p.x_inv_dim + p.x_eps);
         }
     }
-    if (MODE == 1 && blockIdx.x == 0 && p.route_pub != nullptr) {
+    if (MODE == 1 && blockIdx.x == 0 && p.route_pub != nullptr && !p.small) {
         if (tid == 0) p.route_pub[0] = rt.n_local, p.route_pub[1] = rt.n_groups;
         for (int r = tid; r < rt.n_local; r += kMoeThreads) p.route_pub[2 + r] = rt.list[r];
     }
@@ -571,17 +630,18 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
             const int g = u / per_group, rem = u % per_group, tile = rem / p.S, ks = rem % p.S;
             const int db = uc & 1, e = rt.g_expert[g], off = rt.g_off[g], n = rt.g_n[g];
             // the pair whose result sits in accumulator column `lane`
-            int mypair = -1;
-            if (p.direct) {
+            int mypair = -1, myrow = -1;  // myrow: the pair's place in the expert-ordered list (row of `inter`)
+            if (p.direct) {  // column = token
                 if (lane < p.route.T)
                     for (int sl = 0; sl < p.route.top_k; ++sl)
                         if (static_cast<int>(rt.ids_s[lane * p.route.top_k + sl]) == e + p.route.local_start) mypair = lane * p.route.top_k + sl;
+                // compact tables: the row follows from the expert's token mask
+                if (mypair >= 0) myrow = p.small ? off + __popc(static_cast<unsigned>(rt.offs[g]) & ((1u << lane) - 1u)) : rt.pos_s[mypair];
             } else if (lane < n) {
                 mypair = rt.list[off + lane];
+                myrow = off + lane;
             }
             const float myscale = (MODE == 1 && p.x_ssq != nullptr && mypair >= 0) ? rs_s[mypair / p.route.top_k] : 1.0f;
-            // fused activation: the row of `inter` that belongs to that pair (its place in the expert-ordered list)
-            const int myrow = (MODE == 1 && mypair >= 0) ? static_cast<int>(rt.pos_s[mypair]) : -1;
             const float scale = __ldg(p.gs + e);  // the expert's global scale (requested before the wait)
             ok = mbar_wait<kSleepEpilogue>(smem_u32(&bar.d_full[db]), (uc >> 1) & 1, p.status, where | 6);
             if (!ok) break;
@@ -985,6 +1045,8 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
     a.inter = static_cast<__half*>(q->inter_sorted), a.inner = q->I, a.fuse_act = s1 == 1;
     // the staging kernel precedes: the ids are final, unless they arrive from other GPUs during that kernel
     a.route_early = stage && q->logits == nullptr && !(ep != nullptr && ep->wait_flags != nullptr);
+    // compact tables where the build is on the critical path: gemm 1 straight after the kernel that chose the experts
+    a.small = direct && q->logits == nullptr && a.fuse_act && !a.route_early;
     a.share_chunks = q->T <= 4;
     rc = launch_pdl2(moe_gemm_kernel<1>, dim3(sms), dim3(kMoeThreads), smem, s, pdl, tm_b1, a);
     if (rc != 0) return rc;
