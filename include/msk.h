@@ -285,6 +285,63 @@ typedef struct {
 
 int msk_layer_decode(const MskLayerParams* p, int* status, void* stream);
 
+/* ---------------------------------------------------------------- pieces of the reference's own layer form
+ * The reference's layer (muse_decode_layer/reference.py:447-477) differs from the benchmark's op list in its
+ * residual boundaries (norm-preserving gated mixes, :339-344), its routing rule (sigmoid scores chosen by score +
+ * bias, :419-424) and a pooler / unpooler pair of projections around the experts.  These entry points are those
+ * pieces; muse_spark_open_b200/layer.py::native_kernel_fn chains them with msk_proj_skinny, msk_attn_decode and
+ * msk_moe_forward.
+ */
+typedef struct {
+    const float* x;              /* fp32 [T, H]: rows before their RMSNorm (the stream after attention) */
+    const void* norm_w;          /* bf16 [H]: the router sees rmsnorm(x, eps) * (1 + norm_w), in FP32 */
+    float* ssq;                  /* fp32 [ssq_parts + 1, T]: partial sums of squares of the rows (in); the last row
+                                    receives their totals (out) */
+    int ssq_parts;
+    float eps;
+    const float* router_w;       /* fp32 [E, H] */
+    const float* router_bias;    /* fp32 [E] or NULL */
+    int E, T, H, top_k;          /* H a multiple of 1024, <= 8192; E <= 256; top_k <= 8 */
+    int sigmoid_bias;            /* 0: softmax(logits + bias), top-k, renormalise; 1: sigmoid(multiplier * logit), top-k
+                                    of score + bias, weights = scores / (sum + 1e-15) */
+    float multiplier;
+    float* part;                 /* scratch fp32 [H/128, T, E] */
+    int32_t* ticket;             /* scratch int32 [ceil(T/32) * (ceil(E/32) + 1)], zero before the first call */
+    float* logits;               /* fp32 [T, E] (without the bias when sigmoid_bias) */
+    int32_t* topk_ids;           /* int32 [T, top_k] */
+    float* topk_weights;         /* fp32 [T, top_k] */
+    int pdl;
+} MskRouterParams;
+
+/* FP32 router: logits on CUDA cores (expert ids must not depend on tensor-core rounding), then the expert choice.
+ * Stands in for the router GEMM + routing kernel of muse_decode_layer/submission.py:3998-4016. */
+int msk_router(const MskRouterParams* p, int* status, void* stream);
+
+typedef struct {
+    const float* stream;         /* fp32 [T, H] */
+    const void* branch;          /* [T, ldb] fp32, or bf16 when branch_bf16 != 0 */
+    int branch_bf16, ldb;
+    const void* branch_w;        /* bf16 [H] or NULL: the branch is scaled by (1 + branch_w) first */
+    const void* gate;            /* bf16 [H] residual gate, or NULL for a plain add */
+    const void* next_norm_w;     /* bf16 [H] or NULL */
+    float* stream_out;           /* fp32 [T, H] or NULL */
+    void* normed_out;            /* bf16 [T, H] = rmsnorm(stream_out, eps) * (1 + next_norm_w), or NULL */
+    float* ssq_out;              /* fp32 [T] sums of squares of stream_out, or NULL */
+    int T, H;                    /* H a multiple of 4, <= 8192 */
+    float branch_eps, eps, temperature, gate_eps;
+    int pdl;
+} MskBoundaryParams;
+
+/* stream_out = alpha * stream + beta * rmsnorm(branch * (1 + branch_w), branch_eps) with
+ * beta = sigmoid(gate / temperature), alpha = sqrt(max(sigmoid(-gate / temperature) * (1 + beta), gate_eps))
+ * (muse_decode_layer/reference.py:339-344,452-455,473-476: the SGLang residual-boundary kernels of the reference's
+ * submission have no source in its tree; this follows ref_front / ref_back). */
+int msk_residual_boundary(const MskBoundaryParams* p, void* stream);
+
+/* out = bf16(rmsnorm(x, eps) * (1 + w)), ssq[t] = sum x[t]^2 (the pre-expert norm after the pooler,
+ * muse_decode_layer/reference.py:465). */
+int msk_rmsnorm(const float* x, const void* w, void* out_bf16, float* ssq, int T, int H, float eps, int pdl, void* stream);
+
 /* ---------------------------------------------------------------- expert-parallel step
  * The reference runs one GPU and states its collectives as identities (muse_decode_layer/reference.py:8-10,
  * :467 "the all-reduce: identity"); here the exchange is real.  Requests are data-parallel (rank r owns T_local

@@ -64,6 +64,9 @@ def lib() -> C.CDLL:
         _lib.msk_moe_forward_static.argtypes = [vp, vp, vp]
         _lib.msk_layer_front.argtypes = [vp, vp, vp]
         _lib.msk_layer_decode.argtypes = [vp, vp, vp]
+        _lib.msk_router.argtypes = [vp, vp, vp]
+        _lib.msk_residual_boundary.argtypes = [vp, vp]
+        _lib.msk_rmsnorm.argtypes = [vp, vp, vp, vp, ci, ci, C.c_float, ci, vp]
         _lib.msk_ep_row_bytes.argtypes = [ci, ci]
         _lib.msk_ep_region_bytes.argtypes = [ci, ci, ci, ci, vp]
         _lib.msk_ep_region_alloc.argtypes = [C.c_size_t, vp, vp]
@@ -79,7 +82,7 @@ def lib() -> C.CDLL:
 
 # every symbol include/msk.h declares
 EXPORTS = ["msk_version", "msk_device_info", "msk_selftest_umma", "msk_proj_skinny", "msk_proj_scratch_bytes", "msk_attn_decode",
-           "msk_moe_packed_bytes", "msk_moe_pack", "msk_moe_dequant", "msk_moe_scratch_bytes", "msk_moe_forward", "msk_moe_forward_static", "msk_layer_front", "msk_layer_decode",
+           "msk_moe_packed_bytes", "msk_moe_pack", "msk_moe_dequant", "msk_moe_scratch_bytes", "msk_moe_forward", "msk_moe_forward_static", "msk_layer_front", "msk_layer_decode", "msk_router", "msk_residual_boundary", "msk_rmsnorm",
            "msk_ep_row_bytes", "msk_ep_pack", "msk_ep_reduce", "msk_ep_region_bytes", "msk_ep_region_alloc", "msk_ep_region_open",
            "msk_ep_region_close", "msk_ep_region_free", "msk_ep_step", "msk_selftest_flag_timeout"]
 
@@ -189,6 +192,22 @@ class LayerFront(C.Structure):
 
 class LayerParams(C.Structure):
     _fields_ = [("front", LayerFront), ("moe", MoeParams)]
+
+
+class RouterParams(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("norm_w", C.c_void_p), ("ssq", C.c_void_p), ("ssq_parts", C.c_int), ("eps", C.c_float),
+                ("router_w", C.c_void_p), ("router_bias", C.c_void_p), ("E", C.c_int), ("T", C.c_int), ("H", C.c_int),
+                ("top_k", C.c_int), ("sigmoid_bias", C.c_int), ("multiplier", C.c_float), ("part", C.c_void_p),
+                ("ticket", C.c_void_p), ("logits", C.c_void_p), ("topk_ids", C.c_void_p), ("topk_weights", C.c_void_p),
+                ("pdl", C.c_int)]
+
+
+class BoundaryParams(C.Structure):
+    _fields_ = [("stream", C.c_void_p), ("branch", C.c_void_p), ("branch_bf16", C.c_int), ("ldb", C.c_int),
+                ("branch_w", C.c_void_p), ("gate", C.c_void_p), ("next_norm_w", C.c_void_p), ("stream_out", C.c_void_p),
+                ("normed_out", C.c_void_p), ("ssq_out", C.c_void_p), ("T", C.c_int), ("H", C.c_int),
+                ("branch_eps", C.c_float), ("eps", C.c_float), ("temperature", C.c_float), ("gate_eps", C.c_float),
+                ("pdl", C.c_int)]
 
 
 class EpComm(C.Structure):

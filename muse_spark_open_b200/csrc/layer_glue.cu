@@ -66,6 +66,8 @@ struct RouterArgs {
     float* wts_out;
     float* logits;          // [T, E]
     int T, H, E;
+    int sigmoid_bias;       // 0: softmax over logits + bias; 1: sigmoid(multiplier * logit), chosen by score + bias
+    float multiplier;
 };
 
 constexpr int kRouterK = 128;   // k per block (one load phase)
@@ -173,7 +175,7 @@ __global__ void __launch_bounds__(256) router_kernel(RouterArgs p) {
         const int t = tw + 8 * j;
         if (t < nt && el < ne) {
             float o = sum[j] * rs_s[t];
-            if (p.bias != nullptr) o += p.bias[e0 + el];
+            if (p.bias != nullptr && !p.sigmoid_bias) o += p.bias[e0 + el];
             p.logits[static_cast<size_t>(t0 + t) * p.E + e0 + el] = o;
         }
     }
@@ -188,11 +190,109 @@ __global__ void __launch_bounds__(256) router_kernel(RouterArgs p) {
     __threadfence();
     for (int j = 0; j < 4; ++j) {
         const int t = tw + 8 * j;
-        if (t < nt)
-            route_token(p.logits + static_cast<size_t>(t0 + t) * p.E, p.E, p.top_k, el, p.ids_out + (t0 + t) * p.top_k,
-                        p.wts_out + (t0 + t) * p.top_k);
+        if (t < nt) {
+            if (p.sigmoid_bias)
+                route_token_sigmoid(p.logits + static_cast<size_t>(t0 + t) * p.E, p.bias, p.multiplier, p.E, p.top_k, el,
+                                    p.ids_out + (t0 + t) * p.top_k, p.wts_out + (t0 + t) * p.top_k);
+            else
+                route_token(p.logits + static_cast<size_t>(t0 + t) * p.E, p.E, p.top_k, el, p.ids_out + (t0 + t) * p.top_k,
+                            p.wts_out + (t0 + t) * p.top_k);
+        }
     }
     if (tid == 0) *ticket2 = 0;
+    }
+}
+
+// Residual boundary of the reference's own layer form (muse_decode_layer/reference.py:339-344,452-455,473-476):
+//   branch' = branch * (1 + branch_w)                      (optional)
+//   s_out   = alpha * stream + beta * rmsnorm(branch', branch_eps),  (alpha, beta) from the gate; without a gate a plain add
+//   normed  = bf16(rmsnorm(s_out, eps) * (1 + next_w)),   ssq[t] = sum s_out^2
+// One block per token, the row in registers (H <= 8192).
+struct BoundaryArgs {
+    const float* stream;
+    const void* branch;
+    int branch_bf16, ldb;
+    const __nv_bfloat16* branch_w;
+    const __nv_bfloat16* gate;
+    const __nv_bfloat16* next_w;
+    float* s_out;
+    __nv_bfloat16* normed;
+    float* ssq;
+    int H;
+    float branch_eps, eps, temperature, gate_eps;
+};
+
+__device__ __forceinline__ float block_sum_256(float v, float* red) {
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    return ((red[0] + red[1]) + (red[2] + red[3])) + ((red[4] + red[5]) + (red[6] + red[7]));
+}
+
+__global__ void __launch_bounds__(256) boundary_kernel(BoundaryArgs p) {
+    __shared__ float red[8];
+    const int t = blockIdx.x, tid = threadIdx.x;
+    pdl_wait();
+    pdl_launch_dependents();
+    constexpr int kMaxVec = 8;
+    float4 b[kMaxVec], s[kMaxVec];
+    float bs = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+        const int d = tid * 4 + i * 1024;
+        b[i] = make_float4(0, 0, 0, 0), s[i] = make_float4(0, 0, 0, 0);
+        if (d >= p.H) continue;
+        s[i] = __ldcg(reinterpret_cast<const float4*>(p.stream + static_cast<size_t>(t) * p.H + d));
+        if (p.branch_bf16) {
+            const uint2 r = __ldcg(reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p.branch) + static_cast<size_t>(t) * p.ldb + d));
+            b[i] = make_float4(bf16lo(r.x), bf16hi(r.x), bf16lo(r.y), bf16hi(r.y));
+        } else {
+            b[i] = __ldcg(reinterpret_cast<const float4*>(static_cast<const float*>(p.branch) + static_cast<size_t>(t) * p.ldb + d));
+        }
+        if (p.branch_w != nullptr) {
+            const uint2 w = *reinterpret_cast<const uint2*>(p.branch_w + d);
+            b[i].x *= 1.0f + bf16lo(w.x), b[i].y *= 1.0f + bf16hi(w.x), b[i].z *= 1.0f + bf16lo(w.y), b[i].w *= 1.0f + bf16hi(w.y);
+        }
+        bs += b[i].x * b[i].x + b[i].y * b[i].y + b[i].z * b[i].z + b[i].w * b[i].w;
+    }
+    const float br = p.gate != nullptr ? rsqrtf(block_sum_256(bs, red) / p.H + p.branch_eps) : 1.0f;
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+        const int d = tid * 4 + i * 1024;
+        if (d >= p.H) continue;
+        float al[4] = {1.0f, 1.0f, 1.0f, 1.0f}, be[4] = {1.0f, 1.0f, 1.0f, 1.0f};
+        if (p.gate != nullptr) {
+            const uint2 g = *reinterpret_cast<const uint2*>(p.gate + d);
+            const float gv[4] = {bf16lo(g.x), bf16hi(g.x), bf16lo(g.y), bf16hi(g.y)};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float w = gv[j] / p.temperature;
+                be[j] = 1.0f / (1.0f + expf(-w));
+                al[j] = sqrtf(fmaxf((1.0f / (1.0f + expf(w))) * (1.0f + be[j]), p.gate_eps));
+            }
+        }
+        s[i].x = al[0] * s[i].x + be[0] * (b[i].x * br), s[i].y = al[1] * s[i].y + be[1] * (b[i].y * br);
+        s[i].z = al[2] * s[i].z + be[2] * (b[i].z * br), s[i].w = al[3] * s[i].w + be[3] * (b[i].w * br);
+        ss += s[i].x * s[i].x + s[i].y * s[i].y + s[i].z * s[i].z + s[i].w * s[i].w;
+        if (p.s_out != nullptr) *reinterpret_cast<float4*>(p.s_out + static_cast<size_t>(t) * p.H + d) = s[i];
+    }
+    const float tot = block_sum_256(ss, red);
+    if (tid == 0 && p.ssq != nullptr) p.ssq[t] = tot;
+    if (p.normed == nullptr) return;
+    const float rs = rsqrtf(tot / p.H + p.eps);
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+        const int d = tid * 4 + i * 1024;
+        if (d >= p.H) continue;
+        float f[4] = {1.0f, 1.0f, 1.0f, 1.0f};
+        if (p.next_w != nullptr) {
+            const uint2 w = *reinterpret_cast<const uint2*>(p.next_w + d);
+            f[0] += bf16lo(w.x), f[1] += bf16hi(w.x), f[2] += bf16lo(w.y), f[3] += bf16hi(w.y);
+        }
+        *reinterpret_cast<uint2*>(p.normed + static_cast<size_t>(t) * p.H + d) =
+            make_uint2(pack_bf16(s[i].x * rs * f[0], s[i].y * rs * f[1]), pack_bf16(s[i].z * rs * f[2], s[i].w * rs * f[3]));
     }
 }
 
@@ -272,17 +372,54 @@ extern "C" int msk_layer_front(const MskLayerFront* f, int* status, void* stream
     rc = msk_proj_skinny(&o, status, stream);
     if (rc != 0) return rc;
 
+    MskRouterParams r = {};
+    r.x = f->stream1, r.norm_w = f->pre_expert_norm_w, r.ssq = f->ssq1, r.ssq_parts = (H + 127) / 128, r.eps = f->norm_eps;
+    r.router_w = f->router_w, r.router_bias = f->router_bias, r.E = f->E, r.T = T, r.H = H, r.top_k = f->top_k;
+    r.part = f->router_part, r.ticket = f->router_ticket, r.logits = f->logits;
+    r.topk_ids = f->topk_ids, r.topk_weights = f->topk_weights, r.pdl = 1;
+    return msk_router(&r, status, stream);
+}
+
+extern "C" int msk_router(const MskRouterParams* q, int* status, void* stream) {
+    using namespace msk;
+    (void)status;
+    if (q == nullptr || !q->x || !q->norm_w || !q->ssq || !q->router_w || !q->part || !q->ticket || !q->logits || !q->topk_ids ||
+        !q->topk_weights)
+        return MSK_ERR_INVALID;
+    if (q->T < 1 || q->H % 1024 != 0 || q->H > 8192 || q->E < 1 || q->E > 256 || q->top_k < 1 || q->top_k > 8 || q->top_k > q->E ||
+        q->ssq_parts < 1)
+        return MSK_ERR_UNSUPPORTED;
     RouterArgs r = {};
-    r.s1 = f->stream1, r.w = static_cast<const __nv_bfloat16*>(f->pre_expert_norm_w), r.ssq = f->ssq1;
-    r.ssq_parts = (H + 127) / 128, r.eps = f->norm_eps, r.R = f->router_w, r.bias = f->router_bias;
-    r.part = f->router_part, r.ticket = f->router_ticket, r.logits = f->logits, r.T = T, r.H = H, r.E = f->E;
-    r.top_k = f->top_k, r.ids_out = f->topk_ids, r.wts_out = f->topk_weights;
-    const int ks = H / kRouterK;  // <= 64
-    const int et = (f->E + kRouterE - 1) / kRouterE, n_tg = (T + kRouterT - 1) / kRouterT;
+    r.s1 = q->x, r.w = static_cast<const __nv_bfloat16*>(q->norm_w), r.ssq = q->ssq;
+    r.ssq_parts = q->ssq_parts, r.eps = q->eps, r.R = q->router_w, r.bias = q->router_bias;
+    r.part = q->part, r.ticket = q->ticket, r.logits = q->logits, r.T = q->T, r.H = q->H, r.E = q->E;
+    r.top_k = q->top_k, r.ids_out = q->topk_ids, r.wts_out = q->topk_weights;
+    r.sigmoid_bias = q->sigmoid_bias, r.multiplier = q->multiplier;
+    const int ks = q->H / kRouterK;  // <= 64
+    const int et = (q->E + kRouterE - 1) / kRouterE, n_tg = (q->T + kRouterT - 1) / kRouterT;
     // one block per token group: letting a block walk several groups so that the grid stays within one wave of
     // CTAs measured slower (each group is a chain of global round trips; 55 against 45 us at 256 tokens)
-    const int gz = n_tg;
-    return launch1(router_kernel, dim3(ks, et, gz), dim3(256), 0, s, 1, r);
+    return launch1(router_kernel, dim3(ks, et, n_tg), dim3(256), 0, static_cast<cudaStream_t>(stream), q->pdl, r);
+}
+
+extern "C" int msk_residual_boundary(const MskBoundaryParams* q, void* stream) {
+    using namespace msk;
+    if (q == nullptr || !q->stream || !q->branch || q->T < 1 || q->H < 4 || q->H % 4 != 0 || q->H > 8192 || q->ldb % 4 != 0)
+        return MSK_ERR_INVALID;
+    BoundaryArgs a = {};
+    a.stream = q->stream, a.branch = q->branch, a.branch_bf16 = q->branch_bf16, a.ldb = q->ldb > 0 ? q->ldb : q->H;
+    a.branch_w = static_cast<const __nv_bfloat16*>(q->branch_w), a.gate = static_cast<const __nv_bfloat16*>(q->gate);
+    a.next_w = static_cast<const __nv_bfloat16*>(q->next_norm_w), a.s_out = q->stream_out;
+    a.normed = static_cast<__nv_bfloat16*>(q->normed_out), a.ssq = q->ssq_out, a.H = q->H;
+    a.branch_eps = q->branch_eps, a.eps = q->eps, a.temperature = q->temperature > 0.0f ? q->temperature : 0.3f;
+    a.gate_eps = q->gate_eps;
+    return launch1(boundary_kernel, dim3(q->T), dim3(256), 0, static_cast<cudaStream_t>(stream), q->pdl, a);
+}
+
+extern "C" int msk_rmsnorm(const float* x, const void* w, void* out_bf16, float* ssq, int T, int H, float eps, int pdl, void* stream) {
+    using namespace msk;
+    if (!x || !w || !out_bf16 || !ssq || T < 1 || H < 4 || H % 4 != 0 || H > 8192) return MSK_ERR_INVALID;
+    return launch_prep(x, w, out_bf16, ssq, T, H, eps, static_cast<cudaStream_t>(stream), pdl);
 }
 
 extern "C" int msk_layer_decode(const MskLayerParams* p, int* status, void* stream) {

@@ -54,6 +54,54 @@ __device__ __forceinline__ void route_token_nv(const float* logits, int n, int t
         wts[lane] = my_p / sum;
     }
 }
+// The reference layer's own rule (muse_decode_layer/reference.py:419-424,462-463): scores = sigmoid(multiplier *
+// logit); the top-k of score + bias are chosen (ties to the lower expert id); the weights are the UNBIASED scores
+// of the chosen, divided by their sum + 1e-15.
+template <int NV>
+__device__ __forceinline__ void route_token_sigmoid_nv(const float* logits, const float* bias, float multiplier, int n,
+                                                       int top_k, int lane, int* ids, float* wts) {
+    uint32_t key[NV];
+    float sc[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int e = lane + 32 * i;
+        sc[i] = 0.0f, key[i] = 0u;
+        if (e < n) {
+            sc[i] = 1.0f / (1.0f + expf(-multiplier * __ldcg(logits + e)));
+            key[i] = float_ordered(sc[i] + (bias != nullptr ? bias[e] : 0.0f));
+        }
+    }
+    float sum = 0.0f, my_p = 0.0f;
+    int my_id = 0;
+    for (int k = 0; k < top_k; ++k) {
+        uint32_t best = 0;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) best = max(best, key[i]);
+        best = __reduce_max_sync(0xffffffffu, best);
+        int cand = 0x7fffffff;
+        float cand_s = 0.0f;
+#pragma unroll
+        for (int i = NV - 1; i >= 0; --i)
+            if (key[i] == best) cand = lane + 32 * i, cand_s = sc[i];
+        const int bi = __reduce_min_sync(0xffffffffu, cand);
+        const float pk = __shfl_sync(0xffffffffu, cand_s, bi & 31);  // the lane that holds expert bi
+        sum += pk;
+        if (lane == k) my_id = bi, my_p = pk;
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+            if (lane + 32 * i == bi) key[i] = 0u;
+    }
+    if (lane < top_k) {
+        ids[lane] = my_id;
+        wts[lane] = my_p / (sum + 1e-15f);
+    }
+}
+__device__ __forceinline__ void route_token_sigmoid(const float* logits, const float* bias, float multiplier, int n, int top_k,
+                                                    int lane, int* ids, float* wts) {
+    if (n <= 128) route_token_sigmoid_nv<4>(logits, bias, multiplier, n, top_k, lane, ids, wts);
+    else route_token_sigmoid_nv<8>(logits, bias, multiplier, n, top_k, lane, ids, wts);
+}
+
 __device__ __forceinline__ void route_token(const float* logits, int n, int top_k, int lane, int* ids, float* wts) {
     if (n <= 128) route_token_nv<4>(logits, n, top_k, lane, ids, wts);
     else route_token_nv<8>(logits, n, top_k, lane, ids, wts);

@@ -165,3 +165,100 @@ def kernel_fn(data: dict, state: dict, **tune):
     st = abi.status_for(stream.device)
     abi.check(abi.lib().msk_layer_decode(C.byref(p), st.p, abi.stream_ptr()), "msk_layer_decode")
     return hidden, out, ids
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# The reference's own layer form (muse_decode_layer/reference.py:447-477), for head_dim 128: the attention input
+# arrives normalised (bf16), both residual boundaries are norm-preserving gated mixes, the router scores are sigmoids
+# chosen by score + bias, and the experts sit between a pooler and an unpooler projection (for up to 8 tokens only the
+# first eighth of the unpooler's columns is computed, the rest of the branch is zero).  A chain of the same kernels
+# plus msk_residual_boundary / msk_router / msk_rmsnorm; nothing is fused across the boundaries (13 launches).
+ROUTER_MULTIPLIER = 0.1767766952966369
+BRANCH_EPS = 1e-8
+SLICED_MAX_TOKENS = 8
+
+
+def native_prepare(weights: dict) -> dict:
+    """weights: the reference's names (muse_decode_layer/reference.py:89-128): qkv_gate, o, attn_residual_gate,
+    pre_ffn_norm, router, router_bias, pooler, pre_expert_norm, w13 / w13_sf / w13_gs / w2 / w2_sf / w2_gs (this GPU's
+    experts), post_expert_norm, unpooler, post_ffn_norm, ffn_residual_gate, next_pre_attn_norm."""
+    if not weights["qkv_gate"].is_cuda:
+        raise abi.MskError("native_prepare() needs CUDA weights")
+    st = {k: weights[k].contiguous() for k in ("qkv_gate", "o", "attn_residual_gate", "pre_ffn_norm", "pooler", "pre_expert_norm",
+                                               "unpooler", "post_ffn_norm", "ffn_residual_gate", "next_pre_attn_norm")}
+    st["router"] = weights["router"].float().contiguous()
+    st["router_bias"] = weights["router_bias"].float().contiguous()
+    st["moe"] = moe.prepare(weights)
+    st["local_count"] = weights["w13"].shape[0]
+    st["bufs"] = {}
+    return st
+
+
+def native_kernel_fn(data: dict, state: dict):
+    """(hidden bf16 [T, H], stream fp32 [T, H], topk_ids int32 [T, 8]); new K/V rows written in place.  `data` as the
+    reference's generate_input gives it (stream, attn_input, the attention step's cache and metadata, local_start)."""
+    cfg = data["config"]
+    stream, x = data["stream"], data["attn_input"]
+    t, h = stream.shape
+    dev = stream.device
+    if t > MAX_TOKENS or h % 1024 or cfg["head_dim"] != 128:
+        raise abi.MskError("native layer form: up to 256 tokens, hidden a multiple of 1024, head_dim 128")
+    lib, sp = abi.lib(), abi.stream_ptr
+    d_exp, e = state["pooler"].shape[0], state["router"].shape[0]
+    nqkv, no = state["qkv_gate"].shape[0], state["o"].shape[1]
+    key = (t, dev.index)
+    if key not in state["bufs"]:
+        f32, bf = torch.float32, torch.bfloat16
+        mk = lambda shape, dt: torch.empty(shape, dtype=dt, device=dev)  # noqa: E731
+        state["bufs"][key] = {
+            "qkv": mk((t, nqkv), bf), "attn": mk((t, no), bf), "a": mk((t, h), f32), "s1": mk((t, h), f32), "hn": mk((t, h), bf),
+            "ssq": mk((2, t), f32), "part": mk((h // 128, t, e), f32),
+            "ticket": torch.zeros((((t + 31) // 32) * ((e + 31) // 32 + 1),), dtype=torch.int32, device=dev),
+            "logits": mk((t, e), f32), "wts": mk((t, TOP_K), f32), "pool": mk((t, d_exp), f32), "p": mk((t, d_exp), bf),
+            "pssq": mk((t,), f32), "y": mk((t, d_exp), bf), "f": mk((t, h), f32),
+        }
+    b = state["bufs"][key]
+    st = abi.status_for(dev)
+    # attention on the given (already normalised) input
+    proj.skinny(x, state["qkv_gate"], out=b["qkv"])
+    attention.launch(b["qkv"], b["attn"], data, cfg, pdl=True)
+    proj.skinny(b["attn"], state["o"], out=b["a"], pdl=True)
+    # boundary 1: stream1, the FFN input h = rmsnorm(stream1) * (1 + w) and its sum of squares
+    bp = abi.BoundaryParams()
+    bp.stream, bp.branch, bp.branch_bf16, bp.ldb = abi.ptr(stream), abi.ptr(b["a"]), 0, h
+    bp.gate, bp.next_norm_w = abi.ptr(state["attn_residual_gate"]), abi.ptr(state["pre_ffn_norm"])
+    bp.stream_out, bp.normed_out, bp.ssq_out = abi.ptr(b["s1"]), abi.ptr(b["hn"]), abi.ptr(b["ssq"][0])
+    bp.T, bp.H, bp.branch_eps, bp.eps, bp.temperature, bp.gate_eps, bp.pdl = t, h, BRANCH_EPS, RMS_EPS, 0.3, 1e-3, 1
+    abi.check(lib.msk_residual_boundary(C.byref(bp), sp()), "msk_residual_boundary")
+    # router on FP32 rmsnorm(stream1) * (1 + w): sigmoid scores, chosen by score + bias
+    ids = torch.empty((t, TOP_K), dtype=torch.int32, device=dev)
+    rp = abi.RouterParams()
+    rp.x, rp.norm_w, rp.ssq, rp.ssq_parts, rp.eps = abi.ptr(b["s1"]), abi.ptr(state["pre_ffn_norm"]), abi.ptr(b["ssq"]), 1, RMS_EPS
+    rp.router_w, rp.router_bias, rp.E, rp.T, rp.H, rp.top_k = abi.ptr(state["router"]), abi.ptr(state["router_bias"]), e, t, h, TOP_K
+    rp.sigmoid_bias, rp.multiplier = 1, ROUTER_MULTIPLIER
+    rp.part, rp.ticket, rp.logits = abi.ptr(b["part"]), abi.ptr(b["ticket"]), abi.ptr(b["logits"])
+    rp.topk_ids, rp.topk_weights, rp.pdl = abi.ptr(ids), abi.ptr(b["wts"]), 1
+    abi.check(lib.msk_router(C.byref(rp), st.p, sp()), "msk_router")
+    # pooler, pre-expert norm, local experts
+    proj.skinny(b["hn"], state["pooler"], out=b["pool"], pdl=True)
+    abi.check(lib.msk_rmsnorm(abi.ptr(b["pool"]), abi.ptr(state["pre_expert_norm"]), abi.ptr(b["p"]), abi.ptr(b["pssq"]), t, d_exp,
+                              RMS_EPS, 1, sp()), "msk_rmsnorm")
+    local_start = int(data["local_start"])             # the prepared experts are, by definition, the ones that start here
+    state["moe"]["weights_start"] = local_start
+    moe.forward(b["p"], ids, b["wts"], state["moe"], local_start, state["local_count"], out=b["y"], pdl=True)
+    # unpooler (sliced for few tokens), boundary 2
+    if t <= SLICED_MAX_TOKENS:
+        b["f"].zero_()
+        sl = h // 8
+        proj.skinny(b["y"], state["unpooler"][:sl], out=b["f"][:, :sl])
+    else:
+        proj.skinny(b["y"], state["unpooler"], out=b["f"], pdl=True)
+    out = torch.empty((t, h), dtype=torch.float32, device=dev)
+    hidden = torch.empty((t, h), dtype=torch.bfloat16, device=dev)
+    bp2 = abi.BoundaryParams()
+    bp2.stream, bp2.branch, bp2.branch_bf16, bp2.ldb = abi.ptr(b["s1"]), abi.ptr(b["f"]), 0, h
+    bp2.branch_w, bp2.gate, bp2.next_norm_w = abi.ptr(state["post_ffn_norm"]), abi.ptr(state["ffn_residual_gate"]), abi.ptr(state["next_pre_attn_norm"])
+    bp2.stream_out, bp2.normed_out = abi.ptr(out), abi.ptr(hidden)
+    bp2.T, bp2.H, bp2.branch_eps, bp2.eps, bp2.temperature, bp2.gate_eps, bp2.pdl = t, h, BRANCH_EPS, RMS_EPS, 0.3, 1e-3, 1
+    abi.check(lib.msk_residual_boundary(C.byref(bp2), sp()), "msk_residual_boundary")
+    return hidden, out, ids

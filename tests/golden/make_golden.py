@@ -109,7 +109,7 @@ def proj_cases(ref):
 
 def layer_cases(ref):
     """The reference's own layer functions (ref_front / ref_back behind ref_kernel) at small shapes, head_dim 128."""
-    ref.HIDDEN, ref.HEAD_DIM, ref.HQ, ref.HKV = 512, 128, 4, 1
+    ref.HIDDEN, ref.HEAD_DIM, ref.HQ, ref.HKV = 1024, 128, 8, 1
     ref.Q_SIZE, ref.KV_SIZE = ref.HQ * ref.HEAD_DIM, ref.HKV * ref.HEAD_DIM
     ref.QKV_SIZE = 2 * ref.Q_SIZE + 2 * ref.KV_SIZE
     ref.SM_SCALE = ref.HEAD_DIM ** -0.5
