@@ -1,7 +1,16 @@
 // Gated attention decode (L = 1) and 8-token verify (L = 8) over a paged FP8-E4M3 KV cache, one launch.
 //
 // Grid (chunks C, KV heads, requests); the C CTAs of one (request, KV head) form a thread block
-// cluster and split that request's cached keys between them (split-KV).  One CTA = 128 threads.
+// cluster and split that request's cached keys between them (split-KV).
+// Decode CTA: 320 threads = eight arithmetic warps (two row groups of four: one warp per 32-key quarter of a tile,
+// a row group per four query rows), one MMA warp and one copying warp, two CTAs per SM.  The two extra warps do
+// nothing but issue (both MMAs of every tile / the TMA copies) and meet the others only through mbarriers; the K
+// half and the V half of a ring slot are refilled the moment the MMA that read them has finished, so each copy has
+// about two tiles' time to land; P and the output accumulator are double-buffered, so a tile's second MMA has a
+// whole iteration before its result is folded in; the arithmetic warps are left with one named barrier per tile.
+// (Timestamps showed why: with two arithmetic warps issuing, a tile cost 4200 clocks per CTA, 1200 of them the
+// wait for a copy that had been issued a moment before it was needed and 1400 the issuing itself, on the path
+// of all eight warps; now 2200, against 2900 for two CTAs per SM at the copy bandwidth.)
 //
 // Per 128-key tile (two 64-token pages, or 128 / page_size pages):
 //   TMA      4-D boxes [page_size tokens x 128 B] of K and of V land in shared memory with the
@@ -15,13 +24,14 @@
 //   softmax  thread = key: tcgen05.ld its row of S^T, scale, window / causal mask, running maximum
 //            per query row (redux.sync over the warp, shared memory over the 4 warps), p = 2^(s-m)
 //            split into two E4M3 terms the same way, written as the K-major B operand P[row, key].
-//            A single thread can issue only about one tcgen05.mma per 100 clocks whatever N is, so 4 (decode)
-//            or 2 (verify) warps issue, each into its own accumulator columns, summed when read.
+//            A single thread can issue only about one tcgen05.mma per 100 clocks whatever N is; in the verify form
+//            two warps issue, each into its own accumulator columns, summed when read.
 //   MMA 2    O^T[d, row] = V^T[d, key] . P[row, key]; V stays as stored (MN-major A operand).
 //   acc      thread = d: o[row] = o[row] * alpha[row] + O^T[d, row]  (FP32 registers).
 // The L new tokens never travel through global memory: the last CTA of the cluster applies
 // RMSNorm + RoPE to the new keys, quantises keys and values to E4M3, writes them to the cache
-// rows `cache_loc` and attends them from registers / shared memory in FP32.
+// rows `cache_loc` and attends them from registers / shared memory in FP32 (decode: before the tile loop, with
+// the loads of the query rows, so that nothing but the fold-in is left for the end; verify: after the loop).
 // Verify blocks (64 query rows per KV head) run the same tile loop with 512 threads: four row groups of 16 rows,
 // each a full set of four warps (one per 32-key quarter of the tile), so that a thread's serial work per tile is
 // 16 rows, four warps share every scheduler and the instruction latencies overlap (with one warp per scheduler the
@@ -39,7 +49,7 @@
 
 namespace msk {
 
-constexpr int kAttnMaxStages = 4;
+constexpr int kAttnMaxStages = 6;
 constexpr int kTileKeys = 128;
 constexpr int kStageBytes = 2 * kTileKeys * 128;  // K tile + V tile
 constexpr int kMaxTilesPerCta = 160;
@@ -82,6 +92,10 @@ __device__ __forceinline__ float e4m3_to_f(uint32_t byte) {
     __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(byte), __NV_E4M3);
     return __half2float(*reinterpret_cast<__half*>(&h));
 }
+__device__ __forceinline__ float2 e4m3x2_to_f2(uint32_t two) {  // low byte -> x
+    __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(two), __NV_E4M3);
+    return __half22float2(*reinterpret_cast<__half2*>(&h));
+}
 __device__ __forceinline__ uint32_t f_to_e4m3(float a) {
     return __nv_cvt_float_to_fp8(a, __NV_SATFINITE, __NV_E4M3);
 }
@@ -118,27 +132,42 @@ __device__ __forceinline__ void tmem_ld_rows(uint32_t taddr, uint32_t (&r)[BR]) 
 
 // L: tokens per request (1 decode, 8 verify); ISS: MMA-issuing warps (one thread issues only ~1 MMA per 100
 // clocks); RG: row groups = sets of four warps (one per 32-key quarter of a tile) that split the 8 L query rows.
-template <int L, int ISS, int RG>
-__global__ void __launch_bounds__(128 * RG, (L == 1 && RG <= 2) ? 2 : 1) attn_kernel(const __grid_constant__ CUtensorMap tm_k,
-                                                   const __grid_constant__ CUtensorMap tm_v, AttnArgs p) {
+// WS (decode): two more warps do nothing but issue -- one the TMA copies, one both MMAs of every tile -- and meet the
+// others only through mbarriers.  The arithmetic warps then have one named barrier per tile (the row maxima of
+// their row group) instead of two CTA-wide ones behind a warp that also issues; P and the output accumulator are
+// double-buffered so that a tile's second MMA has a whole iteration to finish before anyone needs its result.
+__host__ __device__ constexpr uint32_t attn_tmem_cols(int L, int ISS, bool WS) {
+    const int cols = ((L == 1 ? 2 : 1) + (WS ? 2 : 1)) * (WS ? 1 : ISS) * 16 * L;
+    return cols <= 64 ? 64 : cols <= 128 ? 128 : cols <= 256 ? 256 : 512;
+}
+
+template <int L, int ISS_, int RG, bool WS>
+__global__ void __launch_bounds__(128 * RG + (WS ? 64 : 0), (L == 1 && RG <= 2) ? 2 : 1)
+    attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, AttnArgs p) {
+    static_assert(!WS || L == 1, "the issuing warp exists in the decode form only");
+    constexpr int ISS = WS ? 1 : ISS_;        // accumulators per MMA (one per issuing thread)
     constexpr int NR = 8 * L;                 // query rows per KV head
-    constexpr int NTHR = 128 * RG, NWARP = NTHR / 32;
+    constexpr int NTHR_C = 128 * RG, NWARP_C = NTHR_C / 32;  // arithmetic threads / warps
+    constexpr int NTHR = NTHR_C + (WS ? 64 : 0), NWARP = NTHR / 32;
     constexpr int NRG = NR / RG;              // query rows per row group: a thread's serial work per tile
     constexpr int BR = NRG < 8 ? NRG : 8;     // rows per tensor-memory round trip
     static_assert(NRG % BR == 0 && (BR == 4 || BR == 8), "row groups work on blocks of 4 or 8 rows");
     constexpr int NP = 2 * NR;                // UMMA N: rows [0, NR) hold the first split term, [NR, 2 NR) the second
     constexpr int SBUF = L == 1 ? 2 : 1;      // score buffers in TMEM (2: the next tile's scores are computed ahead)
-    // SBUF * ISS * NP score columns, then ISS * NP output columns, as a power of two
-    constexpr uint32_t kCols = (SBUF + 1) * ISS * NP <= 128 ? 128 : (SBUF + 1) * ISS * NP <= 256 ? 256 : 512;
+    constexpr int PBUF = WS ? 2 : 1;          // P tiles in shared memory and output accumulators in TMEM
+    // SBUF * ISS * NP score columns, then PBUF * ISS * NP output columns, as a power of two
+    constexpr uint32_t kCols = attn_tmem_cols(L, ISS_, WS);
+    static_assert((SBUF + PBUF) * ISS * NP <= kCols, "tensor-memory columns");
     constexpr uint32_t kOCol = SBUF * ISS * NP;
     constexpr int QP_BYTES = NP * 128;
     constexpr float kLoScale = 16.0f;         // the second split term is stored times 16 (keeps small residuals in range)
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[kAttnMaxStages + 3];
+    __shared__ __align__(8) uint64_t bars[4 * kAttnMaxStages + 2];
     __shared__ uint32_t tmem_slot;
     __shared__ int page_ids[kMaxTilesPerCta * 2];
-    __shared__ __align__(16) float wred[4][NR];  // per-warp maxima of the current tile
+    __shared__ __align__(16) float wred_s[PBUF][4][NR];  // per-warp maxima of the current tile (WS: alternating)
+    auto& wred = wred_s[0];
     __shared__ float m_s[NR], alpha_s[NR], mrg_m[NR], mrg_l[NR];
     __shared__ float sc_tail[NR][L];
 
@@ -172,24 +201,38 @@ __global__ void __launch_bounds__(128 * RG, (L == 1 && RG <= 2) ? 2 : 1) attn_ke
     const int nst = p.nstages;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t s_q = base + nst * kStageBytes, s_p = s_q + QP_BYTES, s_mrg = s_p + QP_BYTES;
+    const uint32_t s_q = base + nst * kStageBytes, s_p = s_q + QP_BYTES, s_mrg = s_p + PBUF * QP_BYTES;
     uint8_t* g_q = gbase + nst * kStageBytes;
     uint8_t* g_p = g_q + QP_BYTES;
-    float* mrg_o = reinterpret_cast<float*>(g_q + 2 * QP_BYTES);  // [NR][128]
+    float* mrg_o = reinterpret_cast<float*>(g_q + (1 + PBUF) * QP_BYTES);  // [NR][128]
+    // Barriers.  Without the issuing warps: full(s) = both halves of ring slot s landed; bar_s0 / bar_s1 = scores of an
+    // even / odd tile exist; bar_o = a tile's output product exists.  WS form: the K half and the V half of a slot fill
+    // and drain on their own (full / full_v), and "scores exist" (sdone) and "output product exists" (odone) are kept
+    // per ring slot, because the copying warp waits on them too, to refill the half they free: a barrier per slot
+    // cannot complete twice before that warp has looked, since the next tile of the slot needs the refill itself.
     auto full = [&](int s) { return smem_u32(&bars[s]); };
-    const uint32_t bar_s0 = smem_u32(&bars[kAttnMaxStages]), bar_s1 = smem_u32(&bars[kAttnMaxStages + 1]),
-                   bar_o = smem_u32(&bars[kAttnMaxStages + 2]);
+    auto full_v = [&](int s) { return smem_u32(&bars[kAttnMaxStages + s]); };
+    auto sdone = [&](int s) { return smem_u32(&bars[2 * kAttnMaxStages + s]); };
+    auto odone = [&](int s) { return smem_u32(&bars[3 * kAttnMaxStages + s]); };
+    auto pready = [&](int i) { return smem_u32(&bars[4 * kAttnMaxStages + (i & 1)]); };  // WS: P of tile i written
+    const uint32_t bar_s0 = sdone(0), bar_s1 = sdone(1), bar_o = odone(0);
 
     // ---------------- set-up that does not depend on the previous kernel
     if (warp == 0) {
         tmem_alloc(smem_u32(&tmem_slot), kCols);
         tmem_relinquish();
     }
-    if (tid == 32) {
+    if (tid == (WS ? NTHR_C + 32 : 32)) {  // WS: the copying thread, which goes on to start the first copies itself
         for (int s = 0; s < nst; ++s) mbar_init(full(s), 1);
-        mbar_init(bar_s0, ISS);
-        mbar_init(bar_s1, ISS);
-        mbar_init(bar_o, ISS);
+        if constexpr (WS) {
+            for (int s = 0; s < nst; ++s) mbar_init(full_v(s), 1), mbar_init(sdone(s), 1), mbar_init(odone(s), 1);
+            mbar_init(pready(0), NWARP_C);
+            mbar_init(pready(1), NWARP_C);
+        } else {
+            mbar_init(bar_s0, ISS);
+            mbar_init(bar_s1, ISS);
+            mbar_init(bar_o, ISS);
+        }
         fence_mbar_init();
     }
     const int seq = p.seq_lens[b];
@@ -206,7 +249,40 @@ __global__ void __launch_bounds__(128 * RG, (L == 1 && RG <= 2) ? 2 : 1) attn_ke
         nt = kMaxTilesPerCta;
     }
     const int ppt = kTileKeys / p.page_size;  // pages per tile
-    for (int i = tid; i < nt * ppt; i += NTHR) {
+    // WS: the copying warp only arrives at the CTA's first barrier (it made the mbarriers, the others wait for them
+    // there) and takes no part in the fills below; its thread fetches the page ids of the first tile itself and
+    // starts that copy at once instead of waiting for the shared table.
+    constexpr int NTHR_F = WS ? NTHR_C + 32 : NTHR;  // threads that fill shared memory before the first barrier
+    int started = 0;                                 // tiles whose copies are under way
+    if constexpr (WS) {
+        if (warp == NWARP_C + 1) {
+            __syncwarp();
+            named_bar_arrive<4>(NTHR);
+            if (lane == 0 && nt > 0 && ppt <= 8) {
+                prefetch_tmap(&tm_k);
+                prefetch_tmap(&tm_v);
+                int ids[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const int pg = t_begin * ppt + k;
+                    int id = (k < ppt && pg < p.max_pages) ? p.page_table[b * p.max_pages + pg] : -1;
+                    if (id >= p.num_pages || id < -1) id = -1;  // reported by the table fill below
+                    ids[k] = id;
+                }
+                mbar_expect_tx(full(0), kTileKeys * 128);
+                mbar_expect_tx(full_v(0), kTileKeys * 128);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    if (k < ppt) {
+                        tma_load_4d(base + k * p.page_size * 128, &tm_k, full(0), 0, h, 0, ids[k]);
+                        tma_load_4d(base + kTileKeys * 128 + k * p.page_size * 128, &tm_v, full_v(0), 0, h, 0, ids[k]);
+                    }
+                }
+                started = 1;
+            }
+        }
+    }
+    for (int i = tid; i < nt * ppt && tid < NTHR_F; i += NTHR_F) {
         const int pg = t_begin * ppt + i;
         int id = pg < p.max_pages ? p.page_table[b * p.max_pages + pg] : -1;
         if (id >= p.num_pages || id < -1) {
@@ -215,16 +291,27 @@ __global__ void __launch_bounds__(128 * RG, (L == 1 && RG <= 2) ? 2 : 1) attn_ke
         }
         page_ids[i] = id;
     }
-    for (int i = tid; i < 2 * QP_BYTES / 16; i += NTHR) reinterpret_cast<uint4*>(g_q)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < (1 + PBUF) * QP_BYTES / 16 && tid < NTHR_F; i += NTHR_F)
+        reinterpret_cast<uint4*>(g_q)[i] = make_uint4(0, 0, 0, 0);
     if (tid < NR) m_s[tid] = kNeg;
     tc_fence_before();
-    __syncthreads();
+    if constexpr (WS) {
+        // barrier 5: the table and the zeroed operands exist (the copying warp waits for this one, the others only
+        // arrive); barrier 4: the mbarriers and the tensor-memory address exist (the other way round)
+        if (warp == NWARP_C + 1) {
+            named_bar_sync<5>(NTHR);
+        } else {
+            named_bar_arrive<5>(NTHR);
+            named_bar_sync<4>(NTHR);
+        }
+    } else {
+        __syncthreads();
+    }
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
     pdl_launch_dependents();
 
-    auto issue_tile = [&](int i) {  // thread 0: TMA for this CTA's tile i into ring slot i % nst
-        const int s = i % nst;
+    auto issue_tile = [&](int i, int s) {  // one thread: TMA for this CTA's tile i into ring slot s = i % nst
         const uint32_t kb = base + s * kStageBytes, vb = kb + kTileKeys * 128;
         mbar_expect_tx(full(s), kStageBytes);
         for (int j = 0; j < ppt; ++j) {
@@ -233,46 +320,121 @@ __global__ void __launch_bounds__(128 * RG, (L == 1 && RG <= 2) ? 2 : 1) attn_ke
             tma_load_4d(vb + j * p.page_size * 128, &tm_v, full(s), 0, h, 0, id);
         }
     };
-    const bool issuer = lane == 0 && warp < ISS;
+    auto issue_half = [&](int i, int s, bool values) {  // WS: the keys or the values of tile i into their half of slot s
+        const uint32_t dst = base + s * kStageBytes + (values ? kTileKeys * 128 : 0);
+        const uint32_t bar = values ? full_v(s) : full(s);
+        mbar_expect_tx(bar, kTileKeys * 128);
+        for (int j = 0; j < ppt; ++j)
+            tma_load_4d(dst + j * p.page_size * 128, values ? &tm_v : &tm_k, bar, 0, h, 0, page_ids[i * ppt + j]);
+    };
+    const bool issuer = !WS && lane == 0 && warp < ISS;
+    const int acc = WS ? 0 : warp;  // the accumulator an issuing thread owns
     auto sbar = [&](int i) { return (SBUF == 2 && (i & 1)) ? bar_s1 : bar_s0; };
-    auto issue_mma1 = [&](int i) {  // issuing warp w: S_w^T = K[:, its k-steps] . q^T, score buffer i % SBUF
-        const uint32_t kb = base + (i % nst) * kStageBytes;
+    // `slot`: ring slot of tile i (i % nst; the issuing warp of the WS form counts it instead of dividing)
+    auto issue_mma1 = [&](int i, int slot, uint32_t done) {  // issuing thread w: S_w^T = K[:, its k-steps] . q^T, score buffer i % SBUF
+        const uint32_t kb = base + slot * kStageBytes;
         const uint32_t idesc = umma_idesc(128, NP, 0, 0, 0, 0);
         const uint64_t ad = umma_smem_desc(kb, 16, 1024, kSwizzle128);
         const uint64_t bq = umma_smem_desc(s_q, 16, 1024, kSwizzle128);
-        const uint32_t d = tmem + ((i % SBUF) * ISS + warp) * NP;
+        const uint32_t d = tmem + ((i % SBUF) * ISS + acc) * NP;
 #pragma unroll
-        for (int k = warp; k < 4; k += ISS) umma_f8_ss(d, ad + 2 * k, bq + 2 * k, idesc, k != warp);
-        umma_commit(sbar(i));
+        for (int k = acc; k < 4; k += ISS) umma_f8_ss(d, ad + 2 * k, bq + 2 * k, idesc, k != acc);
+        umma_commit(done);
     };
-    auto issue_mma2 = [&](int i) {  // issuing warp w: O_w^T = V^T[:, its 32-key steps] . P^T
-        const uint32_t vb = base + (i % nst) * kStageBytes + kTileKeys * 128;
+    auto issue_mma2 = [&](int i, int slot, uint32_t done) {  // issuing thread w: O_w^T = V^T[:, its 32-key steps] . P^T
+        const uint32_t vb = base + slot * kStageBytes + kTileKeys * 128;
         const uint32_t idesc = umma_idesc(128, NP, 0, 0, 1, 0);
-        const uint64_t bp = umma_smem_desc(s_p, 16, 1024, kSwizzle128);
-        const uint32_t d = tmem + kOCol + warp * NP;
+        const uint64_t bp = umma_smem_desc(s_p + (WS ? (i & 1) * QP_BYTES : 0), 16, 1024, kSwizzle128);
+        const uint32_t d = tmem + kOCol + (WS ? (i & 1) : acc) * NP;
+        const uint64_t av = umma_smem_desc(vb, 1024, 1024, kSwizzle128);
 #pragma unroll
-        for (int k = warp; k < 4; k += ISS)
-            umma_f8_ss(d, umma_smem_desc(vb + 4096 * k, 1024, 1024, kSwizzle128), bp + 2 * k, idesc, k != warp);
-        umma_commit(bar_o);
+        for (int k = acc; k < 4; k += ISS) umma_f8_ss(d, av + (4096 >> 4) * k, bp + 2 * k, idesc, k != acc);
+        umma_commit(done);
     };
 
-    if (tid == 0) {
-        prefetch_tmap(&tm_k);
-        prefetch_tmap(&tm_v);
-        for (int i = 0; i < nt && i < nst; ++i) issue_tile(i);
+    if (tid == (WS ? NTHR_C + 32 : 0)) {
+        if (started == 0) {
+            prefetch_tmap(&tm_k);
+            prefetch_tmap(&tm_v);
+        }
+        for (int i = started; i < nt && i < nst; ++i) {
+            if constexpr (WS) issue_half(i, i, false), issue_half(i, i, true);
+            else issue_tile(i, i);
+        }
     }
 
     // ---------------- queries: RMSNorm, scale, RoPE, BF16 rounding, split into two E4M3 terms
     pdl_wait();
     const float k_scale = __ldg(p.k_scale), v_scale = __ldg(p.v_scale);
     const float qs = p.q_split_scale;
+    // Decode: the new token's part of the step needs nothing from the cache, so the cluster's last CTA does it here,
+    // with the loads in flight together: every warp derives the new key itself (registers only) and takes the
+    // score of its query row against it; warp 0 also stores the new key and value bytes; each arithmetic thread
+    // keeps the new value of its channel and the gates of the rows it will finalise.
+    const bool tail_cta = rank == C - 1;
+    float vnew_d = 0.0f;
+    float gate_r[L == 1 ? NRG : 1];
+    if constexpr (L == 1) {
+        const int rows_per_cta = NR / C;
+#pragma unroll
+        for (int k = 0; k < NRG; ++k) {
+            const int nl = rg + k * RG, n = rank * rows_per_cta + nl;
+            gate_r[k] = (warp < NWARP_C && nl < rows_per_cta)
+                            ? __bfloat162float(p.qkv[static_cast<size_t>(b) * p.ld_qkv + (p.Hq + 2 * p.Hkv + h * 8 + (n & 7)) * 128 + ktid])
+                            : 0.0f;
+        }
+        if (tail_cta && warp < NWARP_C) {
+            const float v = __bfloat162float(p.qkv[static_cast<size_t>(b) * p.ld_qkv + (p.Hq + p.Hkv + h) * 128 + ktid]);
+            vnew_d = e4m3_to_f(f_to_e4m3(__fdiv_rn(v, v_scale)));
+        }
+    }
     for (int n = warp; n < NR; n += NWARP) {
         const int j = n >> 3, g = n & 7;
         const size_t tok = static_cast<size_t>(b) * L + j;
         const __nv_bfloat16* src = p.qkv + tok * p.ld_qkv + (h * 8 + g) * 128 + 4 * lane;
         const uint2 raw = *reinterpret_cast<const uint2*>(src);
         float x[4] = {bf16lo(raw.x), bf16hi(raw.x), bf16lo(raw.y), bf16hi(raw.y)};
+        float knew_r[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (L == 1 && tail_cta) {
+            const __nv_bfloat16* ksrc = p.qkv + tok * p.ld_qkv + (p.Hq + h) * 128 + 4 * lane;
+            const uint2 kr = *reinterpret_cast<const uint2*>(ksrc);
+            uint2 vr = make_uint2(0, 0);
+            long long row = -1;
+            if (n == 0) {
+                vr = *reinterpret_cast<const uint2*>(ksrc + p.Hkv * 128);
+                row = p.cache_loc[tok];
+            }
+            float kx[4] = {bf16lo(kr.x), bf16hi(kr.x), bf16lo(kr.y), bf16hi(kr.y)};
+            norm_rope_row(kx, 1.0f, p.inv_freq, seq, lane);
+            uint32_t kb = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t a = f_to_e4m3(__fdiv_rn(kx[i], k_scale));
+                kb |= a << (8 * i);
+                knew_r[i] = e4m3_to_f(a);
+            }
+            if (n == 0) {
+                const float vx[4] = {bf16lo(vr.x), bf16hi(vr.x), bf16lo(vr.y), bf16hi(vr.y)};
+                uint32_t vb = 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) vb |= f_to_e4m3(__fdiv_rn(vx[i], v_scale)) << (8 * i);
+                const bool row_ok = row >= 0 && row < static_cast<long long>(p.num_pages) * p.page_size;
+                if (!row_ok && lane == 0) report(p.status, MSK_ERR_BOUNDS, where | 7, static_cast<int>(row), p.num_pages);
+                if (row_ok) {
+                    const size_t off = (static_cast<size_t>(row) * p.Hkv + h) * 128 + 4 * lane;
+                    *reinterpret_cast<uint32_t*>(p.k_cache + off) = kb;
+                    *reinterpret_cast<uint32_t*>(p.v_cache + off) = vb;
+                }
+            }
+        }
         norm_rope_row(x, p.qk_scale_factor, p.inv_freq, seq + j, lane);
+        if (L == 1 && tail_cta) {
+            float dot = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dot += __bfloat162float(__float2bfloat16(x[i])) * knew_r[i];
+            dot = warp_sum(dot);
+            if (lane == 0) sc_tail[n][0] = dot * (k_scale * p.sm_scale * 1.4426950408889634f);
+        }
         uint32_t hi = 0, lo = 0;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -321,16 +483,18 @@ __global__ void __launch_bounds__(128 * RG, (L == 1 && RG <= 2) ? 2 : 1) attn_ke
     };
     // second half of a tile's work: wait for O^T = V^T . P^T, fold it into the running output, refill the ring
     // slot.  It runs one iteration late (after the next tile's maxima), so the MMA's latency is hidden.
-    auto finish_tile = [&](int j) {
-        ok = mbar_wait(bar_o, j & 1, p.status, where | 6) && ok;
+    // (WS: two iterations' worth late, from the accumulator j & 1, with the rescale factors of tile j in `al_j`.)
+    auto finish_tile = [&](int j, const float* al_j, uint32_t done, int parity) {
+        ok = mbar_wait(done, parity, p.status, where | 6) && ok;
         tc_fence_after();
 #pragma unroll
         for (int c0 = 0; c0 < NRG; c0 += BR) {
             uint32_t hi[ISS][BR], lo[ISS][BR];
 #pragma unroll
             for (int w = 0; w < ISS; ++w) {
-                tmem_ld_rows<BR>(trow + kOCol + w * NP + r_lo + c0, hi[w]);
-                tmem_ld_rows<BR>(trow + kOCol + w * NP + NR + r_lo + c0, lo[w]);
+                const uint32_t col = trow + kOCol + (WS ? (j & 1) : w) * NP + r_lo + c0;
+                tmem_ld_rows<BR>(col, hi[w]);
+                tmem_ld_rows<BR>(col + NR, lo[w]);
             }
             tmem_wait_ld();
 #pragma unroll
@@ -338,26 +502,153 @@ __global__ void __launch_bounds__(128 * RG, (L == 1 && RG <= 2) ? 2 : 1) attn_ke
                 float a = 0.0f, b = 0.0f;
 #pragma unroll
                 for (int w = 0; w < ISS; ++w) a += __uint_as_float(hi[w][g]), b += __uint_as_float(lo[w][g]);
-                const float al = L == 1 ? alpha_r[c0 + g] : alpha_s[r_lo + c0 + g];
+                const float al = L == 1 ? al_j[c0 + g] : alpha_s[r_lo + c0 + g];
                 o_acc[c0 + g] = o_acc[c0 + g] * al + (a + b * (1.0f / kLoScale));
             }
         }
         tc_fence_before();
-        if (tid == 0 && ok && j + nst < nt) issue_tile(j + nst);  // both MMAs that read slot j % nst are done
+        if (!WS && tid == 0 && ok && j + nst < nt) issue_tile(j + nst, j % nst);  // both MMAs that read slot j % nst are done
         __syncwarp();
     };
 
+    if constexpr (WS) {
+      if (warp == NWARP_C) {
+        // ---- the MMA warp: one thread, no arithmetic, no CTA barrier inside the loop
+        if (lane == 0 && nt > 0) {
+            bool live = mbar_wait(full(0), 0, p.status, where | 3);
+            tc_fence_after();
+            if (live) issue_mma1(0, 0, sdone(0));
+            int s_cur = 0, ph_cur = 0;                               // ring slot and fill parity of tile i
+            int s_nxt = nst > 1 ? 1 : 0, ph_nxt = nst > 1 ? 0 : 1;   // of tile i + 1
+            for (int i = 0; i < nt && live; ++i) {
+                if (i + 1 < nt) {  // the next tile's scores, one buffer ahead of their readers
+                    live = mbar_wait(full(s_nxt), ph_nxt, p.status, where | 4);
+                    tc_fence_after();
+                    if (!live) break;
+                    issue_mma1(i + 1, s_nxt, sdone(s_nxt));
+                }
+                live = mbar_wait(pready(i), (i >> 1) & 1, p.status, where | 8) &&
+                       mbar_wait(full_v(s_cur), ph_cur, p.status, where | 9);
+                if (!live) break;
+                tc_fence_after();
+                issue_mma2(i, s_cur, odone(s_cur));
+                s_cur = s_nxt, ph_cur = ph_nxt;
+                if (++s_nxt == nst) s_nxt = 0, ph_nxt ^= 1;
+            }
+        }
+        __syncwarp();
+      } else if (warp == NWARP_C + 1) {
+        // ---- the copying warp: refills the K half of a slot as soon as its tile's scores exist and the V half as
+        // soon as its output product exists; every copy then has about two iterations to land
+        if (lane == 0) {
+            int s_i = 0, ph_i = 0, s_p = 0, ph_p = 0;  // slot / parity of tile i and of tile i - 1
+            for (int i = 0; i + nst < nt + 1; ++i) {
+                if (i + nst < nt) {
+                    if (!mbar_wait(sdone(s_i), ph_i, p.status, where | 10)) break;
+                    issue_half(i + nst, s_i, false);
+                }
+                if (i >= 1) {
+                    if (!mbar_wait(odone(s_p), ph_p, p.status, where | 11)) break;
+                    issue_half(i - 1 + nst, s_p, true);
+                }
+                s_p = s_i, ph_p = ph_i;
+                if (++s_i == nst) s_i = 0, ph_i ^= 1;
+            }
+        }
+        __syncwarp();
+      } else {
+        // ---- the arithmetic warps
+        float alpha_p[NRG];  // rescale factors of the tile before the current one (its output is folded in late)
+#pragma unroll
+        for (int g = 0; g < NRG; ++g) alpha_p[g] = 1.0f;
+        int slot = 0, ph = 0, slot_p = 0, ph_p = 0;  // ring slot / fill parity of tile i and of tile i - 1
+        for (int i = 0; i < nt; ++i) {
+            ok = mbar_wait(sdone(slot), ph, p.status, where | 5) && ok;
+            tc_fence_after();
+            const int pos = (t_begin + i) * kTileKeys + ktid;  // this thread's key position
+            const bool vis = pos < seq && (W == 0 || pos > seq - W);
+            float skeep[NRG];
+#pragma unroll
+            for (int c0 = 0; c0 < NRG; c0 += BR) {
+                float sc[BR];
+                load_scores(i, r_lo + c0, sc);
+#pragma unroll
+                for (int g = 0; g < BR; ++g) {
+                    const float sv = vis ? sc[g] * s_scale : kNeg;
+                    skeep[c0 + g] = sv;
+                    const float mx = redux_max(sv);
+                    if (lane == 0) wred_s[i & 1][kq][r_lo + c0 + g] = mx;
+                }
+            }
+            // the four warps of this row group; the maxima buffers alternate, so one barrier per tile is enough
+            if (rg == 0) named_bar_sync<1>(128);
+            else named_bar_sync<2>(128);
+            float tm[NRG];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+#pragma unroll
+                for (int q4 = 0; q4 < NRG / 4; ++q4) {
+                    const float4 a = *reinterpret_cast<const float4*>(&wred_s[i & 1][w][r_lo + 4 * q4]);
+                    const float v4[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) tm[4 * q4 + g] = w == 0 ? v4[g] : fmaxf(tm[4 * q4 + g], v4[g]);
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < NRG; ++g) {
+                const float mn = fmaxf(tm[g], m_r[g]);
+                alpha_p[g] = alpha_r[g];
+                alpha_r[g] = ex2(m_r[g] - mn);
+                m_r[g] = mn;
+            }
+            // V rows past the cached length may hold anything (even NaN bytes): zero them so that 0 * V stays 0
+            if (rg == 0 && pos >= seq) {
+                ok = mbar_wait(full_v(slot), ph, p.status, where | 12) && ok;
+                uint8_t* vrow = gbase + slot * kStageBytes + kTileKeys * 128 + ktid * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) reinterpret_cast<uint4*>(vrow)[c] = make_uint4(0, 0, 0, 0);
+            }
+            // p = 2^(s - m) as two E4M3 terms into P buffer i & 1 (its previous reader, the second MMA of tile
+            // i - 2, was waited for at the end of the last iteration)
+            uint8_t* pb = g_p + (i & 1) * QP_BYTES;
+#pragma unroll
+            for (int g = 0; g < NRG; g += 2) {  // two rows per conversion instruction
+                const int n = r_lo + g;
+                const float pr0 = vis ? ex2(skeep[g] - m_r[g]) : 0.0f;
+                const float pr1 = vis ? ex2(skeep[g + 1] - m_r[g + 1]) : 0.0f;
+                l_part[g] = l_part[g] * alpha_r[g] + pr0;
+                l_part[g + 1] = l_part[g + 1] * alpha_r[g + 1] + pr1;
+                const float ps0 = pr0 * kPScale, ps1 = pr1 * kPScale;
+                const uint32_t bh = f2_to_e4m3x2(ps0, ps1);
+                const float2 back = e4m3x2_to_f2(bh);
+                const uint32_t bl = f2_to_e4m3x2((ps0 - back.x) * kLoScale, (ps1 - back.y) * kLoScale);
+                pb[swz128(n, ktid)] = static_cast<uint8_t>(bh);
+                pb[swz128(n + 1, ktid)] = static_cast<uint8_t>(bh >> 8);
+                pb[swz128(NR + n, ktid)] = static_cast<uint8_t>(bl);
+                pb[swz128(NR + n + 1, ktid)] = static_cast<uint8_t>(bl >> 8);
+            }
+            tc_fence_before();
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(pready(i));
+            if (i > 0) finish_tile(i - 1, alpha_p, odone(slot_p), ph_p);  // issued a whole iteration ago
+            slot_p = slot, ph_p = ph;
+            if (++slot == nst) slot = 0, ph ^= 1;
+        }
+        if (nt > 0) finish_tile(nt - 1, alpha_r, odone(slot_p), ph_p);
+      }
+    } else {
     if (issuer && nt > 0) {
         ok = mbar_wait(full(0), 0, p.status, where | 3);
         tc_fence_after();
-        if (ok) issue_mma1(0);
+        if (ok) issue_mma1(0, 0, sbar(0));
     }
     __syncwarp();
     for (int i = 0; i < nt; ++i) {
         if (SBUF == 2 && issuer && ok && i + 1 < nt) {  // next tile's scores, computed while this tile's softmax runs
             ok = mbar_wait(full((i + 1) % nst), ((i + 1) / nst) & 1, p.status, where | 4);
             tc_fence_after();
-            if (ok) issue_mma1(i + 1);
+            if (ok) issue_mma1(i + 1, (i + 1) % nst, sbar(i + 1));
         }
         __syncwarp();
         ok = mbar_wait(sbar(i), (SBUF == 2 ? (i >> 1) : i) & 1, p.status, where | 5) && ok;
@@ -379,7 +670,7 @@ __global__ void __launch_bounds__(128 * RG, (L == 1 && RG <= 2) ? 2 : 1) attn_ke
                 if (lane == 0) wred[kq][r_lo + c0 + g] = mx;
             }
         }
-        if (i > 0) finish_tile(i - 1);
+        if (i > 0) finish_tile(i - 1, alpha_r, bar_o, (i - 1) & 1);
         if constexpr (SBUF == 1) tc_fence_before();  // the scores are in registers: their buffer may be overwritten
         __syncthreads();
         if constexpr (L == 1) {
@@ -412,7 +703,7 @@ __global__ void __launch_bounds__(128 * RG, (L == 1 && RG <= 2) ? 2 : 1) attn_ke
             if (issuer && ok && i + 1 < nt) {
                 ok = mbar_wait(full((i + 1) % nst), ((i + 1) / nst) & 1, p.status, where | 4);
                 tc_fence_after();
-                if (ok) issue_mma1(i + 1);
+                if (ok) issue_mma1(i + 1, (i + 1) % nst, sbar(i + 1));
             }
             __syncwarp();
         }
@@ -445,24 +736,34 @@ __global__ void __launch_bounds__(128 * RG, (L == 1 && RG <= 2) ? 2 : 1) attn_ke
         __syncthreads();
         if (issuer && ok) {
             tc_fence_after();
-            issue_mma2(i);
+            issue_mma2(i, i % nst, bar_o);
         }
         __syncwarp();
     }
-    if (nt > 0) finish_tile(nt - 1);
+    if (nt > 0) finish_tile(nt - 1, alpha_r, bar_o, (nt - 1) & 1);
+    }
+    // From here on the arithmetic threads only; the issuing warp of the WS form goes straight to the cluster barrier.
+    const int rows_per = NR / C;  // query rows each CTA finalises (C divides NR)
+    auto csync = [&]() {
+        if constexpr (WS) named_bar_sync<3>(NTHR_C);
+        else __syncthreads();
+    };
+    if (!WS || warp < NWARP_C) {
     if constexpr (L == 1) {
 #pragma unroll
         for (int g = 0; g < NRG; ++g)
             if (ktid == g) m_s[r_lo + g] = m_r[g];
     }
-    __syncthreads();
+    csync();
 
     // ---------------- the L new tokens: last CTA of the cluster, FP32 on CUDA cores
+    // (decode: keys, values, cache rows and scores of the new token were done before the main loop)
     if (rank == C - 1) {
         float* knew = reinterpret_cast<float*>(gbase);                 // [L][128] E4M3 values of the new keys
         float* vnew = knew + L * 128;                                  // [L][128]
         __nv_bfloat16* qf = reinterpret_cast<__nv_bfloat16*>(vnew + L * 128);  // [NR][128] BF16 queries
-        for (int j = warp; j < L; j += NWARP) {
+        if constexpr (L != 1) {
+        for (int j = warp; j < L; j += NWARP_C) {
             const size_t tok = static_cast<size_t>(b) * L + j;
             const long long row = p.cache_loc[tok];
             const bool row_ok = row >= 0 && row < static_cast<long long>(p.num_pages) * p.page_size;
@@ -489,7 +790,7 @@ __global__ void __launch_bounds__(128 * RG, (L == 1 && RG <= 2) ? 2 : 1) attn_ke
             }
         }
         // BF16 queries again (the MMA operands hold them split)
-        for (int n = warp; n < NR; n += NWARP) {
+        for (int n = warp; n < NR; n += NWARP_C) {
             const int j = n >> 3, g = n & 7;
             const size_t tok = static_cast<size_t>(b) * L + j;
             const uint2 raw = *reinterpret_cast<const uint2*>(p.qkv + tok * p.ld_qkv + (h * 8 + g) * 128 + 4 * lane);
@@ -497,10 +798,10 @@ __global__ void __launch_bounds__(128 * RG, (L == 1 && RG <= 2) ? 2 : 1) attn_ke
             norm_rope_row(x, p.qk_scale_factor, p.inv_freq, seq + j, lane);
             *reinterpret_cast<uint2*>(qf + n * 128 + 4 * lane) = make_uint2(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]));
         }
-        __syncthreads();
+        csync();
         // scores of (row n, new token r), r <= token of n (causal) and inside the window
         const float t_scale = k_scale * p.sm_scale * 1.4426950408889634f;
-        for (int e = tid; e < NR * L; e += NTHR) {
+        for (int e = tid; e < NR * L; e += NTHR_C) {
             const int n = e / L, r = e % L, j = n >> 3;
             float acc = 0.0f;
             for (int d = 0; d < 128; d += 2) {
@@ -510,7 +811,8 @@ __global__ void __launch_bounds__(128 * RG, (L == 1 && RG <= 2) ? 2 : 1) attn_ke
             const bool vis = r <= j && (W == 0 || r > j - W);
             sc_tail[n][r] = vis ? acc * t_scale : kNeg;
         }
-        __syncthreads();
+        csync();
+        }
         if (tid < NR) {
             float mx = m_s[tid];
             const float mo = mx;
@@ -518,7 +820,7 @@ __global__ void __launch_bounds__(128 * RG, (L == 1 && RG <= 2) ? 2 : 1) attn_ke
             alpha_s[tid] = ex2(mo - mx);
             m_s[tid] = mx;
         }
-        __syncthreads();
+        csync();
 #pragma unroll
         for (int n = 0; n < NRG; ++n) {
             const float a = alpha_s[r_lo + n], m = m_s[r_lo + n];
@@ -528,7 +830,7 @@ __global__ void __launch_bounds__(128 * RG, (L == 1 && RG <= 2) ? 2 : 1) attn_ke
             for (int r = 0; r < L; ++r) {
                 const float sc = sc_tail[r_lo + n][r];
                 const float pr = sc > 0.5f * kNeg ? ex2(sc - m) : 0.0f;
-                o += pr * kPScale * vnew[r * 128 + ktid];
+                o += pr * kPScale * (L == 1 ? vnew_d : vnew[r * 128 + ktid]);
                 if (ktid == r) l_part[n] += pr;
             }
             o_acc[n] = o;
@@ -541,8 +843,7 @@ __global__ void __launch_bounds__(128 * RG, (L == 1 && RG <= 2) ? 2 : 1) attn_ke
         const float s = warp_sum(l_part[n]);
         if (lane == 0) wred[kq][r_lo + n] = s;
     }
-    __syncthreads();
-    const int rows_per = NR / C;  // query rows each CTA finalises (C divides NR)
+    csync();
     if (tid < NR) {
         const int owner = tid / rows_per, nl = tid % rows_per;
         const float lsum = (wred[0][tid] + wred[1][tid]) + (wred[2][tid] + wred[3][tid]);
@@ -554,7 +855,9 @@ __global__ void __launch_bounds__(128 * RG, (L == 1 && RG <= 2) ? 2 : 1) attn_ke
         const int owner = (r_lo + n) / rows_per, nl = (r_lo + n) % rows_per;
         dsmem_st_f32(dsmem_addr(s_mrg + ((rank * rows_per + nl) * 128 + ktid) * 4, owner), o_acc[n]);
     }
+    }
     cluster_sync_all();
+    if (!WS || warp < NWARP_C) {
 
     // this CTA's rows nl = rg, rg + RG, ...: thread = channel d
     float val[NRG];
@@ -577,14 +880,17 @@ __global__ void __launch_bounds__(128 * RG, (L == 1 && RG <= 2) ? 2 : 1) attn_ke
     }
     // the gates of this thread's rows are requested together (a load between two stores is not moved up by the
     // compiler, and one global round trip per row is most of this epilogue)
-    float gate_r[NRG];
+    // (decode asked for them before the main loop)
+    float gate_l[L == 1 ? 1 : NRG];
+    if constexpr (L != 1) {
 #pragma unroll
-    for (int k = 0; k < NRG; ++k) {
-        const int nl = rg + k * RG, n = rank * rows_per + nl;
-        const size_t tok = static_cast<size_t>(b) * L + (n >> 3);
-        gate_r[k] = nl < rows_per ? __bfloat162float(p.qkv[tok * p.ld_qkv + (p.Hq + 2 * p.Hkv + h * 8 + (n & 7)) * 128 + ktid]) : 0.0f;
+        for (int k = 0; k < NRG; ++k) {
+            const int nl = rg + k * RG, n = rank * rows_per + nl;
+            const size_t tok = static_cast<size_t>(b) * L + (n >> 3);
+            gate_l[k] = nl < rows_per ? __bfloat162float(p.qkv[tok * p.ld_qkv + (p.Hq + 2 * p.Hkv + h * 8 + (n & 7)) * 128 + ktid]) : 0.0f;
+        }
     }
-    __syncthreads();
+    csync();
     if (ok) {
 #pragma unroll
         for (int k = 0; k < NRG; ++k) {
@@ -594,19 +900,20 @@ __global__ void __launch_bounds__(128 * RG, (L == 1 && RG <= 2) ? 2 : 1) attn_ke
             const size_t tok = static_cast<size_t>(b) * L + j;
             const float ss = (wred[0][nl] + wred[1][nl]) + (wred[2][nl] + wred[3][nl]);
             const float r = 1.0f / sqrtf(ss * (1.0f / 128.0f) + 1e-5f);
-            const float sg = 1.0f / (1.0f + __expf(-gate_r[k]));
+            const float sg = 1.0f / (1.0f + __expf(-(L == 1 ? gate_r[k] : gate_l[k])));
             p.out[tok * p.ld_out + (h * 8 + g) * 128 + ktid] = __float2bfloat16(val[k] * r * sg);
         }
+    }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, kCols);
 }
 
-template <int L, int ISS, int RG>
+template <int L, int ISS, int RG, bool WS>
 int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
     constexpr int NR = 8 * L, NP = 2 * NR;
-    constexpr int kColsHost = ((L == 1 ? 3 : 2) * ISS * NP <= 128) ? 128 : ((L == 1 ? 3 : 2) * ISS * NP <= 256) ? 256 : 512;
+    constexpr int kColsHost = attn_tmem_cols(L, ISS, WS);
     const int tile_cap = (q->max_pages * q->page_size + kTileKeys - 1) / kTileKeys;
     int tiles_max = tile_cap;
     if (q->window > 0) tiles_max = min(tiles_max, q->window / kTileKeys + 2);
@@ -614,8 +921,9 @@ int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
     // the ring needs 3 slots: a tile's slot is refilled one iteration after its tile (finish_tile runs late),
     // and the next tile's scores are issued one iteration early
     if (q->stages != 0 && (q->stages < 3 || q->stages > kAttnMaxStages)) return MSK_ERR_INVALID;
-    const int nst = q->stages > 0 ? q->stages : 3;
-    const int smem = 1024 + nst * kStageBytes + 2 * NP * 128 + NR * 128 * 4;
+    int nst = q->stages > 0 ? q->stages : 3;
+    int smem = 1024 + nst * kStageBytes + (WS ? 3 : 2) * NP * 128 + NR * 128 * 4;
+    if (smem > 232448) return MSK_ERR_INVALID;
     int resident = min(232448 / (smem + 2048), 512 / kColsHost);  // CTAs per SM: shared memory, tensor memory
     if (resident < 1) resident = 1;
     int C = q->chunks;
@@ -624,11 +932,18 @@ int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
         if (want > tiles_max) want = tiles_max;
         C = 1;
         while (2 * C <= want && C < 8) C *= 2;
-        // plenty of (request, head) pairs but long, uneven contexts: halves balance the last wave better
-        if (C == 1 && tiles_max >= 32) C = 2;
+        // more (request, head) pairs than CTA slots but fewer than two waves of them, and long contexts: halves
+        // balance the last wave better; with several waves (longest first) whole contexts have less fixed cost
+        if (C == 1 && tiles_max >= 32 && q->B * q->Hkv < 2 * resident * 148) C = 2;
+        while ((tiles_max + C - 1) / C > kMaxTilesPerCta && C < 8) C *= 2;
     }
     if (C != 1 && C != 2 && C != 4 && C != 8) return MSK_ERR_INVALID;
     if ((tiles_max + C - 1) / C > kMaxTilesPerCta) return MSK_ERR_UNSUPPORTED;
+    // a grid of at most one CTA per SM is bound by the latency of its own copies: give it a deeper ring
+    if (WS && q->stages == 0 && q->B * q->Hkv * C <= 148) {
+        nst = kAttnMaxStages;
+        smem = 1024 + nst * kStageBytes + 3 * NP * 128 + NR * 128 * 4;
+    }
 
     CUtensorMap tm_k, tm_v;
     const uint64_t dims[4] = {128, static_cast<uint64_t>(q->Hkv), static_cast<uint64_t>(q->page_size),
@@ -661,13 +976,13 @@ int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MSK_ERR_CUDA;
     static int configured[64] = {};  // per device, like the attribute itself
     if (smem > configured[dev]) {
-        if (cudaFuncSetAttribute(attn_kernel<L, ISS, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(attn_kernel<L, ISS, RG, WS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return MSK_ERR_CUDA;
         configured[dev] = smem;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(C, q->Hkv, q->B);
-    cfg.blockDim = dim3(128 * RG, 1, 1);
+    cfg.blockDim = dim3(128 * RG + (WS ? 64 : 0), 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attrs[2];
@@ -684,7 +999,7 @@ int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
     }
     cfg.attrs = attrs;
     cfg.numAttrs = na;
-    return cudaLaunchKernelEx(&cfg, attn_kernel<L, ISS, RG>, tm_k, tm_v, a) == cudaSuccess ? 0 : MSK_ERR_CUDA;
+    return cudaLaunchKernelEx(&cfg, attn_kernel<L, ISS, RG, WS>, tm_k, tm_v, a) == cudaSuccess ? 0 : MSK_ERR_CUDA;
 }
 
 }  // namespace msk
@@ -696,13 +1011,13 @@ extern "C" int msk_attn_decode(const MskAttnParams* q, int* status, void* stream
         return MSK_ERR_INVALID;
     if (q->d != 128 || q->Hkv < 1 || q->Hq != 8 * q->Hkv || q->B < 1) return MSK_ERR_UNSUPPORTED;
     if (q->page_size < 8 || q->page_size > 128 || (q->page_size & (q->page_size - 1)) != 0) return MSK_ERR_UNSUPPORTED;
-    if (q->issuers != 0 && q->issuers != 2 && q->issuers != 4) return MSK_ERR_INVALID;
-    // decode: two issuing warps (128 tensor-memory columns) measured a little faster than four
-    if (q->row_groups != 0 && q->row_groups != 1 && q->row_groups != 2) return MSK_ERR_INVALID;
+    if (q->issuers != 0 && q->issuers != 1 && q->issuers != 2) return MSK_ERR_INVALID;
+    if (q->row_groups != 0 && q->row_groups != 2) return MSK_ERR_INVALID;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (q->L == 1 && q->issuers == 4) return launch_attn<1, 4, 1>(q, status, s);
-    if (q->L == 1 && q->row_groups == 1) return launch_attn<1, 2, 1>(q, status, s);
-    if (q->L == 1) return launch_attn<1, 2, 2>(q, status, s);
-    if (q->L == 8) return launch_attn<8, 2, 4>(q, status, s);
+    // decode: a copying warp and an MMA warp beside the eight arithmetic warps; issuers = 2 selects the form in which
+    // two of the arithmetic warps issue everything themselves (a quarter slower on long contexts, kept for comparison)
+    if (q->L == 1 && q->issuers == 2) return launch_attn<1, 2, 2, false>(q, status, s);
+    if (q->L == 1) return launch_attn<1, 1, 2, true>(q, status, s);
+    if (q->L == 8) return launch_attn<8, 2, 4, false>(q, status, s);
     return MSK_ERR_UNSUPPORTED;
 }

@@ -67,6 +67,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Named CTA barrier over `count` threads (a multiple of 32; ids 1..15, id 0 is __syncthreads): a subset of the
+// CTA's warps meets without the others.
+template <int ID>
+__device__ __forceinline__ void named_bar_sync(uint32_t count) {
+    static_assert(ID >= 1 && ID <= 15, "barrier 0 is __syncthreads");
+    asm volatile("bar.sync %0, %1;" ::"n"(ID), "r"(count) : "memory");
+}
+// Arrive at a named barrier without waiting for it (the whole warp executes this; `count` as in named_bar_sync).
+template <int ID>
+__device__ __forceinline__ void named_bar_arrive(uint32_t count) {
+    static_assert(ID >= 1 && ID <= 15, "barrier 0 is __syncthreads");
+    asm volatile("bar.arrive %0, %1;" ::"n"(ID), "r"(count) : "memory");
+}
 // Wait budget for any single wait, in SM clock cycles (about half a second).  Legitimate waits
 // here last microseconds.
 constexpr long long kWaitBudgetCycles = 1000ll * 1000 * 1000;
