@@ -68,6 +68,7 @@ struct RouterArgs {
     int T, H, E;
     int sigmoid_bias;       // 0: softmax over logits + bias; 1: sigmoid(multiplier * logit), chosen by score + bias
     float multiplier;
+    int phases;             // 128-k tiles a block walks: H = gridDim.x * phases * 128
 };
 
 constexpr int kRouterK = 128;   // k per block (one load phase)
@@ -79,50 +80,59 @@ __global__ void __launch_bounds__(256) router_kernel(RouterArgs p) {
     __shared__ __align__(16) float hs[kRouterT][kRouterK];
     __shared__ int last;
     const int ks = blockIdx.x, et = blockIdx.y, tid = threadIdx.x;
-    const int KS = gridDim.x;  // K splits = H / 128
-    const int e0 = et * kRouterE, kb = ks * kRouterK;
+    const int KS = gridDim.x;  // K splits = H / (128 * phases)
+    const int e0 = et * kRouterE, kb = ks * kRouterK * p.phases;
     const int ne = min(kRouterE, p.E - e0), n_tg = (p.T + kRouterT - 1) / kRouterT;
     const int tw = tid >> 5, el = tid & 31;  // warp w owns tokens w, w+8, w+16, w+24; lane = expert
     // both tiles are 32 rows x 32 float4; thread -> rows tw, tw+8, tw+16, tw+24, float4 column el.  All four loads
     // are issued before the first use; rows past the end re-read the last valid row and are zeroed.
-    {
-        float4 r[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j)  // router weights do not depend on the previous kernel
-            r[j] = __ldg(reinterpret_cast<const float4*>(p.R + static_cast<size_t>(e0 + min(tw + 8 * j, ne - 1)) * p.H + kb) + el);
+    // the first tile of router weights does not depend on the previous kernel: requested before the wait
+    auto load_r = [&](int k0, float4 (&r)[4]) {
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-            *reinterpret_cast<float4*>(&Rs[tw + 8 * j][4 * el]) = tw + 8 * j < ne ? r[j] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    }
-    const uint2 wraw = __ldg(reinterpret_cast<const uint2*>(p.w + kb) + el);
-    const float w0 = 1.0f + bf16lo(wraw.x), w1 = 1.0f + bf16hi(wraw.x), w2 = 1.0f + bf16lo(wraw.y), w3 = 1.0f + bf16hi(wraw.y);
+            r[j] = __ldg(reinterpret_cast<const float4*>(p.R + static_cast<size_t>(e0 + min(tw + 8 * j, ne - 1)) * p.H + k0) + el);
+    };
+    float4 r_first[4];
+    load_r(kb, r_first);
     pdl_wait();
     pdl_launch_dependents();
-    // a block keeps its tile of router weights for several token groups (the grid stays within one wave of CTAs)
+    // With many token groups a block walks `phases` tiles of 128 k: fewer, longer blocks (the grid stays within one
+    // wave of CTAs) and fewer partials for the chain of global round trips at the end.
     for (int tg = blockIdx.z; tg < n_tg; tg += gridDim.z) {
     const int t0 = tg * kRouterT, nt = min(kRouterT, p.T - t0);
-    __syncthreads();  // the previous group's use of hs and `last` is over
-    {
-        float4 h[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-            h[j] = __ldcg(reinterpret_cast<const float4*>(p.s1 + static_cast<size_t>(t0 + min(tw + 8 * j, nt - 1)) * p.H + kb) + el);
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-            *reinterpret_cast<float4*>(&hs[tw + 8 * j][4 * el]) =
-                tw + 8 * j < nt ? make_float4(h[j].x * w0, h[j].y * w1, h[j].z * w2, h[j].w * w3) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    }
-    __syncthreads();
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll 8
-    for (int k4 = 0; k4 < kRouterK / 4; ++k4) {
-        const float4 r = *reinterpret_cast<const float4*>(&Rs[el][4 * k4]);
+    for (int ph = 0; ph < p.phases; ++ph) {
+        const int k0 = kb + ph * kRouterK;
+        float4 r[4], h[4];
+        if (ph == 0) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) r[j] = r_first[j];
+        } else {
+            load_r(k0, r);
+        }
+        const uint2 wraw = __ldg(reinterpret_cast<const uint2*>(p.w + k0) + el);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            h[j] = __ldcg(reinterpret_cast<const float4*>(p.s1 + static_cast<size_t>(t0 + min(tw + 8 * j, nt - 1)) * p.H + k0) + el);
+        const float w0 = 1.0f + bf16lo(wraw.x), w1 = 1.0f + bf16hi(wraw.x), w2 = 1.0f + bf16lo(wraw.y), w3 = 1.0f + bf16hi(wraw.y);
+        __syncthreads();  // the previous tile's (or group's) use of Rs, hs and `last` is over
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            if (tw + 8 * j >= nt) break;  // warp-uniform
-            const float4 h = *reinterpret_cast<const float4*>(&hs[tw + 8 * j][4 * k4]);
-            acc[j] = fmaf(h.x, r.x, acc[j]), acc[j] = fmaf(h.y, r.y, acc[j]);
-            acc[j] = fmaf(h.z, r.z, acc[j]), acc[j] = fmaf(h.w, r.w, acc[j]);
+            *reinterpret_cast<float4*>(&Rs[tw + 8 * j][4 * el]) = tw + 8 * j < ne ? r[j] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            *reinterpret_cast<float4*>(&hs[tw + 8 * j][4 * el]) =
+                tw + 8 * j < nt ? make_float4(h[j].x * w0, h[j].y * w1, h[j].z * w2, h[j].w * w3) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int k4 = 0; k4 < kRouterK / 4; ++k4) {
+            const float4 rr = *reinterpret_cast<const float4*>(&Rs[el][4 * k4]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (tw + 8 * j >= nt) break;  // warp-uniform
+                const float4 hh = *reinterpret_cast<const float4*>(&hs[tw + 8 * j][4 * k4]);
+                acc[j] = fmaf(hh.x, rr.x, acc[j]), acc[j] = fmaf(hh.y, rr.y, acc[j]);
+                acc[j] = fmaf(hh.z, rr.z, acc[j]), acc[j] = fmaf(hh.w, rr.w, acc[j]);
+            }
         }
     }
 #pragma unroll
@@ -395,8 +405,11 @@ extern "C" int msk_router(const MskRouterParams* q, int* status, void* stream) {
     r.part = q->part, r.ticket = q->ticket, r.logits = q->logits, r.T = q->T, r.H = q->H, r.E = q->E;
     r.top_k = q->top_k, r.ids_out = q->topk_ids, r.wts_out = q->topk_weights;
     r.sigmoid_bias = q->sigmoid_bias, r.multiplier = q->multiplier;
-    const int ks = q->H / kRouterK;  // <= 64
     const int et = (q->E + kRouterE - 1) / kRouterE, n_tg = (q->T + kRouterT - 1) / kRouterT;
+    // few tokens: as many K splits as there are 128-k tiles (the 2 MB of router weights spread over the SMs);
+    // four token groups or more: blocks of four tiles (the K-split count must stay a multiple of 8)
+    r.phases = (n_tg >= 4 && (q->H / kRouterK) % 32 == 0) ? 4 : 1;
+    const int ks = q->H / (kRouterK * r.phases);  // <= 64
     // one block per token group: letting a block walk several groups so that the grid stays within one wave of
     // CTAs measured slower (each group is a chain of global round trips; 55 against 45 us at 256 tokens)
     return launch1(router_kernel, dim3(ks, et, n_tg), dim3(256), 0, static_cast<cudaStream_t>(stream), q->pdl, r);
