@@ -111,9 +111,9 @@ typedef struct {
     float qk_scale_factor, sm_scale;
     int chunks;               /* split-KV ways = cluster size (1, 2, 4 or 8); 0 = pick */
     int stages;               /* K/V tile ring depth (3 to 6); 0 = pick: 3, or 6 when the grid is at most one CTA per SM */
-    int issuers;              /* decode: 1 = a separate MMA warp and a separate copying warp (the default), 2 = two of the arithmetic warps issue; 0 = pick */
+    int issuers;              /* MMA-issuing warps beside the arithmetic warps: 1; 0 = pick */
     int pdl;
-    int row_groups;           /* decode: sets of four warps that split the 8 query rows of a KV head: 2; 0 = pick */
+    int row_groups;           /* sets of four arithmetic warps that split the 8 L query rows of a KV head: 2 (decode), 4 (verify); 0 = pick */
 } MskAttnParams;
 
 int msk_attn_decode(const MskAttnParams* p, int* status, void* stream);

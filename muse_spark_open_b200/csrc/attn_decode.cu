@@ -3,14 +3,17 @@
 // Grid (chunks C, KV heads, requests); the C CTAs of one (request, KV head) form a thread block
 // cluster and split that request's cached keys between them (split-KV).
 // Decode CTA: 320 threads = eight arithmetic warps (two row groups of four: one warp per 32-key quarter of a tile,
-// a row group per four query rows), one MMA warp and one copying warp, two CTAs per SM.  The two extra warps do
+// a row group per four query rows), one MMA warp and one copying warp, two CTAs per SM; verify CTA: 576 threads =
+// sixteen arithmetic warps (four row groups of 16 rows) and the same two, one CTA per SM.  The two extra warps do
 // nothing but issue (both MMAs of every tile / the TMA copies) and meet the others only through mbarriers; the K
 // half and the V half of a ring slot are refilled the moment the MMA that read them has finished, so each copy has
-// about two tiles' time to land; P and the output accumulator are double-buffered, so a tile's second MMA has a
-// whole iteration before its result is folded in; the arithmetic warps are left with one named barrier per tile.
-// (Timestamps showed why: with two arithmetic warps issuing, a tile cost 4200 clocks per CTA, 1200 of them the
-// wait for a copy that had been issued a moment before it was needed and 1400 the issuing itself, on the path
-// of all eight warps; now 2200, against 2900 for two CTAs per SM at the copy bandwidth.)
+// about two tiles' time to land; score buffers, P and the output accumulator are double-buffered, so a tile's
+// second MMA has a whole iteration before its result is folded in; the arithmetic warps are left with one (decode)
+// or two (verify) named barriers per tile, each over the four warps of a row group.
+// (Timestamps showed why: with two arithmetic warps issuing, a decode tile cost 4200 clocks per CTA, 1200 of them
+// the wait for a copy that had been issued a moment before it was needed and 1400 the issuing itself, on the path
+// of all eight warps; now 2200, against 2900 for two CTAs per SM at the copy bandwidth.  Verify is bound by the
+// arithmetic warps' instruction issue: ~25 instructions per (key, row) element.)
 //
 // Per 128-key tile (two 64-token pages, or 128 / page_size pages):
 //   TMA      4-D boxes [page_size tokens x 128 B] of K and of V land in shared memory with the
@@ -24,19 +27,16 @@
 //   softmax  thread = key: tcgen05.ld its row of S^T, scale, window / causal mask, running maximum
 //            per query row (redux.sync over the warp, shared memory over the 4 warps), p = 2^(s-m)
 //            split into two E4M3 terms the same way, written as the K-major B operand P[row, key].
-//            A single thread can issue only about one tcgen05.mma per 100 clocks whatever N is; in the verify form
-//            two warps issue, each into its own accumulator columns, summed when read.
 //   MMA 2    O^T[d, row] = V^T[d, key] . P[row, key]; V stays as stored (MN-major A operand).
 //   acc      thread = d: o[row] = o[row] * alpha[row] + O^T[d, row]  (FP32 registers).
 // The L new tokens never travel through global memory: the last CTA of the cluster applies
 // RMSNorm + RoPE to the new keys, quantises keys and values to E4M3, writes them to the cache
 // rows `cache_loc` and attends them from registers / shared memory in FP32 (decode: before the tile loop, with
 // the loads of the query rows, so that nothing but the fold-in is left for the end; verify: after the loop).
-// Verify blocks (64 query rows per KV head) run the same tile loop with 512 threads: four row groups of 16 rows,
-// each a full set of four warps (one per 32-key quarter of the tile), so that a thread's serial work per tile is
-// 16 rows, four warps share every scheduler and the instruction latencies overlap (with one warp per scheduler the
-// 64-row loop ran ten times longer per tile than decode's 8 rows); the next tile's scores are issued as soon as
-// this tile's have been read into registers.
+// Verify blocks (64 query rows per KV head) run the same tile loop with four row groups of 16 rows, each a full set
+// of four warps (one per 32-key quarter of the tile), so that a thread's serial work per tile is 16 rows and several
+// warps share every scheduler (with one warp per scheduler the 64-row loop ran ten times longer per tile than
+// decode's 8 rows).
 // Merge: every CTA pushes its (m, l, o) partials for the query rows another CTA owns into that
 // CTA's shared memory (DSMEM), one cluster barrier, then each owner merges, applies the per-head
 // RMSNorm and the sigmoid gate and stores BF16.
@@ -130,35 +130,30 @@ __device__ __forceinline__ void tmem_ld_rows(uint32_t taddr, uint32_t (&r)[BR]) 
     else tmem_ld4(taddr, r);
 }
 
-// L: tokens per request (1 decode, 8 verify); ISS: MMA-issuing warps (one thread issues only ~1 MMA per 100
-// clocks); RG: row groups = sets of four warps (one per 32-key quarter of a tile) that split the 8 L query rows.
-// WS (decode): two more warps do nothing but issue -- one the TMA copies, one both MMAs of every tile -- and meet the
-// others only through mbarriers.  The arithmetic warps then have one named barrier per tile (the row maxima of
-// their row group) instead of two CTA-wide ones behind a warp that also issues; P and the output accumulator are
-// double-buffered so that a tile's second MMA has a whole iteration to finish before anyone needs its result.
-__host__ __device__ constexpr uint32_t attn_tmem_cols(int L, int ISS, bool WS) {
-    const int cols = ((L == 1 ? 2 : 1) + (WS ? 2 : 1)) * (WS ? 1 : ISS) * 16 * L;
-    return cols <= 64 ? 64 : cols <= 128 ? 128 : cols <= 256 ? 256 : 512;
+// L: tokens per request (1 decode, 8 verify); RG: row groups = sets of four arithmetic warps (one warp per 32-key
+// quarter of a tile) that split the 8 L query rows.  Two more warps do nothing but issue -- one the TMA copies, one
+// both MMAs of every tile -- and meet the others only through mbarriers; score buffers, P tiles and output
+// accumulators are double-buffered, so a tile's second MMA has a whole iteration before its result is folded in.
+__host__ __device__ constexpr uint32_t attn_tmem_cols(int L) {  // two score and two output buffers of 16 L columns
+    return 64 * L <= 64 ? 64 : 64 * L <= 128 ? 128 : 64 * L <= 256 ? 256 : 512;
 }
 
-template <int L, int ISS_, int RG, bool WS>
-__global__ void __launch_bounds__(128 * RG + (WS ? 64 : 0), (L == 1 && RG <= 2) ? 2 : 1)
+template <int L, int RG>
+__global__ void __launch_bounds__(128 * RG + 64, (L == 1 && RG <= 2) ? 2 : 1)
     attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, AttnArgs p) {
-    static_assert(!WS || L == 1, "the issuing warp exists in the decode form only");
-    constexpr int ISS = WS ? 1 : ISS_;        // accumulators per MMA (one per issuing thread)
     constexpr int NR = 8 * L;                 // query rows per KV head
     constexpr int NTHR_C = 128 * RG, NWARP_C = NTHR_C / 32;  // arithmetic threads / warps
-    constexpr int NTHR = NTHR_C + (WS ? 64 : 0), NWARP = NTHR / 32;
+    constexpr int NTHR = NTHR_C + 64, NWARP = NTHR / 32;  // + the MMA warp and the copying warp
     constexpr int NRG = NR / RG;              // query rows per row group: a thread's serial work per tile
     constexpr int BR = NRG < 8 ? NRG : 8;     // rows per tensor-memory round trip
     static_assert(NRG % BR == 0 && (BR == 4 || BR == 8), "row groups work on blocks of 4 or 8 rows");
     constexpr int NP = 2 * NR;                // UMMA N: rows [0, NR) hold the first split term, [NR, 2 NR) the second
-    constexpr int SBUF = L == 1 ? 2 : 1;      // score buffers in TMEM (2: the next tile's scores are computed ahead)
-    constexpr int PBUF = WS ? 2 : 1;          // P tiles in shared memory and output accumulators in TMEM
-    // SBUF * ISS * NP score columns, then PBUF * ISS * NP output columns, as a power of two
-    constexpr uint32_t kCols = attn_tmem_cols(L, ISS_, WS);
-    static_assert((SBUF + PBUF) * ISS * NP <= kCols, "tensor-memory columns");
-    constexpr uint32_t kOCol = SBUF * ISS * NP;
+    constexpr int SBUF = 2;                   // score buffers in TMEM: the next tile's scores are computed ahead
+    constexpr int PBUF = 2;                   // P tiles in shared memory and output accumulators in TMEM
+    // SBUF * NP score columns, then PBUF * NP output columns, as a power of two
+    constexpr uint32_t kCols = attn_tmem_cols(L);
+    static_assert((SBUF + PBUF) * NP <= kCols, "tensor-memory columns");
+    constexpr uint32_t kOCol = SBUF * NP;
     constexpr int QP_BYTES = NP * 128;
     constexpr float kLoScale = 16.0f;         // the second split term is stored times 16 (keeps small residuals in range)
 
@@ -166,9 +161,9 @@ __global__ void __launch_bounds__(128 * RG + (WS ? 64 : 0), (L == 1 && RG <= 2) 
     __shared__ __align__(8) uint64_t bars[4 * kAttnMaxStages + 2];
     __shared__ uint32_t tmem_slot;
     __shared__ int page_ids[kMaxTilesPerCta * 2];
-    __shared__ __align__(16) float wred_s[PBUF][4][NR];  // per-warp maxima of the current tile (WS: alternating)
+    __shared__ __align__(16) float wred_s[PBUF][4][NR];  // per-warp maxima of a tile (alternating buffers)
     auto& wred = wred_s[0];
-    __shared__ float m_s[NR], alpha_s[NR], mrg_m[NR], mrg_l[NR];
+    __shared__ float m_s[NR], alpha_s[PBUF][NR], mrg_m[NR], mrg_l[NR];
     __shared__ float sc_tail[NR][L];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -205,34 +200,25 @@ __global__ void __launch_bounds__(128 * RG + (WS ? 64 : 0), (L == 1 && RG <= 2) 
     uint8_t* g_q = gbase + nst * kStageBytes;
     uint8_t* g_p = g_q + QP_BYTES;
     float* mrg_o = reinterpret_cast<float*>(g_q + (1 + PBUF) * QP_BYTES);  // [NR][128]
-    // Barriers.  Without the issuing warps: full(s) = both halves of ring slot s landed; bar_s0 / bar_s1 = scores of an
-    // even / odd tile exist; bar_o = a tile's output product exists.  WS form: the K half and the V half of a slot fill
-    // and drain on their own (full / full_v), and "scores exist" (sdone) and "output product exists" (odone) are kept
-    // per ring slot, because the copying warp waits on them too, to refill the half they free: a barrier per slot
-    // cannot complete twice before that warp has looked, since the next tile of the slot needs the refill itself.
+    // Barriers.  The K half and the V half of a ring slot fill and drain on their own (full / full_v); "scores exist"
+    // (sdone) and "output product exists" (odone) are kept per ring slot, because the copying warp waits on them too,
+    // to refill the half they free: a barrier per slot cannot complete twice before that warp has looked, since the
+    // next tile of the slot needs the refill itself.
     auto full = [&](int s) { return smem_u32(&bars[s]); };
     auto full_v = [&](int s) { return smem_u32(&bars[kAttnMaxStages + s]); };
     auto sdone = [&](int s) { return smem_u32(&bars[2 * kAttnMaxStages + s]); };
     auto odone = [&](int s) { return smem_u32(&bars[3 * kAttnMaxStages + s]); };
-    auto pready = [&](int i) { return smem_u32(&bars[4 * kAttnMaxStages + (i & 1)]); };  // WS: P of tile i written
-    const uint32_t bar_s0 = sdone(0), bar_s1 = sdone(1), bar_o = odone(0);
+    auto pready = [&](int i) { return smem_u32(&bars[4 * kAttnMaxStages + (i & 1)]); };  // P of tile i written
 
     // ---------------- set-up that does not depend on the previous kernel
     if (warp == 0) {
         tmem_alloc(smem_u32(&tmem_slot), kCols);
         tmem_relinquish();
     }
-    if (tid == (WS ? NTHR_C + 32 : 32)) {  // WS: the copying thread, which goes on to start the first copies itself
-        for (int s = 0; s < nst; ++s) mbar_init(full(s), 1);
-        if constexpr (WS) {
-            for (int s = 0; s < nst; ++s) mbar_init(full_v(s), 1), mbar_init(sdone(s), 1), mbar_init(odone(s), 1);
-            mbar_init(pready(0), NWARP_C);
-            mbar_init(pready(1), NWARP_C);
-        } else {
-            mbar_init(bar_s0, ISS);
-            mbar_init(bar_s1, ISS);
-            mbar_init(bar_o, ISS);
-        }
+    if (tid == NTHR_C + 32) {  // the copying thread, which goes on to start the first copies itself
+        for (int s = 0; s < nst; ++s) mbar_init(full(s), 1), mbar_init(full_v(s), 1), mbar_init(sdone(s), 1), mbar_init(odone(s), 1);
+        mbar_init(pready(0), NWARP_C);
+        mbar_init(pready(1), NWARP_C);
         fence_mbar_init();
     }
     const int seq = p.seq_lens[b];
@@ -249,12 +235,12 @@ __global__ void __launch_bounds__(128 * RG + (WS ? 64 : 0), (L == 1 && RG <= 2) 
         nt = kMaxTilesPerCta;
     }
     const int ppt = kTileKeys / p.page_size;  // pages per tile
-    // WS: the copying warp only arrives at the CTA's first barrier (it made the mbarriers, the others wait for them
+    // The copying warp only arrives at the CTA's first barrier (it made the mbarriers, the others wait for them
     // there) and takes no part in the fills below; its thread fetches the page ids of the first tile itself and
     // starts that copy at once instead of waiting for the shared table.
-    constexpr int NTHR_F = WS ? NTHR_C + 32 : NTHR;  // threads that fill shared memory before the first barrier
-    int started = 0;                                 // tiles whose copies are under way
-    if constexpr (WS) {
+    constexpr int NTHR_F = NTHR_C + 32;  // threads that fill shared memory before the first barrier
+    int started = 0;                     // tiles whose copies are under way
+    {
         if (warp == NWARP_C + 1) {
             __syncwarp();
             named_bar_arrive<4>(NTHR);
@@ -295,71 +281,55 @@ __global__ void __launch_bounds__(128 * RG + (WS ? 64 : 0), (L == 1 && RG <= 2) 
         reinterpret_cast<uint4*>(g_q)[i] = make_uint4(0, 0, 0, 0);
     if (tid < NR) m_s[tid] = kNeg;
     tc_fence_before();
-    if constexpr (WS) {
-        // barrier 5: the table and the zeroed operands exist (the copying warp waits for this one, the others only
-        // arrive); barrier 4: the mbarriers and the tensor-memory address exist (the other way round)
-        if (warp == NWARP_C + 1) {
-            named_bar_sync<5>(NTHR);
-        } else {
-            named_bar_arrive<5>(NTHR);
-            named_bar_sync<4>(NTHR);
-        }
+    // barrier 5: the table and the zeroed operands exist (the copying warp waits for this one, the others only
+    // arrive); barrier 4: the mbarriers and the tensor-memory address exist (the other way round)
+    if (warp == NWARP_C + 1) {
+        named_bar_sync<5>(NTHR);
     } else {
-        __syncthreads();
+        named_bar_arrive<5>(NTHR);
+        named_bar_sync<4>(NTHR);
     }
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
     pdl_launch_dependents();
 
-    auto issue_tile = [&](int i, int s) {  // one thread: TMA for this CTA's tile i into ring slot s = i % nst
-        const uint32_t kb = base + s * kStageBytes, vb = kb + kTileKeys * 128;
-        mbar_expect_tx(full(s), kStageBytes);
-        for (int j = 0; j < ppt; ++j) {
-            const int id = page_ids[i * ppt + j];
-            tma_load_4d(kb + j * p.page_size * 128, &tm_k, full(s), 0, h, 0, id);
-            tma_load_4d(vb + j * p.page_size * 128, &tm_v, full(s), 0, h, 0, id);
-        }
-    };
-    auto issue_half = [&](int i, int s, bool values) {  // WS: the keys or the values of tile i into their half of slot s
+    auto issue_half = [&](int i, int s, bool values) {  // one thread: the keys or the values of tile i into their half of slot s
         const uint32_t dst = base + s * kStageBytes + (values ? kTileKeys * 128 : 0);
         const uint32_t bar = values ? full_v(s) : full(s);
         mbar_expect_tx(bar, kTileKeys * 128);
         for (int j = 0; j < ppt; ++j)
             tma_load_4d(dst + j * p.page_size * 128, values ? &tm_v : &tm_k, bar, 0, h, 0, page_ids[i * ppt + j]);
     };
-    const bool issuer = !WS && lane == 0 && warp < ISS;
-    const int acc = WS ? 0 : warp;  // the accumulator an issuing thread owns
-    auto sbar = [&](int i) { return (SBUF == 2 && (i & 1)) ? bar_s1 : bar_s0; };
-    // `slot`: ring slot of tile i (i % nst; the issuing warp of the WS form counts it instead of dividing)
-    auto issue_mma1 = [&](int i, int slot, uint32_t done) {  // issuing thread w: S_w^T = K[:, its k-steps] . q^T, score buffer i % SBUF
+    // `slot`: ring slot of tile i (i % nst; the roles count it instead of dividing)
+    auto issue_mma1 = [&](int i, int slot, uint32_t done) {  // S^T = K . q^T into score buffer i & 1
         const uint32_t kb = base + slot * kStageBytes;
         const uint32_t idesc = umma_idesc(128, NP, 0, 0, 0, 0);
         const uint64_t ad = umma_smem_desc(kb, 16, 1024, kSwizzle128);
         const uint64_t bq = umma_smem_desc(s_q, 16, 1024, kSwizzle128);
-        const uint32_t d = tmem + ((i % SBUF) * ISS + acc) * NP;
+        const uint32_t d = tmem + (i & 1) * NP;
 #pragma unroll
-        for (int k = acc; k < 4; k += ISS) umma_f8_ss(d, ad + 2 * k, bq + 2 * k, idesc, k != acc);
+        for (int k = 0; k < 4; ++k) umma_f8_ss(d, ad + 2 * k, bq + 2 * k, idesc, k != 0);
         umma_commit(done);
     };
-    auto issue_mma2 = [&](int i, int slot, uint32_t done) {  // issuing thread w: O_w^T = V^T[:, its 32-key steps] . P^T
+    auto issue_mma2 = [&](int i, int slot, uint32_t done) {  // O^T = V^T . P^T from P buffer i & 1 into output buffer i & 1
         const uint32_t vb = base + slot * kStageBytes + kTileKeys * 128;
         const uint32_t idesc = umma_idesc(128, NP, 0, 0, 1, 0);
-        const uint64_t bp = umma_smem_desc(s_p + (WS ? (i & 1) * QP_BYTES : 0), 16, 1024, kSwizzle128);
-        const uint32_t d = tmem + kOCol + (WS ? (i & 1) : acc) * NP;
+        const uint64_t bp = umma_smem_desc(s_p + (i & 1) * QP_BYTES, 16, 1024, kSwizzle128);
+        const uint32_t d = tmem + kOCol + (i & 1) * NP;
         const uint64_t av = umma_smem_desc(vb, 1024, 1024, kSwizzle128);
 #pragma unroll
-        for (int k = acc; k < 4; k += ISS) umma_f8_ss(d, av + (4096 >> 4) * k, bp + 2 * k, idesc, k != acc);
+        for (int k = 0; k < 4; ++k) umma_f8_ss(d, av + (4096 >> 4) * k, bp + 2 * k, idesc, k != 0);
         umma_commit(done);
     };
 
-    if (tid == (WS ? NTHR_C + 32 : 0)) {
+    if (tid == NTHR_C + 32) {
         if (started == 0) {
             prefetch_tmap(&tm_k);
             prefetch_tmap(&tm_v);
         }
         for (int i = started; i < nt && i < nst; ++i) {
-            if constexpr (WS) issue_half(i, i, false), issue_half(i, i, true);
-            else issue_tile(i, i);
+            issue_half(i, i, false);
+            issue_half(i, i, true);
         }
     }
 
@@ -462,56 +432,40 @@ __global__ void __launch_bounds__(128 * RG + (WS ? 64 : 0), (L == 1 && RG <= 2) 
 #pragma unroll
     for (int g = 0; g < (L == 1 ? NRG : 1); ++g) m_r[g] = kNeg, alpha_r[g] = 1.0f;
 
-    // scores of 8 query rows (c0 .. c0+7) for this thread's key: both split terms, all issuing warps' partials
-    // scores of BR query rows (c0 .. c0+BR-1) for this thread's key: both split terms, all issuing warps' partials
+    // scores of BR query rows (c0 .. c0+BR-1) for this thread's key: both split terms
     auto load_scores = [&](int i, int c0, float (&sc)[BR]) {
-        uint32_t hi[ISS][BR], lo[ISS][BR];
-#pragma unroll
-        for (int w = 0; w < ISS; ++w) {
-            const uint32_t col = trow + ((i % SBUF) * ISS + w) * NP + c0;
-            tmem_ld_rows<BR>(col, hi[w]);
-            tmem_ld_rows<BR>(col + NR, lo[w]);
-        }
+        uint32_t hi[BR], lo[BR];
+        const uint32_t col = trow + (i & 1) * NP + c0;
+        tmem_ld_rows<BR>(col, hi);
+        tmem_ld_rows<BR>(col + NR, lo);
         tmem_wait_ld();
 #pragma unroll
-        for (int g = 0; g < BR; ++g) {
-            float a = 0.0f, b = 0.0f;
-#pragma unroll
-            for (int w = 0; w < ISS; ++w) a += __uint_as_float(hi[w][g]), b += __uint_as_float(lo[w][g]);
-            sc[g] = a + b * (1.0f / kLoScale);
-        }
+        for (int g = 0; g < BR; ++g) sc[g] = __uint_as_float(hi[g]) + __uint_as_float(lo[g]) * (1.0f / kLoScale);
     };
-    // second half of a tile's work: wait for O^T = V^T . P^T, fold it into the running output, refill the ring
-    // slot.  It runs one iteration late (after the next tile's maxima), so the MMA's latency is hidden.
-    // (WS: two iterations' worth late, from the accumulator j & 1, with the rescale factors of tile j in `al_j`.)
+    // second half of a tile's work: wait for O^T = V^T . P^T (output buffer j & 1) and fold it into the running
+    // output with tile j's rescale factors (decode: `al_j`).  It runs at the end of the next iteration, so the MMA
+    // has had a whole iteration to finish.
     auto finish_tile = [&](int j, const float* al_j, uint32_t done, int parity) {
         ok = mbar_wait(done, parity, p.status, where | 6) && ok;
         tc_fence_after();
 #pragma unroll
         for (int c0 = 0; c0 < NRG; c0 += BR) {
-            uint32_t hi[ISS][BR], lo[ISS][BR];
-#pragma unroll
-            for (int w = 0; w < ISS; ++w) {
-                const uint32_t col = trow + kOCol + (WS ? (j & 1) : w) * NP + r_lo + c0;
-                tmem_ld_rows<BR>(col, hi[w]);
-                tmem_ld_rows<BR>(col + NR, lo[w]);
-            }
+            uint32_t hi[BR], lo[BR];
+            const uint32_t col = trow + kOCol + (j & 1) * NP + r_lo + c0;
+            tmem_ld_rows<BR>(col, hi);
+            tmem_ld_rows<BR>(col + NR, lo);
             tmem_wait_ld();
 #pragma unroll
             for (int g = 0; g < BR; ++g) {
-                float a = 0.0f, b = 0.0f;
-#pragma unroll
-                for (int w = 0; w < ISS; ++w) a += __uint_as_float(hi[w][g]), b += __uint_as_float(lo[w][g]);
-                const float al = L == 1 ? al_j[c0 + g] : alpha_s[r_lo + c0 + g];
-                o_acc[c0 + g] = o_acc[c0 + g] * al + (a + b * (1.0f / kLoScale));
+                const float al = L == 1 ? al_j[c0 + g] : alpha_s[j & 1][r_lo + c0 + g];
+                o_acc[c0 + g] = o_acc[c0 + g] * al + (__uint_as_float(hi[g]) + __uint_as_float(lo[g]) * (1.0f / kLoScale));
             }
         }
         tc_fence_before();
-        if (!WS && tid == 0 && ok && j + nst < nt) issue_tile(j + nst, j % nst);  // both MMAs that read slot j % nst are done
         __syncwarp();
     };
 
-    if constexpr (WS) {
+    {
       if (warp == NWARP_C) {
         // ---- the MMA warp: one thread, no arithmetic, no CTA barrier inside the loop
         if (lane == 0 && nt > 0) {
@@ -557,21 +511,30 @@ __global__ void __launch_bounds__(128 * RG + (WS ? 64 : 0), (L == 1 && RG <= 2) 
         }
         __syncwarp();
       } else {
-        // ---- the arithmetic warps
-        float alpha_p[NRG];  // rescale factors of the tile before the current one (its output is folded in late)
+        // ---- the arithmetic warps.  Decode keeps the running maxima and rescale factors of its 4 rows in every
+        // thread's registers (one named barrier per tile); verify keeps them in shared memory, written by one
+        // thread per row of the row group between two named barriers.
+        float alpha_p[L == 1 ? NRG : 1];  // decode: rescale factors of the tile before the current one (folded in late)
 #pragma unroll
-        for (int g = 0; g < NRG; ++g) alpha_p[g] = 1.0f;
+        for (int g = 0; g < (L == 1 ? NRG : 1); ++g) alpha_p[g] = 1.0f;
+        auto rg_sync = [&]() {  // the four warps of this row group
+            if (rg == 0) named_bar_sync<1>(128);
+            else if (rg == 1) named_bar_sync<2>(128);
+            else if (rg == 2) named_bar_sync<6>(128);
+            else named_bar_sync<7>(128);
+        };
         int slot = 0, ph = 0, slot_p = 0, ph_p = 0;  // ring slot / fill parity of tile i and of tile i - 1
         for (int i = 0; i < nt; ++i) {
             ok = mbar_wait(sdone(slot), ph, p.status, where | 5) && ok;
             tc_fence_after();
             const int pos = (t_begin + i) * kTileKeys + ktid;  // this thread's key position
-            const bool vis = pos < seq && (W == 0 || pos > seq - W);
             float skeep[NRG];
 #pragma unroll
             for (int c0 = 0; c0 < NRG; c0 += BR) {
                 float sc[BR];
                 load_scores(i, r_lo + c0, sc);
+                const int j = (r_lo + c0) >> 3;
+                const bool vis = pos < seq && (W == 0 || pos > seq + j - W);
 #pragma unroll
                 for (int g = 0; g < BR; ++g) {
                     const float sv = vis ? sc[g] * s_scale : kNeg;
@@ -580,26 +543,34 @@ __global__ void __launch_bounds__(128 * RG + (WS ? 64 : 0), (L == 1 && RG <= 2) 
                     if (lane == 0) wred_s[i & 1][kq][r_lo + c0 + g] = mx;
                 }
             }
-            // the four warps of this row group; the maxima buffers alternate, so one barrier per tile is enough
-            if (rg == 0) named_bar_sync<1>(128);
-            else named_bar_sync<2>(128);
-            float tm[NRG];
+            rg_sync();  // the maxima buffers alternate, so decode needs no second barrier
+            if constexpr (L == 1) {
+                float tm[NRG];
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
+                for (int w = 0; w < 4; ++w) {
 #pragma unroll
-                for (int q4 = 0; q4 < NRG / 4; ++q4) {
-                    const float4 a = *reinterpret_cast<const float4*>(&wred_s[i & 1][w][r_lo + 4 * q4]);
-                    const float v4[4] = {a.x, a.y, a.z, a.w};
+                    for (int q4 = 0; q4 < NRG / 4; ++q4) {
+                        const float4 a = *reinterpret_cast<const float4*>(&wred_s[i & 1][w][r_lo + 4 * q4]);
+                        const float v4[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) tm[4 * q4 + g] = w == 0 ? v4[g] : fmaxf(tm[4 * q4 + g], v4[g]);
+                        for (int g = 0; g < 4; ++g) tm[4 * q4 + g] = w == 0 ? v4[g] : fmaxf(tm[4 * q4 + g], v4[g]);
+                    }
                 }
-            }
 #pragma unroll
-            for (int g = 0; g < NRG; ++g) {
-                const float mn = fmaxf(tm[g], m_r[g]);
-                alpha_p[g] = alpha_r[g];
-                alpha_r[g] = ex2(m_r[g] - mn);
-                m_r[g] = mn;
+                for (int g = 0; g < NRG; ++g) {
+                    const float mn = fmaxf(tm[g], m_r[g]);
+                    alpha_p[g] = alpha_r[g];
+                    alpha_r[g] = ex2(m_r[g] - mn);
+                    m_r[g] = mn;
+                }
+            } else {
+                if (ktid < NRG) {
+                    const int r = r_lo + ktid;
+                    const float mo = m_s[r];
+                    const float mn = fmaxf(fmaxf(fmaxf(wred_s[i & 1][0][r], wred_s[i & 1][1][r]), fmaxf(wred_s[i & 1][2][r], wred_s[i & 1][3][r])), mo);
+                    alpha_s[i & 1][r] = ex2(mo - mn);
+                    m_s[r] = mn;
+                }
             }
             // V rows past the cached length may hold anything (even NaN bytes): zero them so that 0 * V stays 0
             if (rg == 0 && pos >= seq) {
@@ -608,16 +579,20 @@ __global__ void __launch_bounds__(128 * RG + (WS ? 64 : 0), (L == 1 && RG <= 2) 
 #pragma unroll
                 for (int c = 0; c < 8; ++c) reinterpret_cast<uint4*>(vrow)[c] = make_uint4(0, 0, 0, 0);
             }
+            if constexpr (L != 1) rg_sync();
             // p = 2^(s - m) as two E4M3 terms into P buffer i & 1 (its previous reader, the second MMA of tile
             // i - 2, was waited for at the end of the last iteration)
             uint8_t* pb = g_p + (i & 1) * QP_BYTES;
 #pragma unroll
             for (int g = 0; g < NRG; g += 2) {  // two rows per conversion instruction
                 const int n = r_lo + g;
-                const float pr0 = vis ? ex2(skeep[g] - m_r[g]) : 0.0f;
-                const float pr1 = vis ? ex2(skeep[g + 1] - m_r[g + 1]) : 0.0f;
-                l_part[g] = l_part[g] * alpha_r[g] + pr0;
-                l_part[g + 1] = l_part[g + 1] * alpha_r[g + 1] + pr1;
+                const bool vis = pos < seq && (W == 0 || pos > seq + (n >> 3) - W);  // rows n and n + 1: same token
+                const float m0 = L == 1 ? m_r[g] : m_s[n], m1 = L == 1 ? m_r[g + 1] : m_s[n + 1];
+                const float a0 = L == 1 ? alpha_r[g] : alpha_s[i & 1][n], a1 = L == 1 ? alpha_r[g + 1] : alpha_s[i & 1][n + 1];
+                const float pr0 = vis ? ex2(skeep[g] - m0) : 0.0f;
+                const float pr1 = vis ? ex2(skeep[g + 1] - m1) : 0.0f;
+                l_part[g] = l_part[g] * a0 + pr0;
+                l_part[g + 1] = l_part[g + 1] * a1 + pr1;
                 const float ps0 = pr0 * kPScale, ps1 = pr1 * kPScale;
                 const uint32_t bh = f2_to_e4m3x2(ps0, ps1);
                 const float2 back = e4m3x2_to_f2(bh);
@@ -637,118 +612,11 @@ __global__ void __launch_bounds__(128 * RG + (WS ? 64 : 0), (L == 1 && RG <= 2) 
         }
         if (nt > 0) finish_tile(nt - 1, alpha_r, odone(slot_p), ph_p);
       }
-    } else {
-    if (issuer && nt > 0) {
-        ok = mbar_wait(full(0), 0, p.status, where | 3);
-        tc_fence_after();
-        if (ok) issue_mma1(0, 0, sbar(0));
     }
-    __syncwarp();
-    for (int i = 0; i < nt; ++i) {
-        if (SBUF == 2 && issuer && ok && i + 1 < nt) {  // next tile's scores, computed while this tile's softmax runs
-            ok = mbar_wait(full((i + 1) % nst), ((i + 1) / nst) & 1, p.status, where | 4);
-            tc_fence_after();
-            if (ok) issue_mma1(i + 1, (i + 1) % nst, sbar(i + 1));
-        }
-        __syncwarp();
-        ok = mbar_wait(sbar(i), (SBUF == 2 ? (i >> 1) : i) & 1, p.status, where | 5) && ok;
-        tc_fence_after();
-        const int pos = (t_begin + i) * kTileKeys + ktid;  // this thread's key position
-        float skeep[NRG];  // this key's scaled scores of the thread's rows
-        // pass 1: tile maximum per query row
-#pragma unroll
-        for (int c0 = 0; c0 < NRG; c0 += BR) {
-            float sc[BR];
-            load_scores(i, r_lo + c0, sc);
-            const int j = (r_lo + c0) >> 3;
-            const bool vis = pos < seq && (W == 0 || pos > seq + j - W);
-#pragma unroll
-            for (int g = 0; g < BR; ++g) {
-                const float sv = vis ? sc[g] * s_scale : kNeg;
-                skeep[c0 + g] = sv;
-                const float mx = redux_max(sv);
-                if (lane == 0) wred[kq][r_lo + c0 + g] = mx;
-            }
-        }
-        if (i > 0) finish_tile(i - 1, alpha_r, bar_o, (i - 1) & 1);
-        if constexpr (SBUF == 1) tc_fence_before();  // the scores are in registers: their buffer may be overwritten
-        __syncthreads();
-        if constexpr (L == 1) {
-            // every thread folds the four warps' maxima of its rows itself: no second barrier, no shared-memory round trip
-            float tm[NRG];
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-#pragma unroll
-                for (int q4 = 0; q4 < NRG / 4; ++q4) {
-                    const float4 a = *reinterpret_cast<const float4*>(&wred[w][r_lo + 4 * q4]);
-                    const float v4[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) tm[4 * q4 + g] = w == 0 ? v4[g] : fmaxf(tm[4 * q4 + g], v4[g]);
-                }
-            }
-#pragma unroll
-            for (int g = 0; g < NRG; ++g) {
-                const float mn = fmaxf(tm[g], m_r[g]);
-                alpha_r[g] = ex2(m_r[g] - mn);
-                m_r[g] = mn;
-            }
-        } else {
-            if (tid < NR) {
-                const float mo = m_s[tid];
-                const float mn = fmaxf(fmaxf(fmaxf(wred[0][tid], wred[1][tid]), fmaxf(wred[2][tid], wred[3][tid])), mo);
-                alpha_s[tid] = ex2(mo - mn);
-                m_s[tid] = mn;
-            }
-            // one score buffer: the next tile's scores start now, under this tile's exponentials
-            if (issuer && ok && i + 1 < nt) {
-                ok = mbar_wait(full((i + 1) % nst), ((i + 1) / nst) & 1, p.status, where | 4);
-                tc_fence_after();
-                if (ok) issue_mma1(i + 1, (i + 1) % nst, sbar(i + 1));
-            }
-            __syncwarp();
-        }
-        // V rows past the cached length may hold anything (even NaN bytes): zero them so that 0 * V stays 0
-        if (rg == 0 && pos >= seq) {
-            uint8_t* vrow = gbase + (i % nst) * kStageBytes + kTileKeys * 128 + ktid * 128;
-#pragma unroll
-            for (int c = 0; c < 8; ++c) reinterpret_cast<uint4*>(vrow)[c] = make_uint4(0, 0, 0, 0);
-        }
-        if constexpr (L != 1) __syncthreads();
-        // pass 2: p = 2^(s - m) as two E4M3 terms (the second times 16), bytes of the B operand P[row][key]
-#pragma unroll
-        for (int c0 = 0; c0 < NRG; c0 += BR) {
-            const int j = (r_lo + c0) >> 3;
-            const bool vis = pos < seq && (W == 0 || pos > seq + j - W);
-#pragma unroll
-            for (int g = 0; g < BR; ++g) {
-                const int n = r_lo + c0 + g;
-                const float pr = vis ? ex2(skeep[c0 + g] - (L == 1 ? m_r[c0 + g] : m_s[n])) : 0.0f;
-                l_part[c0 + g] = l_part[c0 + g] * (L == 1 ? alpha_r[c0 + g] : alpha_s[n]) + pr;
-                const float ps = pr * kPScale;
-                const uint32_t bh = f_to_e4m3(ps);
-                const uint32_t bl = f_to_e4m3((ps - e4m3_to_f(bh)) * kLoScale);
-                g_p[swz128(n, ktid)] = static_cast<uint8_t>(bh);
-                g_p[swz128(NR + n, ktid)] = static_cast<uint8_t>(bl);
-            }
-        }
-        tc_fence_before();
-        fence_proxy_async_smem();
-        __syncthreads();
-        if (issuer && ok) {
-            tc_fence_after();
-            issue_mma2(i, i % nst, bar_o);
-        }
-        __syncwarp();
-    }
-    if (nt > 0) finish_tile(nt - 1, alpha_r, bar_o, (nt - 1) & 1);
-    }
-    // From here on the arithmetic threads only; the issuing warp of the WS form goes straight to the cluster barrier.
+    // From here on the arithmetic threads only; the two issuing warps go straight to the cluster barrier.
     const int rows_per = NR / C;  // query rows each CTA finalises (C divides NR)
-    auto csync = [&]() {
-        if constexpr (WS) named_bar_sync<3>(NTHR_C);
-        else __syncthreads();
-    };
-    if (!WS || warp < NWARP_C) {
+    auto csync = [&]() { named_bar_sync<3>(NTHR_C); };
+    if (warp < NWARP_C) {
     if constexpr (L == 1) {
 #pragma unroll
         for (int g = 0; g < NRG; ++g)
@@ -817,13 +685,13 @@ __global__ void __launch_bounds__(128 * RG + (WS ? 64 : 0), (L == 1 && RG <= 2) 
             float mx = m_s[tid];
             const float mo = mx;
             for (int r = 0; r < L; ++r) mx = fmaxf(mx, sc_tail[tid][r]);
-            alpha_s[tid] = ex2(mo - mx);
+            alpha_s[0][tid] = ex2(mo - mx);
             m_s[tid] = mx;
         }
         csync();
 #pragma unroll
         for (int n = 0; n < NRG; ++n) {
-            const float a = alpha_s[r_lo + n], m = m_s[r_lo + n];
+            const float a = alpha_s[0][r_lo + n], m = m_s[r_lo + n];
             float o = o_acc[n] * a;
             l_part[n] *= a;
 #pragma unroll
@@ -857,7 +725,7 @@ __global__ void __launch_bounds__(128 * RG + (WS ? 64 : 0), (L == 1 && RG <= 2) 
     }
     }
     cluster_sync_all();
-    if (!WS || warp < NWARP_C) {
+    if (warp < NWARP_C) {
 
     // this CTA's rows nl = rg, rg + RG, ...: thread = channel d
     float val[NRG];
@@ -910,10 +778,10 @@ __global__ void __launch_bounds__(128 * RG + (WS ? 64 : 0), (L == 1 && RG <= 2) 
     if (warp == 0) tmem_dealloc(tmem, kCols);
 }
 
-template <int L, int ISS, int RG, bool WS>
+template <int L, int RG>
 int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
     constexpr int NR = 8 * L, NP = 2 * NR;
-    constexpr int kColsHost = attn_tmem_cols(L, ISS, WS);
+    constexpr int kColsHost = attn_tmem_cols(L);
     const int tile_cap = (q->max_pages * q->page_size + kTileKeys - 1) / kTileKeys;
     int tiles_max = tile_cap;
     if (q->window > 0) tiles_max = min(tiles_max, q->window / kTileKeys + 2);
@@ -922,7 +790,7 @@ int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
     // and the next tile's scores are issued one iteration early
     if (q->stages != 0 && (q->stages < 3 || q->stages > kAttnMaxStages)) return MSK_ERR_INVALID;
     int nst = q->stages > 0 ? q->stages : 3;
-    int smem = 1024 + nst * kStageBytes + (WS ? 3 : 2) * NP * 128 + NR * 128 * 4;
+    int smem = 1024 + nst * kStageBytes + 3 * NP * 128 + NR * 128 * 4;
     if (smem > 232448) return MSK_ERR_INVALID;
     int resident = min(232448 / (smem + 2048), 512 / kColsHost);  // CTAs per SM: shared memory, tensor memory
     if (resident < 1) resident = 1;
@@ -940,9 +808,10 @@ int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
     if (C != 1 && C != 2 && C != 4 && C != 8) return MSK_ERR_INVALID;
     if ((tiles_max + C - 1) / C > kMaxTilesPerCta) return MSK_ERR_UNSUPPORTED;
     // a grid of at most one CTA per SM is bound by the latency of its own copies: give it a deeper ring
-    if (WS && q->stages == 0 && q->B * q->Hkv * C <= 148) {
-        nst = kAttnMaxStages;
-        smem = 1024 + nst * kStageBytes + 3 * NP * 128 + NR * 128 * 4;
+    if (q->stages == 0 && (L != 1 || q->B * q->Hkv * C <= 148)) {
+        const int fixed = 1024 + 3 * NP * 128 + NR * 128 * 4;
+        nst = min(kAttnMaxStages, (232448 - fixed) / kStageBytes);
+        smem = fixed + nst * kStageBytes;
     }
 
     CUtensorMap tm_k, tm_v;
@@ -976,13 +845,13 @@ int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MSK_ERR_CUDA;
     static int configured[64] = {};  // per device, like the attribute itself
     if (smem > configured[dev]) {
-        if (cudaFuncSetAttribute(attn_kernel<L, ISS, RG, WS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(attn_kernel<L, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return MSK_ERR_CUDA;
         configured[dev] = smem;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(C, q->Hkv, q->B);
-    cfg.blockDim = dim3(128 * RG + (WS ? 64 : 0), 1, 1);
+    cfg.blockDim = dim3(128 * RG + 64, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attrs[2];
@@ -999,7 +868,7 @@ int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
     }
     cfg.attrs = attrs;
     cfg.numAttrs = na;
-    return cudaLaunchKernelEx(&cfg, attn_kernel<L, ISS, RG, WS>, tm_k, tm_v, a) == cudaSuccess ? 0 : MSK_ERR_CUDA;
+    return cudaLaunchKernelEx(&cfg, attn_kernel<L, RG>, tm_k, tm_v, a) == cudaSuccess ? 0 : MSK_ERR_CUDA;
 }
 
 }  // namespace msk
@@ -1011,13 +880,10 @@ extern "C" int msk_attn_decode(const MskAttnParams* q, int* status, void* stream
         return MSK_ERR_INVALID;
     if (q->d != 128 || q->Hkv < 1 || q->Hq != 8 * q->Hkv || q->B < 1) return MSK_ERR_UNSUPPORTED;
     if (q->page_size < 8 || q->page_size > 128 || (q->page_size & (q->page_size - 1)) != 0) return MSK_ERR_UNSUPPORTED;
-    if (q->issuers != 0 && q->issuers != 1 && q->issuers != 2) return MSK_ERR_INVALID;
-    if (q->row_groups != 0 && q->row_groups != 2) return MSK_ERR_INVALID;
+    if (q->issuers != 0 && q->issuers != 1) return MSK_ERR_INVALID;
+    if (q->row_groups != 0 && q->row_groups != (q->L == 1 ? 2 : 4)) return MSK_ERR_INVALID;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // decode: a copying warp and an MMA warp beside the eight arithmetic warps; issuers = 2 selects the form in which
-    // two of the arithmetic warps issue everything themselves (a quarter slower on long contexts, kept for comparison)
-    if (q->L == 1 && q->issuers == 2) return launch_attn<1, 2, 2, false>(q, status, s);
-    if (q->L == 1) return launch_attn<1, 1, 2, true>(q, status, s);
-    if (q->L == 8) return launch_attn<8, 2, 4, false>(q, status, s);
+    if (q->L == 1) return launch_attn<1, 2>(q, status, s);  // 8 arithmetic warps + MMA warp + copying warp, 2 CTAs per SM
+    if (q->L == 8) return launch_attn<8, 4>(q, status, s);  // 16 arithmetic warps + the same two
     return MSK_ERR_UNSUPPORTED;
 }
