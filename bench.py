@@ -252,7 +252,7 @@ def single_gpu_configs(weights, dev, peak):
 
 # dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes, from the captures summarised under profiles/
 # (attention 32 requests x 8192; experts 32 tokens; projection 16 x 6144 x 4096)
-NCU_TRAFFIC_RATIO = {"attn_decode": 1.013, "experts": 1.018, "proj_skinny": 0.998}
+NCU_TRAFFIC_RATIO = {"attn_decode": 1.014, "experts": 1.018, "proj_skinny": 0.998}
 
 
 def run_ours(args):
