@@ -213,6 +213,155 @@ __global__ void __launch_bounds__(256) router_kernel(RouterArgs p) {
     }
 }
 
+// Many tokens: one block takes 32 tokens x all experts (<= 128) x `phases` tiles of 128 k.  Thread = 4 tokens x 4
+// experts (16 FP32 accumulators: 8 shared-memory loads per 64 FMAs, where the kernel above has 5 per 16), the grid is
+// about one block per SM, and there is one ticket per token group instead of two stages: the block that draws the
+// last ticket adds the K splits' partials in split order, writes the logits and chooses the experts.  A thread ends
+// up with the logits of tokens tw + 8 i and experts lane + 32 j: exactly what a warp needs to choose for its tokens.
+constexpr int kWideE = 128;
+constexpr int kRouterWideSmem = (kWideE * (kRouterK + 4) + kRouterT * kRouterK) * 4;
+
+__global__ void __launch_bounds__(256) router_wide_kernel(RouterArgs p) {
+    extern __shared__ __align__(16) float wsm[];
+    float (*Rs)[kRouterK + 4] = reinterpret_cast<float (*)[kRouterK + 4]>(wsm);                     // [128][132]
+    float (*hs)[kRouterK] = reinterpret_cast<float (*)[kRouterK]>(wsm + kWideE * (kRouterK + 4));  // [32][128]
+    __shared__ int last;
+    const int ks = blockIdx.x, tg = blockIdx.y, tid = threadIdx.x, KS = gridDim.x;
+    const int tw = tid >> 5, el = tid & 31;
+    const int kb = ks * kRouterK * p.phases;
+    const int t0 = tg * kRouterT, nt = min(kRouterT, p.T - t0);
+    auto load_r = [&](int k0, float4 (&r)[16]) {  // rows tw + 8 j of the weight tile, float4 column el
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int e = tw + 8 * j;
+            r[j] = e < p.E ? __ldg(reinterpret_cast<const float4*>(p.R + static_cast<size_t>(e) * p.H + k0) + el)
+                           : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+    };
+    float4 r[16];
+    load_r(kb, r);  // the router weights do not depend on the previous kernel
+    pdl_wait();
+    pdl_launch_dependents();
+    float acc[4][4];  // [token tw + 8 i][expert el + 32 j]
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    uint2 wraw = make_uint2(0, 0);
+    float4 h[4];
+    auto load_h = [&](int k0) {
+        wraw = __ldg(reinterpret_cast<const uint2*>(p.w + k0) + el);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            h[i] = __ldcg(reinterpret_cast<const float4*>(p.s1 + static_cast<size_t>(t0 + min(tw + 8 * i, nt - 1)) * p.H + k0) + el);
+    };
+    load_h(kb);
+    for (int ph = 0; ph < p.phases; ++ph) {
+        const float w0 = 1.0f + bf16lo(wraw.x), w1 = 1.0f + bf16hi(wraw.x), w2 = 1.0f + bf16lo(wraw.y), w3 = 1.0f + bf16hi(wraw.y);
+        __syncthreads();  // the previous tile has been used
+#pragma unroll
+        for (int j = 0; j < 16; ++j) *reinterpret_cast<float4*>(&Rs[tw + 8 * j][4 * el]) = r[j];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            *reinterpret_cast<float4*>(&hs[tw + 8 * i][4 * el]) =
+                tw + 8 * i < nt ? make_float4(h[i].x * w0, h[i].y * w1, h[i].z * w2, h[i].w * w3) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        __syncthreads();
+        if (ph + 1 < p.phases) {  // the next tile's loads fly under this tile's arithmetic
+            load_r(kb + (ph + 1) * kRouterK, r);
+            load_h(kb + (ph + 1) * kRouterK);
+        }
+#pragma unroll 4
+        for (int k4 = 0; k4 < kRouterK / 4; ++k4) {
+            float4 rr[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) rr[j] = *reinterpret_cast<const float4*>(&Rs[el + 32 * j][4 * k4]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float4 hh = *reinterpret_cast<const float4*>(&hs[tw + 8 * i][4 * k4]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[i][j] = fmaf(hh.x, rr[j].x, acc[i][j]), acc[i][j] = fmaf(hh.y, rr[j].y, acc[i][j]);
+                    acc[i][j] = fmaf(hh.z, rr[j].z, acc[i][j]), acc[i][j] = fmaf(hh.w, rr[j].w, acc[i][j]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int t = tw + 8 * i;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (t < nt && el + 32 * j < p.E) p.part[(static_cast<size_t>(ks) * p.T + t0 + t) * p.E + el + 32 * j] = acc[i][j];
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) last = atomicAdd(p.ticket + tg, 1) == KS - 1;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    // per-token 1/rms: lane q sums parts q, q + 32, ...
+    float rs[4];
+    {
+        float ss[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int q = el; q < p.ssq_parts; q += 32)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (tw + 8 * i < nt) ss[i] += __ldcg(p.ssq + q * p.T + t0 + tw + 8 * i);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss[i] += __shfl_xor_sync(0xffffffffu, ss[i], o);
+            rs[i] = rsqrtf(ss[i] / p.H + p.eps);
+            if (el == 0 && tw + 8 * i < nt) p.ssq[p.ssq_parts * p.T + t0 + tw + 8 * i] = ss[i];  // total, one value for the experts' GEMM
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    // split order (the sum does not depend on which block came last), four splits' loads in flight together: one
+    // round trip to L2 per batch, not per split
+    for (int s0 = 0; s0 < KS; s0 += 4) {
+        float v[4][4][4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    v[q][i][j] = (s0 + q < KS && tw + 8 * i < nt && el + 32 * j < p.E)
+                                     ? __ldcg(p.part + (static_cast<size_t>(s0 + q) * p.T + t0 + tw + 8 * i) * p.E + el + 32 * j)
+                                     : 0.0f;
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] += v[q][i][j];
+    }
+    for (int i = 0; i < 4; ++i) {
+        const int t = tw + 8 * i;
+        if (t >= nt) break;  // warp-uniform
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int e = el + 32 * j;
+            if (e < p.E) {
+                float o = acc[i][j] * rs[i];
+                if (p.bias != nullptr && !p.sigmoid_bias) o += p.bias[e];
+                p.logits[static_cast<size_t>(t0 + t) * p.E + e] = o;
+            }
+        }
+        // every lane reads back exactly the logits it has just written
+        if (p.sigmoid_bias)
+            route_token_sigmoid(p.logits + static_cast<size_t>(t0 + t) * p.E, p.bias, p.multiplier, p.E, p.top_k, el,
+                                p.ids_out + (t0 + t) * p.top_k, p.wts_out + (t0 + t) * p.top_k);
+        else
+            route_token(p.logits + static_cast<size_t>(t0 + t) * p.E, p.E, p.top_k, el, p.ids_out + (t0 + t) * p.top_k,
+                        p.wts_out + (t0 + t) * p.top_k);
+    }
+    if (tid == 0) p.ticket[tg] = 0;  // ready for the next call
+}
+
 // Residual boundary of the reference's own layer form (muse_decode_layer/reference.py:339-344,452-455,473-476):
 //   branch' = branch * (1 + branch_w)                      (optional)
 //   s_out   = alpha * stream + beta * rmsnorm(branch', branch_eps),  (alpha, beta) from the gate; without a gate a plain add
@@ -406,6 +555,21 @@ extern "C" int msk_router(const MskRouterParams* q, int* status, void* stream) {
     r.top_k = q->top_k, r.ids_out = q->topk_ids, r.wts_out = q->topk_weights;
     r.sigmoid_bias = q->sigmoid_bias, r.multiplier = q->multiplier;
     const int et = (q->E + kRouterE - 1) / kRouterE, n_tg = (q->T + kRouterT - 1) / kRouterT;
+    if (n_tg >= 4 && q->E <= kWideE) {
+        // many tokens: whole expert range per block, about one block per SM
+        int tiles = q->H / kRouterK, ph = 1;
+        while (n_tg * (tiles / ph) > 160 && (tiles / ph) % 2 == 0) ph *= 2;
+        r.phases = ph;
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MSK_ERR_CUDA;
+        static bool configured[64] = {};  // per device, like the attribute itself
+        if (!configured[dev]) {
+            if (cudaFuncSetAttribute(router_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRouterWideSmem) != cudaSuccess)
+                return MSK_ERR_CUDA;
+            configured[dev] = true;
+        }
+        return launch1(router_wide_kernel, dim3(tiles / ph, n_tg), dim3(256), kRouterWideSmem, static_cast<cudaStream_t>(stream), q->pdl, r);
+    }
     // few tokens: as many K splits as there are 128-k tiles (the 2 MB of router weights spread over the SMs);
     // four token groups or more: blocks of four tiles (the K-split count must stay a multiple of 8)
     r.phases = (n_tg >= 4 && (q->H / kRouterK) % 32 == 0) ? 4 : 1;

@@ -119,8 +119,8 @@ def test_layer_benchmark_shapes(batch, q_len, bench_weights):
 def test_layer_256_requests(bench_weights):
     """The token count of the 256-request benchmark step (contexts kept short so that the CPU oracle stays cheap):
     attention takes the requests longest first over several waves of CTAs (once with one CTA per request and KV
-    head, once with the keys split over two, as the benchmark's long contexts make the launch choose), the router
-    runs eight token groups with both ticket stages, the experts read gathered input rows with all 128 experts
+    head, once with the keys split over two), the router
+    runs its many-token kernel over eight token groups, the experts read gathered input rows with all 128 experts
     touched, and both projections run at M = 256 with the fused epilogue."""
     g = torch.Generator().manual_seed(5)
     seqs = torch.randint(1, 700, (256,), generator=g).tolist()
