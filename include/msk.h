@@ -188,7 +188,7 @@ typedef struct {
     float post_eps;
     int H, I;
     float* h1_part;             /* scratch fp32 [s1, T*top_k, 2I]; only needed for s1 > 1 */
-    float* y_part;              /* scratch fp32 [s2, T*top_k, H] */
+    float* y_part;              /* scratch fp32 [s2, T*top_k, H]: the down projections' sums before the experts' global scales (the combine kernel applies them) */
     void* inter_sorted;         /* scratch fp16 [T*top_k, I]: activations between the GEMMs, expert-list order */
     void* x_sorted;             /* scratch fp16: [T, H] up to 32 tokens, else [T*top_k, H] (inputs gathered in
                                    expert-list order); not needed for T <= 32 with x_fp16 */

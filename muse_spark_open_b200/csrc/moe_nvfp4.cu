@@ -642,7 +642,10 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
                 myrow = off + lane;
             }
             const float myscale = (MODE == 1 && p.x_ssq != nullptr && mypair >= 0) ? rs_s[mypair / p.route.top_k] : 1.0f;
-            const float scale = __ldg(p.gs + e);  // the expert's global scale (requested before the wait)
+            // gemm 1 applies the expert's global scale (requested before the wait); gemm 2 leaves it, like everything
+            // else that is per expert or per pair, to the combine kernel: its epilogue bounds the rate at many tokens
+            const float scale = MODE == 1 ? __ldg(p.gs + e) : 1.0f;
+            const int myoff = mypair >= 0 ? mypair * p.R : -1;  // of the pair's row in a partial plane
             ok = mbar_wait<kSleepEpilogue>(smem_u32(&bar.d_full[db]), (uc >> 1) & 1, p.status, where | 6);
             if (!ok) break;
             tc_fence_after();
@@ -679,15 +682,14 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_gemm_kernel(const __grid_c
 #pragma unroll
                     for (int w = 0; w < kIssuers; ++w)
                         if (has & (1u << w)) v += __uint_as_float(t[w][c]);
-                    const float sc = __shfl_sync(0xffffffffu, myscale, c0 + c);
-                    v *= scale * sc;
+                    if (MODE == 1) v *= scale * __shfl_sync(0xffffffffu, myscale, c0 + c);
                     if (MODE == 1 && p.fuse_act) {
                         const int sr = __shfl_sync(0xffffffffu, myrow, c0 + c);
                         const float up = __shfl_xor_sync(0xffffffffu, v, 16);
                         if (sr >= 0 && lane < 16) dst_act[static_cast<size_t>(sr) * p.inner] = __float2half_rn(clamp_f16(silu_mul(v, up)));
                     } else {
-                        const int pr = __shfl_sync(0xffffffffu, mypair, c0 + c);
-                        if (pr >= 0) dst[static_cast<size_t>(pr) * p.R] = v;
+                        const int off = __shfl_sync(0xffffffffu, myoff, c0 + c);
+                        if (off >= 0) dst[off] = v;
                     }
                 }
             }
@@ -746,7 +748,8 @@ struct MoeCombineArgs {
     const int* ids;
     const float* wts;
     int top_k, local_start, local_count, H, S, P, ld_ids;
-    const float* yp;            // [S][P][H]
+    const float* yp;            // [S][P][H]: gemm 2's sums without the experts' global scales
+    const float* gs;            // [local_count] global scales of the down projections
     const __nv_bfloat16* post_w;
     float eps;
     const float* resid;
@@ -798,14 +801,15 @@ __global__ void __launch_bounds__(kCombineThreads) moe_combine_kernel(MoeCombine
         peer_row = reinterpret_cast<float*>(static_cast<char*>(p.peers[t / p.rows_per_peer]) + p.out_off) +
                    static_cast<size_t>(t % p.rows_per_peer) * p.ldo;
     int local[8];
-    float w[8];
+    float w[8], g[8];
 #pragma unroll
     for (int s = 0; s < 8; ++s) {
-        local[s] = 0, w[s] = 0.0f;
+        local[s] = 0, w[s] = 0.0f, g[s] = 0.0f;
         if (s < p.top_k) {
             const int e = __ldcg(p.ids + t * p.ld_ids + s) - p.local_start;
             local[s] = e >= 0 && e < p.local_count;
             w[s] = __ldcg(p.wts + t * p.ld_ids + s);
+            if (local[s]) g[s] = __ldg(p.gs + e);
         }
     }
     bool any_local = false;
@@ -855,7 +859,7 @@ __global__ void __launch_bounds__(kCombineThreads) moe_combine_kernel(MoeCombine
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
             float4& y = z[it][s];
-            y.x *= f[0], y.y *= f[1], y.z *= f[2], y.w *= f[3];
+            y.x *= f[0] * g[s], y.y *= f[1] * g[s], y.z *= f[2] * g[s], y.w *= f[3] * g[s];
             ss[s] += y.x * y.x + y.y * y.y + y.z * y.z + y.w * y.w;
         }
     }
@@ -1074,7 +1078,7 @@ extern "C" int msk_moe_forward(const MskMoeParams* q, int* status, void* stream)
     MoeCombineArgs c{};
     c.ids = q->topk_ids, c.wts = q->topk_weights, c.top_k = q->top_k, c.local_start = q->local_start;
     c.ld_ids = ra.ld_ids;
-    c.local_count = q->local_count, c.H = q->H, c.S = s2, c.P = P, c.yp = q->y_part;
+    c.local_count = q->local_count, c.H = q->H, c.S = s2, c.P = P, c.yp = q->y_part, c.gs = q->w2_gs;
     c.post_w = static_cast<const __nv_bfloat16*>(q->post_norm_w), c.eps = q->post_eps, c.resid = q->resid, c.ldr = q->ldr;
     c.out = q->out, c.out_fp32 = q->out_fp32, c.ldo = q->ldo;
     c.out_copy = static_cast<__nv_bfloat16*>(q->out_copy), c.ldc = q->ldc;
