@@ -128,3 +128,24 @@ def test_attention_replay_is_bitwise_stable():
     a = _run(data)[0]
     b = _run(data)[0]
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("q_len,stages", [(1, 3), (1, 4), (1, 5), (1, 6), (8, 3), (8, 4)])
+def test_attention_ring_depths(q_len, stages):
+    """Every ring depth the launch accepts (the library itself picks 3, or the deepest that fits when the grid is at
+    most one CTA per SM): slots and barrier parities wrap at different tiles, the result must not change."""
+    data = oattn.make_input(3, [1500, 129, 2900], seed=21, q_len=q_len, hq=16, hkv=2, d=128, page=64, window=0,
+                            rope_theta=0.0)
+    base = _run(data, chunks=1)[0]
+    out, k_new, v_new, _ = _run(data, chunks=1, stages=stages)
+    assert torch.equal(out, base), (q_len, stages)
+    _check(data, out, k_new, v_new, f"stages {stages}")
+
+
+def test_attention_rejects_ring_depths_that_do_not_fit():
+    from muse_spark_open_b200 import abi, attention
+    data = oattn.make_input(1, [300], seed=3, q_len=8, hq=16, hkv=2, d=128, page=64, window=0, rope_theta=0.0)
+    dev = oattn.to_device(data, "cuda")
+    for stages in (2, 5, 7):  # below the minimum; beyond shared memory for the verify form; beyond the maximum
+        with pytest.raises(abi.MskError):
+            attention.kernel_fn(dev, stages=stages)
