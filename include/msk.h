@@ -110,7 +110,7 @@ typedef struct {
     int B, L, Hq, Hkv, d, page_size, num_pages, window;
     float qk_scale_factor, sm_scale;
     int chunks;               /* split-KV ways = cluster size (1, 2, 4 or 8); 0 = pick */
-    int stages;               /* K/V tile ring depth (3 to 6); 0 = pick: 3, or 6 when the grid is at most one CTA per SM */
+    int stages;               /* K/V tile ring depth (3 to 6, as far as shared memory allows); 0 = pick: 3 for decode, 4 for verify */
     int issuers;              /* MMA-issuing warps beside the arithmetic warps: 1; 0 = pick */
     int pdl;
     int row_groups;           /* sets of four arithmetic warps that split the 8 L query rows of a KV head: 2 (decode), 4 (verify); 0 = pick */

@@ -807,8 +807,10 @@ int launch_attn(const MskAttnParams* q, int* status, cudaStream_t stream) {
     }
     if (C != 1 && C != 2 && C != 4 && C != 8) return MSK_ERR_INVALID;
     if ((tiles_max + C - 1) / C > kMaxTilesPerCta) return MSK_ERR_UNSUPPORTED;
-    // a grid of at most one CTA per SM is bound by the latency of its own copies: give it a deeper ring
-    if (q->stages == 0 && (L != 1 || q->B * q->Hkv * C <= 148)) {
+    // The verify form is one CTA per SM whatever the ring: it takes the deepest that fits.  Decode stays at three
+    // slots even when the grid is small: a deeper ring gained 0.3 us there and, being one CTA per SM, could not hold
+    // 16 clusters of 8 at once (4 requests x 4 KV heads x 8 chunks took 28 us instead of 17).
+    if (q->stages == 0 && L != 1) {
         const int fixed = 1024 + 3 * NP * 128 + NR * 128 * 4;
         nst = min(kAttnMaxStages, (232448 - fixed) / kStageBytes);
         smem = fixed + nst * kStageBytes;

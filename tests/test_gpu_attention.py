@@ -132,8 +132,8 @@ def test_attention_replay_is_bitwise_stable():
 
 @pytest.mark.parametrize("q_len,stages", [(1, 3), (1, 4), (1, 5), (1, 6), (8, 3), (8, 4)])
 def test_attention_ring_depths(q_len, stages):
-    """Every ring depth the launch accepts (the library itself picks 3, or the deepest that fits when the grid is at
-    most one CTA per SM): slots and barrier parities wrap at different tiles, the result must not change."""
+    """Every ring depth the launch accepts (the library itself picks 3 for decode and 4 for verify): slots and barrier
+    parities wrap at different tiles, the result must not change."""
     data = oattn.make_input(3, [1500, 129, 2900], seed=21, q_len=q_len, hq=16, hkv=2, d=128, page=64, window=0,
                             rope_theta=0.0)
     base = _run(data, chunks=1)[0]
