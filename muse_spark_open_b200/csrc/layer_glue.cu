@@ -555,8 +555,8 @@ extern "C" int msk_router(const MskRouterParams* q, int* status, void* stream) {
     r.top_k = q->top_k, r.ids_out = q->topk_ids, r.wts_out = q->topk_weights;
     r.sigmoid_bias = q->sigmoid_bias, r.multiplier = q->multiplier;
     const int et = (q->E + kRouterE - 1) / kRouterE, n_tg = (q->T + kRouterT - 1) / kRouterT;
-    if (n_tg >= 4 && q->E <= kWideE) {
-        // many tokens: whole expert range per block, about one block per SM
+    if (n_tg >= 3 && q->E <= kWideE) {
+        // many tokens (measured: from three token groups on): whole expert range per block, about one block per SM
         int tiles = q->H / kRouterK, ph = 1;
         while (n_tg * (tiles / ph) > 160 && (tiles / ph) % 2 == 0) ph *= 2;
         r.phases = ph;

@@ -64,7 +64,7 @@ def _run(t, h, e, sigmoid, seed):
     torch.testing.assert_close(wts.double(), want_w, rtol=2e-4, atol=1e-6)
 
 
-@pytest.mark.parametrize("t", [1, 31, 100, 128, 150, 256])
+@pytest.mark.parametrize("t", [1, 31, 64, 70, 100, 128, 150, 256])
 @pytest.mark.parametrize("sigmoid", [False, True])
 def test_router_matches_fp64(t, sigmoid):
     _run(t, 4096, 128, sigmoid, seed=t)
