@@ -73,15 +73,17 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(EpDispatchArgs p) {
         }
         if (tid == 32) *reinterpret_cast<float4*>(row + p.row_bytes - 16) = make_float4(s, 0.0f, 0.0f, 0.0f);
     }
-    __threadfence_system();
+    // The block's stores are ordered before the barrier, the barrier before thread 0's fence: one system-scope fence
+    // per block covers all of them (256 of them cost the step several microseconds).
     __syncthreads();
     if (tid == 0) {
+        __threadfence_system();
         const int old = atomicAdd(p.counter, 1);
         if (old == static_cast<int>(gridDim.x) - 1) {
             *p.counter = 0;
-            __threadfence_system();
+            __threadfence_system();  // every block's rows (each fenced before its ticket) precede the flags
             for (int r = 0; r < p.world; ++r)
-                st_release_sys(reinterpret_cast<int*>(static_cast<char*>(p.peers[r]) + p.flag_off), p.step);
+                st_relaxed_sys(reinterpret_cast<int*>(static_cast<char*>(p.peers[r]) + p.flag_off), p.step);
         }
     }
 }

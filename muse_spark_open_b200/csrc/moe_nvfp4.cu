@@ -776,15 +776,15 @@ constexpr int kCombineThreads = 512;
 // Expert parallelism: every block, after its row is on its way, takes a ticket; the last one tells every peer
 // that this GPU's partial rows of the step are complete.
 __device__ __forceinline__ void combine_signal(const MoeCombineArgs& p, int tid) {
-    __threadfence_system();
-    __syncthreads();
+    __syncthreads();  // the block's stores, then one system-scope fence by the thread that takes the ticket
     if (tid == 0) {
+        __threadfence_system();
         const int old = atomicAdd(p.done_counter, 1);
         if (old == static_cast<int>(gridDim.x) - 1) {
             *p.done_counter = 0;
             __threadfence_system();
             for (int r = 0; r < p.n_peers; ++r)
-                st_release_sys(reinterpret_cast<int*>(static_cast<char*>(p.peers[r]) + p.flag_off), p.flag_value);
+                st_relaxed_sys(reinterpret_cast<int*>(static_cast<char*>(p.peers[r]) + p.flag_off), p.flag_value);
         }
     }
 }

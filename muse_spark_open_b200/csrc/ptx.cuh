@@ -317,6 +317,11 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 __device__ __forceinline__ void st_release_sys(int* p, int v) {
     asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+// A flag store after a __threadfence_system(): the fence orders everything before it, so the store itself can be
+// relaxed.  (A release store per peer made the signalling thread wait for a system-wide flush once per peer.)
+__device__ __forceinline__ void st_relaxed_sys(int* p, int v) {
+    asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
     int v;
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
