@@ -48,8 +48,11 @@ struct EpDispatchArgs {
 
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(EpDispatchArgs p) {
     const int t = blockIdx.x, tid = threadIdx.x;
+    __shared__ uint8_t* peer_s[32];  // the regions' addresses do not depend on the previous kernel: fetched under its tail
+    if (tid < p.world) peer_s[tid] = static_cast<uint8_t*>(p.peers[tid]);
     pdl_wait();
     pdl_launch_dependents();
+    __syncthreads();
     // the row's pieces are loaded once and stored to every region
     const uint4* src = reinterpret_cast<const uint4*>(p.xn + static_cast<size_t>(t) * p.H);
     const int nv = p.H / 8;  // 16-byte pieces of x
@@ -63,7 +66,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(EpDispatchArgs p) {
     const size_t row_off = p.rows_off + (static_cast<size_t>(p.rank) * p.T_local + t) * p.row_bytes;
     for (int r0 = 0; r0 < p.world; ++r0) {
         const int r = (r0 + p.rank) % p.world;  // every rank starts with a different peer
-        uint8_t* row = static_cast<uint8_t*>(p.peers[r]) + row_off;
+        uint8_t* row = peer_s[r] + row_off;
 #pragma unroll
         for (int i = 0; i < 4; ++i)
             if (tid + 256 * i < nv) reinterpret_cast<uint4*>(row)[tid + 256 * i] = v[i];
@@ -83,7 +86,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(EpDispatchArgs p) {
             *p.counter = 0;
             __threadfence_system();  // every block's rows (each fenced before its ticket) precede the flags
             for (int r = 0; r < p.world; ++r)
-                st_relaxed_sys(reinterpret_cast<int*>(static_cast<char*>(p.peers[r]) + p.flag_off), p.step);
+                st_relaxed_sys(reinterpret_cast<int*>(peer_s[r] + p.flag_off), p.step);
         }
     }
 }
